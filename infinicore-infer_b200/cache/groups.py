@@ -1,0 +1,110 @@
+"""Cache groups: layers with the same needs share one pool and one block table per request.
+
+A mixer says what it needs with a request record: ``PagedKV`` (keys and values in pages,
+all of them or a window) or ``StateSlot`` (state of fixed size per request) or nothing.
+Caches whose ``PagedKV`` records are equal form a group: they have pages of their own, a
+block table per request that all caches of the group index with, and their own rule for
+giving pages back (a window group frees the pages that every later query has passed).
+
+The reference has one kind only, a whole-context tensor per layer and request
+(src/models/jiuge/jiuge_kv_cache.cpp:3-23); pages, tables and groups have no counterpart.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+from .pages import OutOfPages, PagePool
+
+NO_PAGE = 0     # block-table entry of a block that holds nothing (the null page)
+
+
+@dataclass(frozen=True)
+class PagedKV:
+    """Keys and values of ``num_kv_heads`` heads of ``head_dim`` for every cached position."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None      # None: all keys are kept
+
+
+@dataclass(frozen=True)
+class StateSlot:
+    """Per-request state of fixed shape, e.g. a recurrent mixer's."""
+    shape: Tuple[int, ...]
+    dtype: str = "float32"
+
+
+class CacheGroup:
+    """Host bookkeeping of one group: pool, block tables, trimming."""
+
+    def __init__(self, need: PagedKV, cache_ids: List[int], num_pages: int, page_size: int, name: str = ""):
+        self.need = need
+        self.cache_ids = list(cache_ids)
+        self.page_size = page_size
+        self.name = name or f"kv{need.num_kv_heads}x{need.head_dim}" + (f"w{need.window}" if need.window else "")
+        self.pool = PagePool(num_pages, reserved=1, name=self.name)
+        self.tables: Dict[object, List[int]] = {}      # request -> page of each block (NO_PAGE if none)
+        self.first_block: Dict[object, int] = {}       # request -> first block still held
+
+    # -- how many new pages a request needs to hold positions [first_needed, new_len) -------
+    def _first_needed_block(self, start: int) -> int:
+        """First block that queries at positions >= start can still see."""
+        if self.need.window is None:
+            return 0
+        return max(0, start - self.need.window + 1) // self.page_size
+
+    def pages_needed(self, req, start: int, new_len: int) -> int:
+        table = self.tables.get(req, [])
+        last = (new_len + self.page_size - 1) // self.page_size
+        first = max(self._first_needed_block(start), self.first_block.get(req, 0))
+        return sum(1 for b in range(first, last) if b >= len(table) or table[b] == NO_PAGE)
+
+    def reserve(self, req, start: int, new_len: int) -> List[int]:
+        """Make sure pages exist for positions that a step over [start, new_len) touches."""
+        table = self.tables.setdefault(req, [])
+        self.first_block.setdefault(req, 0)
+        last = (new_len + self.page_size - 1) // self.page_size
+        first = max(self._first_needed_block(start), self.first_block[req])
+        want = [b for b in range(first, last) if b >= len(table) or table[b] == NO_PAGE]
+        pages = self.pool.alloc(len(want))           # raises OutOfPages before anything changes
+        while len(table) < last:
+            table.append(NO_PAGE)
+        for b, p in zip(want, pages):
+            table[b] = p
+        return pages
+
+    def give_back(self, req, pages: List[int]) -> None:
+        """Undo a ``reserve`` (used when another group of the same step ran out)."""
+        table = self.tables[req]
+        back = set(pages)
+        for b, p in enumerate(table):
+            if p in back:
+                table[b] = NO_PAGE
+        self.pool.free(pages)
+
+    def trim(self, req, new_len: int) -> int:
+        """Free the pages that no query at a position >= new_len can see.  Returns the count."""
+        if self.need.window is None or req not in self.tables:
+            return 0
+        table = self.tables[req]
+        keep_from = self._first_needed_block(new_len)
+        freed = []
+        for b in range(self.first_block[req], min(keep_from, len(table))):
+            if table[b] != NO_PAGE:
+                freed.append(table[b])
+                table[b] = NO_PAGE
+        self.first_block[req] = max(self.first_block[req], min(keep_from, len(table)))
+        self.pool.free(freed)
+        return len(freed)
+
+    def release(self, req) -> int:
+        table = self.tables.pop(req, None)
+        self.first_block.pop(req, None)
+        if table is None:
+            return 0
+        pages = [p for p in table if p != NO_PAGE]
+        self.pool.free(pages)
+        return len(pages)
+
+    def table(self, req) -> List[int]:
+        return self.tables.get(req, [])

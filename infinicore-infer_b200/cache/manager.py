@@ -1,0 +1,173 @@
+"""The cache manager: pages for every group, a slot per request, and the device storage.
+
+Lifecycle of a request: ``admit`` (a slot), then before each step ``reserve`` (pages in
+every group for the positions the step touches; all or nothing), after the step ``commit``
+(the new length; window groups give passed pages back), at the end ``release`` (everything
+back).  Host-side logic needs no GPU: with ``device=None`` no storage is allocated and only
+the bookkeeping runs.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .groups import NO_PAGE, CacheGroup, PagedKV, StateSlot
+from .pages import OutOfPages
+from .slots import OutOfSlots, SlotAllocator
+
+
+class KVView:
+    """What a mixer sees of its cache: its pages and the group whose block table indexes them."""
+
+    def __init__(self, group_index: int, k_pages, v_pages, page_size: int):
+        self.group_index = group_index
+        self.k_pages, self.v_pages, self.page_size = k_pages, v_pages, page_size
+
+
+class StateView:
+    """A state-keeping mixer's tensor ``[num_slots, *shape]``; index it with the step's slot ids."""
+
+    def __init__(self, state):
+        self.state = state
+
+
+class CacheManager:
+    def __init__(self, needs: Sequence[object], num_pages: int, page_size: int, max_requests: int,
+                 max_positions: int, dtype: torch.dtype = torch.bfloat16, device=None,
+                 pages_per_group: Optional[Dict[int, int]] = None):
+        """``needs[c]`` is what cache ``c`` asks for: a ``PagedKV``, a ``StateSlot`` or None.
+
+        ``num_pages`` is the number of usable pages of every group (one more, the null page,
+        is added); ``pages_per_group`` overrides it by group index.
+        """
+        if page_size < 1:
+            raise ValueError("page size must be positive")
+        self.page_size = page_size
+        self.max_positions = max_positions
+        self.max_blocks = (max_positions + page_size - 1) // page_size
+        self.dtype, self.device = dtype, device
+        self.slots = SlotAllocator(max_requests)
+        self.groups: List[CacheGroup] = []
+        self.views: List[object] = [None] * len(needs)
+        self.lengths: Dict[object, int] = {}
+        self._state_tensors: List[torch.Tensor] = []
+
+        by_need: Dict[PagedKV, List[int]] = {}
+        for c, need in enumerate(needs):
+            if isinstance(need, PagedKV):
+                by_need.setdefault(need, []).append(c)
+        for gi, (need, ids) in enumerate(by_need.items()):
+            n = (pages_per_group or {}).get(gi, num_pages)
+            group = CacheGroup(need, ids, n + 1, page_size)
+            self.groups.append(group)
+            if device is not None:
+                shape = (len(ids), n + 1, need.num_kv_heads, page_size, need.head_dim)
+                k = torch.zeros(shape, dtype=dtype, device=device)
+                v = torch.zeros(shape, dtype=dtype, device=device)
+                for i, c in enumerate(ids):
+                    self.views[c] = KVView(gi, k[i], v[i], page_size)
+            else:
+                for c in ids:
+                    self.views[c] = KVView(gi, None, None, page_size)
+        for c, need in enumerate(needs):
+            if isinstance(need, StateSlot):
+                st = None
+                if device is not None:
+                    st = torch.zeros((self.slots.num_slots,) + tuple(need.shape),
+                                     dtype=getattr(torch, need.dtype), device=device)
+                    self._state_tensors.append(st)
+                self.views[c] = StateView(st)
+
+    # ---- requests ------------------------------------------------------------------------
+    def admit(self, req) -> int:
+        slot = self.slots.acquire(req)         # raises OutOfSlots
+        self.lengths[req] = 0
+        for st in self._state_tensors:
+            st[slot].zero_()
+        return slot
+
+    def is_live(self, req) -> bool:
+        return req in self.lengths
+
+    def length(self, req) -> int:
+        return self.lengths[req]
+
+    def pages_needed(self, req, new_len: int) -> List[int]:
+        start = self.lengths.get(req, 0)
+        return [g.pages_needed(req, start, new_len) for g in self.groups]
+
+    def can_reserve(self, wants: Dict[object, int]) -> bool:
+        """Would ``reserve`` succeed for all of ``{request: new_len}`` together?"""
+        need = [0] * len(self.groups)
+        for req, new_len in wants.items():
+            for gi, n in enumerate(self.pages_needed(req, new_len)):
+                need[gi] += n
+        return all(n <= g.pool.available for n, g in zip(need, self.groups))
+
+    def reserve(self, req, new_len: int) -> None:
+        """Pages in every group for a step that takes ``req`` from its length to ``new_len``."""
+        if req not in self.lengths:
+            raise KeyError(f"request {req!r} was not admitted")
+        if new_len > self.max_positions:
+            raise ValueError(f"request {req!r}: {new_len} positions exceed the maximum of {self.max_positions}")
+        start = self.lengths[req]
+        done = []
+        try:
+            for g in self.groups:
+                done.append((g, g.reserve(req, start, new_len)))
+        except OutOfPages:
+            for g, pages in done:
+                g.give_back(req, pages)
+            raise
+
+    def commit(self, req, new_len: int) -> None:
+        self.lengths[req] = new_len
+        for g in self.groups:
+            g.trim(req, new_len)
+
+    def release(self, req) -> None:
+        if req not in self.lengths:
+            raise KeyError(f"request {req!r} is not live")
+        for g in self.groups:
+            g.release(req)
+        self.slots.release(req)
+        del self.lengths[req]
+
+    # ---- what a step uploads ----------------------------------------------------------------
+    def block_table_rows(self, group_index: int, reqs: Sequence[object], out: np.ndarray) -> None:
+        """Fill ``out[i, :]`` (int32, ``[len(reqs), max_blocks]``) with request i's pages."""
+        g = self.groups[group_index]
+        out[:len(reqs)].fill(NO_PAGE)
+        for i, r in enumerate(reqs):
+            t = g.table(r)
+            out[i, :len(t)] = t
+
+    def slot_ids(self, reqs: Sequence[object]) -> List[int]:
+        return [self.slots.slot_of(r) for r in reqs]
+
+    # ---- accounting ------------------------------------------------------------------------
+    def stats(self) -> dict:
+        return {
+            "live_requests": len(self.lengths),
+            "groups": [{"name": g.name, "pages_in_use": g.pool.in_use, "pages_free": g.pool.available,
+                        "high_water": g.pool.high_water} for g in self.groups],
+        }
+
+    def check_invariants(self) -> None:
+        """No page lost, none held twice: every page is free or in exactly one table."""
+        for g in self.groups:
+            seen = {}
+            for req, table in g.tables.items():
+                for p in table:
+                    if p == NO_PAGE:
+                        continue
+                    if p in seen:
+                        raise AssertionError(f"{g.name}: page {p} held by {seen[p]!r} and {req!r}")
+                    seen[p] = req
+            held = set(g.pool.held_pages())
+            if held != set(seen):
+                raise AssertionError(f"{g.name}: pool says {sorted(held)} are out, tables hold {sorted(seen)}")
+            if g.pool.in_use + g.pool.available != g.pool.capacity:
+                raise AssertionError(f"{g.name}: a page is lost")

@@ -1,0 +1,102 @@
+// Shared helpers of the sm_100a kernels: element types, status reporting, reductions.
+//
+// Every exported function has C linkage, takes raw device pointers plus the stream to
+// launch on, and returns 0 on success.  On failure it returns a non-zero code and leaves
+// a message that `jk_last_error` hands out; nothing calls exit().  (The reference's
+// RUN_INFINI macro prints and exits the process: src/utils.hpp:10-34.)
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define JK_EXPORT extern "C" __attribute__((visibility("default")))
+
+enum JkDtype : int { JK_F32 = 0, JK_BF16 = 1 };
+
+enum JkStatus : int {
+    JK_OK = 0,
+    JK_BAD_ARGUMENT = 1,
+    JK_UNSUPPORTED = 2,
+    JK_CUDA_ERROR = 3,
+};
+
+char *jk_error_buffer();   // one per shared object, defined by JK_DEFINE_ERROR_BUFFER
+
+#define JK_DEFINE_ERROR_BUFFER(prefix)                                              \
+    static thread_local char g_error[512] = "";                                    \
+    char *jk_error_buffer() { return g_error; }                                    \
+    JK_EXPORT const char *prefix##_last_error() { return g_error; }
+
+#define JK_FAIL(code, ...)                                                          \
+    do {                                                                            \
+        snprintf(jk_error_buffer(), 512, __VA_ARGS__);                              \
+        return (code);                                                              \
+    } while (0)
+
+#define JK_REQUIRE(cond, ...)                                                       \
+    do {                                                                            \
+        if (!(cond)) JK_FAIL(JK_BAD_ARGUMENT, __VA_ARGS__);                         \
+    } while (0)
+
+#define JK_CHECK_LAUNCH(name)                                                       \
+    do {                                                                            \
+        cudaError_t e_ = cudaGetLastError();                                        \
+        if (e_ != cudaSuccess)                                                      \
+            JK_FAIL(JK_CUDA_ERROR, "%s: %s", name, cudaGetErrorString(e_));         \
+    } while (0)
+
+// ---- element access: storage type T (float or __nv_bfloat16), arithmetic in float ----
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+// ---- reductions ------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` holds
+// 33 floats of shared memory.  The order of the additions depends on the block size only.
+__device__ __forceinline__ float block_sum(float v, float *scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarp ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float *scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarp ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}

@@ -1,0 +1,330 @@
+// Row-wise kernels of the step: embedding gather, residual add + RMSNorm, rotary position
+// encoding fused with the write of keys and values into cache pages, SwiGLU, and a
+// float32 matrix product on the CUDA cores (the true 32-bit path).
+//
+// The residual stream is float32 in both precisions; products, norms and rotations are
+// computed in float32 and rounded once when they are stored as bfloat16.
+#include "common.cuh"
+
+JK_DEFINE_ERROR_BUFFER(jk_elementwise)
+
+// ---------------------------------------------------------------------------------------
+// Embedding: x[i, :] = scale * E[tokens[i], :]      (reference: jiuge.cpp:164-168 does one
+// device-to-device copy per token of a table that was scaled on the host, jiuge.py:194-197)
+// ---------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_kernel(const int *__restrict__ tokens, const TW *__restrict__ table,
+                             float *__restrict__ out, int d, float scale) {
+    const int row = blockIdx.x;
+    const TW *src = table + (size_t)tokens[row] * d;
+    float *dst = out + (size_t)row * d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) dst[c] = scale * to_f32(src[c]);
+}
+
+JK_EXPORT int jk_embed(const int *tokens, int ntok, const void *table, int table_dtype, int d,
+                       float scale, float *out, cudaStream_t stream) {
+    if (ntok == 0) return JK_OK;
+    JK_REQUIRE(ntok > 0 && d > 0, "embed: ntok %d, d %d", ntok, d);
+    const int threads = d >= 1024 ? 256 : 128;
+    if (table_dtype == JK_F32)
+        embed_kernel<float><<<ntok, threads, 0, stream>>>(tokens, (const float *)table, out, d, scale);
+    else if (table_dtype == JK_BF16)
+        embed_kernel<__nv_bfloat16><<<ntok, threads, 0, stream>>>(tokens, (const __nv_bfloat16 *)table, out, d, scale);
+    else
+        JK_FAIL(JK_UNSUPPORTED, "embed: table dtype %d", table_dtype);
+    JK_CHECK_LAUNCH("embed");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Residual add + RMSNorm.  For output row i (source row r = rows ? rows[i] : i):
+//     v = x[r] + delta_scale * delta[r]          (delta may be null)
+//     x[r] = v                                   (only when rows is null)
+//     out[i] = out_scale * v * w / sqrt(mean(v^2) + eps)
+// One block per row; the row is held in shared memory between the two passes.
+// (reference: rmsnorm at jiuge.cpp:198, :246, :262; the residual add is the beta=1 of the
+// preceding product, inference_context.cpp:207-210.)
+// ---------------------------------------------------------------------------------------
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ delta,
+                                   float delta_scale, const float *__restrict__ w, float eps,
+                                   float out_scale, TO *__restrict__ out,
+                                   const int *__restrict__ rows, int d) {
+    extern __shared__ float row_buf[];
+    __shared__ float scratch[33];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    float *xr = x + (size_t)r * d;
+    const TD *dr = delta ? delta + (size_t)r * d : nullptr;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float v = xr[c];
+        if (dr) v += delta_scale * to_f32(dr[c]);
+        row_buf[c] = v;
+        if (dr && !rows) xr[c] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)d + eps);
+    TO *o = out + (size_t)i * d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x)
+        o[c] = from_f32<TO>(out_scale * (row_buf[c] * inv) * w[c]);
+}
+
+template <typename TD, typename TO>
+static int launch_add_rmsnorm(float *x, const void *delta, float delta_scale, const float *w,
+                              float eps, float out_scale, void *out, const int *rows, int nout,
+                              int d, cudaStream_t stream) {
+    const size_t smem = (size_t)d * sizeof(float);
+    JK_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: width %d needs %zu bytes of shared memory", d, smem);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "add_rmsnorm: %s", cudaGetErrorString(e));
+    }
+    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+    add_rmsnorm_kernel<TD, TO><<<nout, threads, smem, stream>>>(
+        x, (const TD *)delta, delta_scale, w, eps, out_scale, (TO *)out, rows, d);
+    JK_CHECK_LAUNCH("add_rmsnorm");
+    return JK_OK;
+}
+
+JK_EXPORT int jk_add_rmsnorm(float *x, const void *delta, int delta_dtype, float delta_scale,
+                             const float *w, float eps, float out_scale, void *out, int out_dtype,
+                             const int *rows, int nout, int d, cudaStream_t stream) {
+    if (nout == 0) return JK_OK;
+    JK_REQUIRE(nout > 0 && d > 0, "add_rmsnorm: nout %d, d %d", nout, d);
+    if (delta_dtype == JK_F32 && out_dtype == JK_F32)
+        return launch_add_rmsnorm<float, float>(x, delta, delta_scale, w, eps, out_scale, out, rows, nout, d, stream);
+    if (delta_dtype == JK_F32 && out_dtype == JK_BF16)
+        return launch_add_rmsnorm<float, __nv_bfloat16>(x, delta, delta_scale, w, eps, out_scale, out, rows, nout, d, stream);
+    if (delta_dtype == JK_BF16 && out_dtype == JK_BF16)
+        return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(x, delta, delta_scale, w, eps, out_scale, out, rows, nout, d, stream);
+    if (delta_dtype == JK_BF16 && out_dtype == JK_F32)
+        return launch_add_rmsnorm<__nv_bfloat16, float>(x, delta, delta_scale, w, eps, out_scale, out, rows, nout, d, stream);
+    JK_FAIL(JK_UNSUPPORTED, "add_rmsnorm: dtypes %d, %d", delta_dtype, out_dtype);
+}
+
+// x += delta_scale * delta, without a norm (used when a residual must be made whole).
+template <typename TD>
+__global__ void residual_add_kernel(float *__restrict__ x, const TD *__restrict__ delta,
+                                    float delta_scale, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) x[i] += delta_scale * to_f32(delta[i]);
+}
+
+JK_EXPORT int jk_residual_add(float *x, const void *delta, int delta_dtype, float delta_scale,
+                              long long n, cudaStream_t stream) {
+    if (n == 0) return JK_OK;
+    const int threads = 256;
+    long long blocks = (n + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (delta_dtype == JK_F32)
+        residual_add_kernel<float><<<(int)blocks, threads, 0, stream>>>(x, (const float *)delta, delta_scale, (size_t)n);
+    else if (delta_dtype == JK_BF16)
+        residual_add_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(x, (const __nv_bfloat16 *)delta, delta_scale, (size_t)n);
+    else
+        JK_FAIL(JK_UNSUPPORTED, "residual_add: dtype %d", delta_dtype);
+    JK_CHECK_LAUNCH("residual_add");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// SwiGLU: out[t, c] = silu(gu[t, c]) * gu[t, di + c],  silu(z) = z / (1 + exp(-z))
+// (reference: jiuge.cpp:191-192, :248: gate is the first half of the fused product, up the second)
+// ---------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void swiglu_kernel(const TI *__restrict__ gu, TO *__restrict__ out, int di, size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const size_t t = i / di;
+        const int c = (int)(i - t * di);
+        const float g = to_f32(gu[t * 2 * di + c]);
+        const float u = to_f32(gu[t * 2 * di + di + c]);
+        out[i] = from_f32<TO>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+JK_EXPORT int jk_swiglu(const void *gu, int in_dtype, void *out, int out_dtype, int ntok, int di,
+                        cudaStream_t stream) {
+    if (ntok == 0) return JK_OK;
+    JK_REQUIRE(ntok > 0 && di > 0, "swiglu: ntok %d, di %d", ntok, di);
+    const size_t total = (size_t)ntok * di;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (in_dtype == JK_F32 && out_dtype == JK_F32)
+        swiglu_kernel<float, float><<<(int)blocks, threads, 0, stream>>>((const float *)gu, (float *)out, di, total);
+    else if (in_dtype == JK_F32 && out_dtype == JK_BF16)
+        swiglu_kernel<float, __nv_bfloat16><<<(int)blocks, threads, 0, stream>>>((const float *)gu, (__nv_bfloat16 *)out, di, total);
+    else if (in_dtype == JK_BF16 && out_dtype == JK_BF16)
+        swiglu_kernel<__nv_bfloat16, __nv_bfloat16><<<(int)blocks, threads, 0, stream>>>((const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, di, total);
+    else
+        JK_FAIL(JK_UNSUPPORTED, "swiglu: dtypes %d -> %d", in_dtype, out_dtype);
+    JK_CHECK_LAUNCH("swiglu");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Rotary position encoding + cache write.  For token row t at position p of request r:
+//   q_out[t, h, :]            = rot(qkv[t, h, :] + bias, p)                  h < nh
+//   K[page, hk, off, :]       = rot(qkv[t, nh + hk, :] + bias, p)            hk < nkvh
+//   V[page, hk, off, :]       = qkv[t, nh + nkvh + hk, :] + bias
+// with page = block_table[r, p / page_size], off = p % page_size.  rot pairs element j with
+// j + dh/2 (or 2j with 2j+1 when interleaved) at angle p / theta^(j / (dh/2)); cos and sin
+// come from float32 tables [max_positions, dh/2].  A null table means no rotation.
+// (reference: rope at jiuge.cpp:202-203, cache rows at jiuge.cpp:217-218, tables at
+// jiuge_weight.hpp:134-186)
+// ---------------------------------------------------------------------------------------
+struct RopeKvArgs {
+    const void *qkv;
+    const float *bias;
+    const int *positions;
+    const int *row_req;
+    const int *block_table;
+    const float *cos_table;
+    const float *sin_table;
+    void *q_out;
+    void *k_pages;
+    void *v_pages;
+    int ld_qkv, nh, nkvh, dh, page_size, max_blocks, interleaved, write_cache;
+};
+
+template <typename TI, typename TO>
+__global__ void rope_kv_kernel(RopeKvArgs a) {
+    const int t = blockIdx.x;
+    const int pos = a.positions[t];
+    const int half = a.dh / 2;
+    const TI *src = (const TI *)a.qkv + (size_t)t * a.ld_qkv;
+    const float *cs = a.cos_table ? a.cos_table + (size_t)pos * half : nullptr;
+    const float *sn = a.sin_table ? a.sin_table + (size_t)pos * half : nullptr;
+    size_t slot = 0;   // element offset of (page, head 0, off, 0) in the pages
+    if (a.write_cache) {
+        const int page = a.block_table[(size_t)a.row_req[t] * a.max_blocks + pos / a.page_size];
+        slot = ((size_t)page * a.nkvh * a.page_size + (pos % a.page_size)) * a.dh;
+    }
+    const size_t head_stride = (size_t)a.page_size * a.dh;
+    // rotated heads: queries, then keys
+    const int nrot = a.write_cache ? (a.nh + a.nkvh) : a.nh;
+    for (int i = threadIdx.x; i < nrot * half; i += blockDim.x) {
+        const int h = i / half, j = i - h * half;
+        const int e0 = a.interleaved ? 2 * j : j;
+        const int e1 = a.interleaved ? 2 * j + 1 : j + half;
+        float x0 = to_f32(src[h * a.dh + e0]), x1 = to_f32(src[h * a.dh + e1]);
+        if (a.bias) { x0 += a.bias[h * a.dh + e0]; x1 += a.bias[h * a.dh + e1]; }
+        float y0 = x0, y1 = x1;
+        if (cs) {
+            const float c = cs[j], s = sn[j];
+            y0 = x0 * c - x1 * s;
+            y1 = x0 * s + x1 * c;
+        }
+        if (h < a.nh) {
+            TO *q = (TO *)a.q_out + ((size_t)t * a.nh + h) * a.dh;
+            q[e0] = from_f32<TO>(y0);
+            q[e1] = from_f32<TO>(y1);
+        } else {
+            TO *k = (TO *)a.k_pages + slot + (size_t)(h - a.nh) * head_stride;
+            k[e0] = from_f32<TO>(y0);
+            k[e1] = from_f32<TO>(y1);
+        }
+    }
+    if (a.write_cache) {
+        const int vbase = (a.nh + a.nkvh) * a.dh;
+        for (int i = threadIdx.x; i < a.nkvh * a.dh; i += blockDim.x) {
+            const int h = i / a.dh, e = i - h * a.dh;
+            float v = to_f32(src[vbase + i]);
+            if (a.bias) v += a.bias[vbase + i];
+            ((TO *)a.v_pages)[slot + (size_t)h * head_stride + e] = from_f32<TO>(v);
+        }
+    }
+}
+
+JK_EXPORT int jk_rope_kv(const void *qkv, int in_dtype, int ld_qkv, const float *bias,
+                         const int *positions, const int *row_req, const int *block_table,
+                         int max_blocks, int page_size, const float *cos_table,
+                         const float *sin_table, int interleaved, void *q_out, void *k_pages,
+                         void *v_pages, int out_dtype, int ntok, int nh, int nkvh, int dh,
+                         int write_cache, cudaStream_t stream) {
+    if (ntok == 0) return JK_OK;
+    JK_REQUIRE(ntok > 0 && nh > 0 && nkvh >= 0 && dh > 0 && dh % 2 == 0,
+               "rope_kv: ntok %d, heads %d/%d, head size %d", ntok, nh, nkvh, dh);
+    JK_REQUIRE(!write_cache || (page_size > 0 && max_blocks > 0 && block_table && k_pages && v_pages),
+               "rope_kv: cache write asked for without pages");
+    JK_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "rope_kv: one of cos/sin is null");
+    RopeKvArgs a{qkv, bias, positions, row_req, block_table, cos_table, sin_table, q_out, k_pages,
+                 v_pages, ld_qkv, nh, nkvh, dh, page_size, max_blocks, interleaved, write_cache};
+    const int work = (nh + nkvh) * dh / 2;
+    const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
+    if (in_dtype == JK_F32 && out_dtype == JK_F32)
+        rope_kv_kernel<float, float><<<ntok, threads, 0, stream>>>(a);
+    else if (in_dtype == JK_F32 && out_dtype == JK_BF16)
+        rope_kv_kernel<float, __nv_bfloat16><<<ntok, threads, 0, stream>>>(a);
+    else if (in_dtype == JK_BF16 && out_dtype == JK_BF16)
+        rope_kv_kernel<__nv_bfloat16, __nv_bfloat16><<<ntok, threads, 0, stream>>>(a);
+    else
+        JK_FAIL(JK_UNSUPPORTED, "rope_kv: dtypes %d -> %d", in_dtype, out_dtype);
+    JK_CHECK_LAUNCH("rope_kv");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// float32 matrix product on the CUDA cores:  C[M, N] = A[M, K] * W[N, K]^T (+ bias[N]).
+// Plain fused multiply-adds in float32: no tensor cores, hence no TF32 rounding of the
+// operands.  Each output element sums over k in ascending order whatever M and N are, so a
+// row's result does not depend on what else is in the batch.
+// (reference: the products at jiuge.cpp:200, :236, :247, :249, :264 go to a library.)
+// ---------------------------------------------------------------------------------------
+constexpr int GF_BM = 64, GF_BN = 64, GF_BK = 16;
+
+__global__ void __launch_bounds__(256)
+gemm_f32_kernel(const float *__restrict__ A, const float *__restrict__ W,
+                const float *__restrict__ bias, float *__restrict__ C, int M, int N, int K,
+                int lda, int ldw, int ldc) {
+    __shared__ float As[GF_BK][GF_BM + 1];
+    __shared__ float Ws[GF_BK][GF_BN + 1];
+    const int m0 = blockIdx.y * GF_BM, n0 = blockIdx.x * GF_BN;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += GF_BK) {
+        for (int i = threadIdx.x; i < GF_BM * GF_BK; i += 256) {
+            const int r = i / GF_BK, c = i % GF_BK;
+            As[c][r] = (m0 + r < M && k0 + c < K) ? A[(size_t)(m0 + r) * lda + k0 + c] : 0.f;
+            Ws[c][r] = (n0 + r < N && k0 + c < K) ? W[(size_t)(n0 + r) * ldw + k0 + c] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < GF_BK; ++k) {
+            float a[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { a[i] = As[k][ty * 4 + i]; w[i] = Ws[k][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) C[(size_t)m * ldc + n] = acc[i][j] + (bias ? bias[n] : 0.f);
+        }
+    }
+}
+
+JK_EXPORT int jk_gemm_f32(const float *A, int lda, const float *W, int ldw, const float *bias,
+                          float *C, int ldc, int M, int N, int K, cudaStream_t stream) {
+    if (M == 0 || N == 0) return JK_OK;
+    JK_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_f32: M %d N %d K %d", M, N, K);
+    dim3 grid((N + GF_BN - 1) / GF_BN, (M + GF_BM - 1) / GF_BM);
+    JK_REQUIRE(grid.y <= 65535, "gemm_f32: M %d is too large for one launch", M);
+    gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K, lda, ldw, ldc);
+    JK_CHECK_LAUNCH("gemm_f32");
+    return JK_OK;
+}

@@ -1,0 +1,272 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted rows out.
+
+One call runs exactly the tokens it is given, as one batch, against the cache that earlier
+calls left: portions of prompts beside single decoded tokens, cut anywhere.  The reference's
+counterpart is ``inferBatch`` / ``forwardBatch`` with ``tokens, req_lens, req_pos``
+(include/infinicore_infer/models/jiuge.h:89-110, src/models/jiuge/jiuge.cpp:114-298); here a
+request's position is what the cache holds of it, logits come back for the rows asked for,
+and errors are exceptions raised before anything ran.
+
+A step whose entries all carry one token is a decode step: it runs as a CUDA graph captured
+once per batch-size bucket, with the batch padded by rows that read and write the null page.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, OutOfPages
+from ..config import read_config
+from ..parts import Model, Runtime, StepContext, cache_needs, model_manifest
+from ..weights import FileWeights, check_manifest
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places (indices into ``tokens``)
+    whose logits are wanted."""
+    req_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=tuple)
+
+
+class StepError(ValueError):
+    """A step that cannot run as given (bad token, context overflow, unknown place)."""
+
+
+def _align(n: int, a: int = 4) -> int:
+    return (n + a - 1) // a * a
+
+
+class _Layout:
+    """Offsets (in int32 elements) of a step's arrays inside the metadata buffer."""
+
+    def __init__(self, T: int, B: int, n_groups: int, max_blocks: int):
+        self.T, self.B = T, B
+        o = 0
+        self.tokens = o; o += _align(T)
+        self.positions = o; o += _align(T)
+        self.row_req = o; o += _align(T)
+        self.want_rows = o; o += _align(T)
+        self.req_start = o; o += _align(B + 1)
+        self.req_pos = o; o += _align(B)
+        self.slot_ids = o; o += _align(B)
+        self.tables = []
+        for _ in range(n_groups):
+            self.tables.append(o); o += _align(B * max_blocks)
+        self.total = o
+
+
+class Engine:
+    """A model, its cache and the step function over them."""
+
+    def __init__(self, spec, weights, dtype: torch.dtype = torch.bfloat16, device="cuda:0",
+                 cache_tokens: int = 4096, page_size: int = 16, max_requests: int = 64,
+                 max_step_tokens: int = 8192, use_graphs: bool = True):
+        if not torch.cuda.is_available():
+            raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
+        self.spec = spec
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.runtime = Runtime(dtype, self.device)
+        shapes = weights.shapes()
+        check_manifest(model_manifest(spec), shapes, where=getattr(weights, "model_dir", ""))
+        self.model = Model(spec, weights, self.runtime)
+        num_pages = (cache_tokens + page_size - 1) // page_size
+        self.cache = CacheManager(cache_needs(spec), num_pages, page_size, max_requests,
+                                  spec.max_positions, dtype=dtype, device=self.device)
+        self.max_requests = max_requests
+        self.max_step_tokens = max_step_tokens
+        self.use_graphs = use_graphs
+        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
+        cap = _Layout(max_step_tokens, max_requests, n_groups, mb).total
+        self._meta_dev = torch.zeros(cap, dtype=torch.int32, device=self.device)
+        self._meta_host = [torch.zeros(cap, dtype=torch.int32, pin_memory=True) for _ in range(3)]
+        self._meta_events: List[Optional[torch.cuda.Event]] = [None] * 3
+        self._meta_turn = 0
+        self._graphs: Dict[int, object] = {}
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # ---- construction -------------------------------------------------------------------------
+    @classmethod
+    def from_folder(cls, model_dir: str, dtype: torch.dtype = torch.bfloat16, device="cuda:0",
+                    max_tokens: Optional[int] = None, **kw) -> "Engine":
+        """Load ``config.json`` and the safetensors of a folder; the architecture's registry
+        entry decides the configuration class."""
+        config = read_config(model_dir, max_tokens=max_tokens)
+        weights = FileWeights(model_dir, dtype, device)
+        eng = cls(config.model_spec(), weights, dtype=dtype, device=device, **kw)
+        eng.config = config
+        return eng
+
+    # ---- requests -----------------------------------------------------------------------------
+    def begin(self, req_id) -> None:
+        self.cache.admit(req_id)
+
+    def end(self, req_id) -> None:
+        self.cache.release(req_id)
+
+    def position(self, req_id) -> int:
+        return self.cache.length(req_id) if self.cache.is_live(req_id) else 0
+
+    # ---- the step -------------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the entries as one batch; return float32 logits ``[wanted, vocab]`` on the device,
+        in the order of the entries and of their ``want``."""
+        entries = [e for e in entries if len(e.tokens)]
+        if not entries:
+            return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=self.device)
+        self._validate(entries)
+        for e in entries:
+            if not self.cache.is_live(e.req_id):
+                self.cache.admit(e.req_id)
+        starts = [self.cache.length(e.req_id) for e in entries]
+        new_len = {e.req_id: s + len(e.tokens) for e, s in zip(entries, starts)}
+        if not self.cache.can_reserve(new_len):
+            raise OutOfPages(sum(sum(self.cache.pages_needed(r, n)) for r, n in new_len.items()),
+                             min(g.pool.available for g in self.cache.groups), "step")
+        for r, n in new_len.items():
+            self.cache.reserve(r, n)
+
+        decode = self.use_graphs and all(len(e.tokens) == 1 for e in entries)
+        if decode:
+            logits = self._run_decode_graph(entries, starts)
+        else:
+            ctx = self._upload(entries, starts, len(entries), sum(len(e.tokens) for e in entries))
+            logits = self.model.forward(ctx, self.cache.views)
+        for r, n in new_len.items():
+            self.cache.commit(r, n)
+        self.steps_run += 1
+        self.tokens_run += sum(len(e.tokens) for e in entries)
+        return logits
+
+    # ---- checks that run before anything touches the device ------------------------------------
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        seen = set()
+        total = 0
+        for e in entries:
+            if e.req_id in seen:
+                raise StepError(f"request {e.req_id!r} appears twice in one step")
+            seen.add(e.req_id)
+            n = len(e.tokens)
+            total += n
+            lo, hi = min(e.tokens), max(e.tokens)
+            if lo < 0 or hi >= self.spec.vocab_size:
+                raise StepError(f"request {e.req_id!r}: token id {lo if lo < 0 else hi} is outside "
+                                f"the vocabulary of {self.spec.vocab_size}")
+            if self.position(e.req_id) + n > self.spec.max_positions:
+                raise StepError(f"request {e.req_id!r}: position {self.position(e.req_id) + n} exceeds "
+                                f"the model's {self.spec.max_positions}")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise StepError(f"request {e.req_id!r}: wanted place {w} is not among its {n} tokens")
+        if total > self.max_step_tokens:
+            raise StepError(f"{total} tokens in one step exceed the engine's {self.max_step_tokens}")
+        new = sum(1 for e in entries if not self.cache.is_live(e.req_id))
+        if new > self.cache.slots.available:
+            raise StepError(f"{new} new requests but {self.cache.slots.available} request slots free")
+
+    # ---- host -> device metadata ------------------------------------------------------------------
+    def _upload(self, entries, starts, B: int, T: int, pad_to: Optional[int] = None) -> StepContext:
+        """Fill the pinned buffer, copy it in one piece, return views of the device copy.
+
+        ``pad_to``: batch size of a captured decode step; missing entries become rows that use
+        slot 0 and the null page at position 0.
+        """
+        nB = pad_to or B
+        nT = pad_to or T
+        lay = _Layout(nT, nB, len(self.cache.groups), self.cache.max_blocks)
+        turn = self._meta_turn
+        self._meta_turn = (turn + 1) % len(self._meta_host)
+        if self._meta_events[turn] is not None:
+            self._meta_events[turn].synchronize()
+        host = self._meta_host[turn].numpy()
+        host[:lay.total] = 0
+        row = 0
+        want_rows: List[int] = []
+        req_start = [0]
+        for i, (e, s) in enumerate(zip(entries, starts)):
+            n = len(e.tokens)
+            host[lay.tokens + row: lay.tokens + row + n] = np.asarray(e.tokens, dtype=np.int32)
+            host[lay.positions + row: lay.positions + row + n] = np.arange(s, s + n, dtype=np.int32)
+            host[lay.row_req + row: lay.row_req + row + n] = i
+            want_rows.extend(row + w for w in e.want)
+            row += n
+            req_start.append(row)
+        for i in range(B, nB):           # padding rows of a captured step
+            host[lay.row_req + row] = i
+            row += 1
+            req_start.append(row)
+        n_want = len(want_rows)
+        if pad_to:                       # a captured step computes logits for every row
+            want_rows = list(range(nT))
+        host[lay.want_rows: lay.want_rows + len(want_rows)] = want_rows
+        host[lay.req_start: lay.req_start + nB + 1] = req_start
+        host[lay.req_pos: lay.req_pos + B] = starts
+        reqs = [e.req_id for e in entries]
+        slots = self.cache.slot_ids(reqs)
+        host[lay.slot_ids: lay.slot_ids + B] = slots
+        mb = self.cache.max_blocks
+        for gi, off in enumerate(lay.tables):
+            self.cache.block_table_rows(gi, reqs, host[off: off + nB * mb].reshape(nB, mb))
+        self._meta_dev[:lay.total].copy_(self._meta_host[turn][:lay.total], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._meta_events[turn] = ev
+        ctx = self._context(lay, len(want_rows))
+        ctx.host_req_start = req_start
+        ctx.host_req_pos = list(starts) + [0] * (nB - B)
+        ctx.host_slot_ids = list(slots) + [0] * (nB - B)
+        ctx.n_want = n_want if not pad_to else nT
+        return ctx
+
+    def _context(self, lay: _Layout, n_want: int) -> StepContext:
+        m, mb = self._meta_dev, self.cache.max_blocks
+        sl = lambda off, n: m[off: off + n]
+        return StepContext(
+            ntok=lay.T, nreq=lay.B,
+            tokens=sl(lay.tokens, lay.T), positions=sl(lay.positions, lay.T),
+            row_req=sl(lay.row_req, lay.T), req_start=sl(lay.req_start, lay.B + 1),
+            req_pos=sl(lay.req_pos, lay.B), slot_ids=sl(lay.slot_ids, lay.B),
+            block_tables=[sl(off, lay.B * mb).view(lay.B, mb) for off in lay.tables],
+            want_rows=sl(lay.want_rows, n_want), n_want=n_want)
+
+    # ---- decode steps as CUDA graphs -----------------------------------------------------------------
+    @staticmethod
+    def _bucket(n: int) -> int:
+        b = 1
+        while b < n:
+            b *= 2
+        return b
+
+    def _run_decode_graph(self, entries, starts) -> torch.Tensor:
+        B = len(entries)
+        bucket = self._bucket(B)
+        if bucket > self.max_requests:
+            bucket = B
+        ctx = self._upload(entries, starts, B, B, pad_to=bucket)
+        ctx.decode_only = True
+        rec = self._graphs.get(bucket)
+        if rec is None:
+            # run once eagerly (library handles, lazy module loads), then capture
+            self.model.forward(ctx, self.cache.views)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self.model.forward(ctx, self.cache.views)
+            rec = (graph, out)
+            self._graphs[bucket] = rec
+        graph, out = rec
+        graph.replay()
+        rows = []
+        for i, e in enumerate(entries):
+            rows.extend([i] * len(e.want))
+        if len(rows) == B and all(r == i for i, r in enumerate(rows)):
+            return out[:B]
+        if not rows:
+            return out[:0]
+        return out[torch.tensor(rows, device=self.device)]

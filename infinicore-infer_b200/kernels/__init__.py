@@ -1,0 +1,219 @@
+"""Python bindings of the CUDA kernels in ``csrc``: one thin function per exported symbol.
+
+Arguments are CUDA tensors; each binding checks types, shapes and contiguity, passes raw
+device pointers and the current stream to the C function, and raises ``KernelError`` with
+the library's message if it returns non-zero.  There is no fallback path: without the
+compiled module a call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+F32, BF16 = 0, 1
+_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _CODE[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, contiguous=True):
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (the engine has no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, is {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _check(module: str, rc: int):
+    if rc:
+        lib = _build.load(module)
+        fn = getattr(lib, f"jk_{module}_last_error")
+        fn.restype = ctypes.c_char_p
+        raise KernelError(fn().decode(errors="replace") or f"kernel module {module} returned {rc}")
+
+
+_c_int, _c_float, _c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+
+def embed(tokens: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Tensor) -> torch.Tensor:
+    """out[i, :] = scale * table[tokens[i], :], float32."""
+    _need(tokens, "tokens", torch.int32); _need(table, "table"); _need(out, "out", torch.float32)
+    n, d = tokens.numel(), table.shape[1]
+    if out.shape[-1] != d or out.numel() < n * d:
+        raise KernelError(f"embed: out {tuple(out.shape)} does not hold {n} rows of {d}")
+    lib = _build.load("elementwise")
+    _check("elementwise", lib.jk_embed(_ptr(tokens), _c_int(n), _ptr(table), _c_int(dtype_code(table.dtype)),
+                                       _c_int(d), _c_float(scale), _ptr(out), _stream()))
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], delta_scale: float, weight: torch.Tensor,
+                eps: float, out: torch.Tensor, out_scale: float = 1.0,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x += delta_scale * delta (when rows is None); out = out_scale * rmsnorm(x[rows]) * weight."""
+    _need(x, "x", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
+    d = x.shape[-1]
+    if weight.numel() != d or out.shape[-1] != d:
+        raise KernelError(f"add_rmsnorm: width {d}, weight {weight.numel()}, out {out.shape[-1]}")
+    if delta is not None:
+        _need(delta, "delta")
+        if delta.shape != x.shape:
+            raise KernelError(f"add_rmsnorm: delta {tuple(delta.shape)} vs x {tuple(x.shape)}")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        nout = rows.numel()
+    else:
+        nout = x.numel() // d
+    if out.numel() < nout * d:
+        raise KernelError("add_rmsnorm: out is too small")
+    lib = _build.load("elementwise")
+    _check("elementwise", lib.jk_add_rmsnorm(
+        _ptr(x), _ptr(delta), _c_int(dtype_code(delta.dtype) if delta is not None else F32),
+        _c_float(delta_scale), _ptr(weight), _c_float(eps), _c_float(out_scale), _ptr(out),
+        _c_int(dtype_code(out.dtype)), _ptr(rows), _c_int(nout), _c_int(d), _stream()))
+    return out
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor, delta_scale: float) -> torch.Tensor:
+    _need(x, "x", torch.float32); _need(delta, "delta")
+    if delta.numel() != x.numel():
+        raise KernelError("residual_add: sizes differ")
+    lib = _build.load("elementwise")
+    _check("elementwise", lib.jk_residual_add(_ptr(x), _ptr(delta), _c_int(dtype_code(delta.dtype)),
+                                              _c_float(delta_scale), _c_ll(x.numel()), _stream()))
+    return x
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, c] = silu(gate_up[t, c]) * gate_up[t, di + c]."""
+    _need(gate_up, "gate_up"); _need(out, "out")
+    ntok, di = out.shape
+    if gate_up.shape != (ntok, 2 * di):
+        raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} vs out {tuple(out.shape)}")
+    lib = _build.load("elementwise")
+    _check("elementwise", lib.jk_swiglu(_ptr(gate_up), _c_int(dtype_code(gate_up.dtype)), _ptr(out),
+                                        _c_int(dtype_code(out.dtype)), _c_int(ntok), _c_int(di), _stream()))
+    return out
+
+
+def rope_kv(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor, row_req: torch.Tensor,
+            block_table: Optional[torch.Tensor], page_size: int, cos: Optional[torch.Tensor],
+            sin: Optional[torch.Tensor], interleaved: bool, q_out: torch.Tensor,
+            k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], ntok: int, nh: int, nkvh: int,
+            dh: int, write_cache: bool = True) -> None:
+    """Rotate query and key heads of ``qkv`` rows; write keys and values into their pages."""
+    _need(qkv, "qkv"); _need(positions, "positions", torch.int32); _need(row_req, "row_req", torch.int32)
+    _need(q_out, "q_out")
+    width = (nh + 2 * nkvh) * dh
+    if qkv.shape[-1] != width or qkv.shape[0] < ntok:
+        raise KernelError(f"rope_kv: qkv {tuple(qkv.shape)} does not hold {ntok} rows of {width}")
+    if q_out.numel() < ntok * nh * dh:
+        raise KernelError("rope_kv: q_out is too small")
+    max_blocks = 0
+    if write_cache:
+        _need(block_table, "block_table", torch.int32); _need(k_pages, "k_pages"); _need(v_pages, "v_pages")
+        if k_pages.dtype != q_out.dtype or v_pages.dtype != q_out.dtype:
+            raise KernelError("rope_kv: pages and q_out must have one type")
+        if tuple(k_pages.shape[1:]) != (nkvh, page_size, dh) or k_pages.shape != v_pages.shape:
+            raise KernelError(f"rope_kv: pages {tuple(k_pages.shape)} are not [*, {nkvh}, {page_size}, {dh}]")
+        max_blocks = block_table.shape[1]
+    if cos is not None:
+        _need(cos, "cos", torch.float32); _need(sin, "sin", torch.float32)
+        if cos.shape[1] != dh // 2 or sin.shape != cos.shape:
+            raise KernelError("rope_kv: cos/sin tables must be [positions, head_dim/2]")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    lib = _build.load("elementwise")
+    _check("elementwise", lib.jk_rope_kv(
+        _ptr(qkv), _c_int(dtype_code(qkv.dtype)), _c_int(width), _ptr(bias), _ptr(positions), _ptr(row_req),
+        _ptr(block_table), _c_int(max_blocks), _c_int(page_size), _ptr(cos), _ptr(sin),
+        _c_int(1 if interleaved else 0), _ptr(q_out), _ptr(k_pages), _ptr(v_pages),
+        _c_int(dtype_code(q_out.dtype)), _c_int(ntok), _c_int(nh), _c_int(nkvh), _c_int(dh),
+        _c_int(1 if write_cache else 0), _stream()))
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T (+ bias) in float32 on the CUDA cores (no TF32)."""
+    _need(a, "a", torch.float32); _need(w, "w", torch.float32); _need(out, "out", torch.float32)
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or tuple(out.shape) != (m, n):
+        raise KernelError(f"gemm_f32: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    lib = _build.load("elementwise")
+    _check("elementwise", lib.jk_gemm_f32(_ptr(a), _c_int(k), _ptr(w), _c_int(k), _ptr(bias), _ptr(out),
+                                          _c_int(n), _c_int(m), _c_int(n), _c_int(k), _stream()))
+    return out
+
+
+def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                   positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor, ntok: int,
+                   nh: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Causal attention of ``ntok`` query rows over the paged cache, one warp per (row, head)."""
+    _need(q, "q"); _need(k_pages, "k_pages"); _need(v_pages, "v_pages"); _need(out, "out")
+    _need(positions, "positions", torch.int32); _need(row_req, "row_req", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype):
+        raise KernelError("attention: q, pages and out must have one type")
+    _, nkvh, page_size, dh = k_pages.shape
+    if q.numel() < ntok * nh * dh or out.numel() < ntok * nh * dh:
+        raise KernelError("attention: q or out is too small")
+    lib = _build.load("attention")
+    _check("attention", lib.jk_attention_rows(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _c_int(dtype_code(q.dtype)), _ptr(positions),
+        _ptr(row_req), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size), _c_int(ntok),
+        _c_int(nh), _c_int(nkvh), _c_int(dh), _c_float(scale), _c_int(window or 0), _stream()))
+    return out
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need(logits, "logits", torch.float32, contiguous=False); _need(out, "out", torch.int32)
+    n, v = logits.shape
+    if logits.stride(1) != 1:
+        raise KernelError("argmax: rows must be contiguous")
+    lib = _build.load("sampling")
+    _check("sampling", lib.jk_argmax(_ptr(logits), _c_ll(logits.stride(0)), _c_int(n), _c_int(v), _ptr(out), _stream()))
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, topk: torch.Tensor, topp: torch.Tensor,
+           uniform: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need(logits, "logits", torch.float32, contiguous=False); _need(out, "out", torch.int32)
+    _need(temperature, "temperature", torch.float32); _need(topk, "topk", torch.int32)
+    _need(topp, "topp", torch.float32); _need(uniform, "uniform", torch.float32)
+    n, v = logits.shape
+    if logits.stride(1) != 1:
+        raise KernelError("sample: rows must be contiguous")
+    if min(temperature.numel(), topk.numel(), topp.numel(), uniform.numel(), out.numel()) < n:
+        raise KernelError("sample: a per-row array is shorter than the number of rows")
+    lib = _build.load("sampling")
+    _check("sampling", lib.jk_sample(_ptr(logits), _c_ll(logits.stride(0)), _c_int(n), _c_int(v), _ptr(temperature),
+                                     _ptr(topk), _ptr(topp), _ptr(uniform), _ptr(out), _stream()))
+    return out
+
+
+def build_all(verbose: bool = True):
+    return _build.build_all(verbose)

@@ -1,0 +1,68 @@
+"""Causal softmax attention over the paged cache: the mixer of this architecture.
+
+Per layer, in the reference's order (src/models/jiuge/jiuge.cpp:200-236): the fused
+query/key/value product, rotary encoding of query and key heads, keys and values into the
+cache at the rows' positions, softmax(q k^T / sqrt(dh)) v over the request's cached
+positions under the causal mask, then the output product.  Query head h reads key/value
+head h // (num_heads / num_kv_heads) (jiuge.cpp:210-211).
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..cache import PagedKV
+from ..weights import MATRIX, VECTOR, TensorDecl
+from .base import part_class, register
+
+
+@register("mixer", "attention")
+class Attention:
+    @staticmethod
+    def tensor_decls(spec) -> Dict[str, TensorDecl]:
+        d, q, kv = spec.hidden_size, spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
+        decls = {
+            "q_proj.weight": TensorDecl((q, d)), "k_proj.weight": TensorDecl((kv, d)),
+            "v_proj.weight": TensorDecl((kv, d)), "o_proj.weight": TensorDecl((d, q)),
+        }
+        if spec.bias:
+            decls.update({"q_proj.bias": TensorDecl((q,), VECTOR), "k_proj.bias": TensorDecl((kv,), VECTOR),
+                          "v_proj.bias": TensorDecl((kv,), VECTOR)})
+        return decls
+
+    @staticmethod
+    def cache_need(spec):
+        return PagedKV(spec.num_kv_heads, spec.head_dim, spec.window)
+
+    def __init__(self, spec, weights, prefix: str, runtime):
+        self.spec, self.runtime = spec, runtime
+        # one fused [q | k | v] matrix (scripts/jiuge.py:217-240 concatenates the same way)
+        self.w_qkv = torch.cat([weights.get(prefix + n + "_proj.weight", MATRIX) for n in "qkv"], dim=0).contiguous()
+        self.w_o = weights.get(prefix + "o_proj.weight", MATRIX)
+        self.b_qkv = None
+        if spec.bias:
+            self.b_qkv = torch.cat([weights.get(prefix + n + "_proj.bias", VECTOR) for n in "qkv"]).contiguous()
+        self.position = None
+        if spec.position is not None:
+            self.position = part_class("position", spec.position)(spec.position, weights, prefix, runtime)
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o))
+
+    def forward(self, h: torch.Tensor, ctx, view, writes_cache: bool = True) -> torch.Tensor:
+        from .. import kernels
+        s, rt = self.spec, self.runtime
+        T = ctx.ntok
+        qkv = rt.linear(h, self.w_qkv, out_dtype=torch.float32)
+        q = rt.empty(T, s.num_heads * s.head_dim)
+        table = ctx.block_tables[view.group_index]
+        pos = self.position
+        kernels.rope_kv(qkv, self.b_qkv, ctx.positions, ctx.row_req, table, view.page_size,
+                        pos.cos if pos else None, pos.sin if pos else None,
+                        pos.interleaved if pos else False, q, view.k_pages, view.v_pages,
+                        T, s.num_heads, s.num_kv_heads, s.head_dim, write_cache=writes_cache)
+        o = rt.empty(T, s.num_heads * s.head_dim)
+        kernels.attention_rows(q, view.k_pages, view.v_pages, o, ctx.positions, ctx.row_req, table, T,
+                               s.num_heads, s.softmax_scale, s.window or 0)
+        return rt.linear(o, self.w_o, out_dtype=torch.float32)

@@ -1,0 +1,141 @@
+"""What parts are made of: registries, the runtime, the step context, the residual stream.
+
+A part is a class registered under the ``kind`` of its specification.  It is built from
+(specification, weight source, name prefix, runtime) and knows nothing else: not the model
+it is in, not the other layers.  Four registries hold the four families:
+
+    norm            forward(residual, ctx, out_scale=1.0, rows=None) -> tensor [rows, size]
+    position        tables for a mixer; an object the mixer knows how to use
+    mixer           cache_need(spec) -> PagedKV | StateSlot | None   (static)
+                    forward(h, ctx, view, writes_cache) -> tensor [T, hidden]
+    feed_forward    forward(h, ctx) -> tensor [T, hidden]
+    block           forward(residual, ctx, view, writes_cache) -> None
+
+Every part class also has ``tensor_decls(spec) -> {local name: TensorDecl}``, a static
+method that needs no GPU: the model's manifest, the loader's checks and the random-weights
+mode are all derived from it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+NORMS: Dict[str, type] = {}
+POSITIONS: Dict[str, type] = {}
+MIXERS: Dict[str, type] = {}
+FEED_FORWARDS: Dict[str, type] = {}
+BLOCKS: Dict[str, type] = {}
+
+_FAMILIES = {"norm": NORMS, "position": POSITIONS, "mixer": MIXERS,
+             "feed_forward": FEED_FORWARDS, "block": BLOCKS}
+
+
+def register(family: str, kind: str) -> Callable[[type], type]:
+    """Class decorator: ``@register("mixer", "attention")``."""
+    table = _FAMILIES[family]
+
+    def deco(cls: type) -> type:
+        table[kind] = cls
+        return cls
+    return deco
+
+
+def part_class(family: str, spec) -> type:
+    table = _FAMILIES[family]
+    kind = getattr(spec, "kind", None)
+    if kind not in table:
+        raise KeyError(f"no {family} registered under kind {kind!r}; known: {sorted(table)}")
+    return table[kind]
+
+
+class Runtime:
+    """The precision and device a model runs in, and the matrix product the parts use.
+
+    ``dtype`` float32: every product runs on the CUDA cores in float32 (no tensor cores, no
+    TF32).  ``dtype`` bfloat16: operands are bfloat16, accumulation and (where asked) the
+    output are float32; the product goes to the library, as the reference sends its products
+    to one (src/models/inference_context.cpp:59-79), or to this package's own kernels.
+    """
+
+    def __init__(self, dtype: torch.dtype, device):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"the engine runs in float32 or bfloat16, not {dtype}")
+        self.dtype = dtype
+        self.device = torch.device(device)
+
+    def empty(self, *shape, dtype=None) -> torch.Tensor:
+        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+    def linear(self, h: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+               bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """h [T, K] times weight [N, K] transposed -> [T, N]."""
+        from .. import kernels
+        if self.dtype == torch.float32:
+            out = self.empty(h.shape[0], weight.shape[0], dtype=torch.float32)
+            return kernels.gemm_f32(h, weight, out, bias)
+        out_dtype = out_dtype or torch.bfloat16
+        if out_dtype == torch.bfloat16:
+            out = torch.mm(h, weight.t())
+        else:
+            out = torch.mm(h, weight.t(), out_dtype=out_dtype)
+        if bias is not None:
+            out += bias.to(out.dtype)
+        return out
+
+
+@dataclass
+class StepContext:
+    """One step's batch, as the parts see it.
+
+    Rows of all requests are concatenated: request i owns rows
+    ``req_start[i] .. req_start[i+1]-1`` at positions ``req_pos[i] ...``.  The ``host_*``
+    lists mirror the device arrays for parts that work on the host side.
+    """
+    ntok: int
+    nreq: int
+    tokens: torch.Tensor            # int32 [T]
+    positions: torch.Tensor         # int32 [T]   absolute position of each row
+    row_req: torch.Tensor           # int32 [T]   batch entry of each row
+    req_start: torch.Tensor         # int32 [nreq + 1]
+    req_pos: torch.Tensor           # int32 [nreq] position of each request's first row
+    slot_ids: torch.Tensor          # int32 [nreq] state slot of each request
+    block_tables: List[torch.Tensor]  # per cache group: int32 [nreq, max_blocks]
+    want_rows: torch.Tensor         # int32 [n_want] rows whose logits are wanted
+    n_want: int
+    host_req_start: List[int] = field(default_factory=list)
+    host_req_pos: List[int] = field(default_factory=list)
+    host_slot_ids: List[int] = field(default_factory=list)
+    decode_only: bool = False
+
+
+class ResidualStream:
+    """The float32 residual ``x`` plus at most one addition that has not been done yet.
+
+    A mixer or feed-forward returns its output; the block calls ``add(delta, scale)``.  The
+    sum is put off so that the next norm can do ``x += scale * delta`` and the normalisation
+    in one kernel.  ``value()`` makes the stream whole for a part that wants plain ``x``.
+    """
+
+    def __init__(self, x: torch.Tensor):
+        self.x = x
+        self.delta: Optional[torch.Tensor] = None
+        self.scale: float = 1.0
+
+    def add(self, delta: torch.Tensor, scale: float = 1.0) -> None:
+        if self.delta is not None:
+            self.value()
+        self.delta, self.scale = delta, scale
+
+    def take_pending(self):
+        d, s = self.delta, self.scale
+        self.delta, self.scale = None, 1.0
+        return d, s
+
+    def value(self) -> torch.Tensor:
+        if self.delta is not None:
+            from .. import kernels
+            d, s = self.take_pending()
+            kernels.residual_add(self.x, d, s)
+        return self.x

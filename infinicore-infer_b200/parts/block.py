@@ -1,0 +1,53 @@
+"""The pre-norm residual block: x += s * mixer(norm_a(x)); x += s * feed_forward(norm_b(x)).
+
+Reference: one iteration of the layer loop, src/models/jiuge/jiuge.cpp:195-258; ``s`` is
+MiniCPM's scale_depth / sqrt(num_layers), which the reference multiplies into the output
+and down matrices on the host (scripts/jiuge.py:297, :348) and which stays a float32
+constant of the block here.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+from ..weights import TensorDecl
+from .base import ResidualStream, part_class, register
+
+
+@register("block", "prenorm")
+class PreNormBlock:
+    @staticmethod
+    def tensor_decls(spec) -> Dict[str, TensorDecl]:
+        out = {}
+        for sub, prefix, family in _children(spec):
+            for name, decl in part_class(family, sub).tensor_decls(sub).items():
+                out[prefix + name] = decl
+        return out
+
+    @staticmethod
+    def cache_need(spec):
+        return part_class("mixer", spec.mixer).cache_need(spec.mixer)
+
+    def __init__(self, spec, weights, prefix: str, runtime):
+        self.spec = spec
+        build = lambda family, sub, p: part_class(family, sub)(sub, weights, prefix + p, runtime)
+        self.mixer_norm = build("norm", spec.mixer_norm, spec.mixer_norm_prefix)
+        self.mixer = build("mixer", spec.mixer, spec.mixer_prefix)
+        self.ffn_norm = build("norm", spec.ffn_norm, spec.ffn_norm_prefix)
+        self.feed_forward = build("feed_forward", spec.feed_forward, spec.ffn_prefix)
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights one pass over this block reads."""
+        parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+        return sum(p.weight_bytes() for p in parts if hasattr(p, "weight_bytes"))
+
+    def forward(self, residual: ResidualStream, ctx, view, writes_cache: bool = True) -> None:
+        s = self.spec.residual_scale
+        h = self.mixer_norm.forward(residual, ctx)
+        residual.add(self.mixer.forward(h, ctx, view, writes_cache), s)
+        h = self.ffn_norm.forward(residual, ctx)
+        residual.add(self.feed_forward.forward(h, ctx), s)
+
+
+def _children(spec):
+    return ((spec.mixer_norm, spec.mixer_norm_prefix, "norm"), (spec.mixer, spec.mixer_prefix, "mixer"),
+            (spec.ffn_norm, spec.ffn_norm_prefix, "norm"), (spec.feed_forward, spec.ffn_prefix, "feed_forward"))

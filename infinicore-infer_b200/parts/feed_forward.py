@@ -1,0 +1,40 @@
+"""SwiGLU feed-forward: down(silu(gate(h)) * up(h)).
+
+Reference: src/models/jiuge/jiuge.cpp:247-249 — one fused gate|up product, the SwiGLU
+operator over its two halves (jiuge.cpp:191-192), the down product.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..weights import MATRIX, TensorDecl
+from .base import register
+
+
+@register("feed_forward", "swiglu")
+class SwiGLU:
+    @staticmethod
+    def tensor_decls(spec) -> Dict[str, TensorDecl]:
+        d, di = spec.hidden_size, spec.intermediate_size
+        return {"gate_proj.weight": TensorDecl((di, d)), "up_proj.weight": TensorDecl((di, d)),
+                "down_proj.weight": TensorDecl((d, di))}
+
+    def __init__(self, spec, weights, prefix: str, runtime):
+        self.spec, self.runtime = spec, runtime
+        # gate rows, then up rows (scripts/jiuge.py:311-323)
+        self.w_gate_up = torch.cat([weights.get(prefix + "gate_proj.weight", MATRIX),
+                                    weights.get(prefix + "up_proj.weight", MATRIX)], dim=0).contiguous()
+        self.w_down = weights.get(prefix + "down_proj.weight", MATRIX)
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
+
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        from .. import kernels
+        rt = self.runtime
+        gu = rt.linear(h, self.w_gate_up, out_dtype=torch.float32)
+        act = rt.empty(h.shape[0], self.spec.intermediate_size)
+        kernels.swiglu(gu, act)
+        return rt.linear(act, self.w_down, out_dtype=torch.float32)
