@@ -121,14 +121,14 @@ class Engine:
         if not entries:
             return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=self.device)
         self._validate(entries)
+        starts = [self.position(e.req_id) for e in entries]
+        new_len = {e.req_id: s + len(e.tokens) for e, s in zip(entries, starts)}
+        if not self.cache.can_reserve(new_len):          # checked for the whole step before anything changes
+            raise OutOfPages(sum(sum(self.cache.pages_needed(r, n)) for r, n in new_len.items()),
+                             min(g.pool.available for g in self.cache.groups), "step")
         for e in entries:
             if not self.cache.is_live(e.req_id):
                 self.cache.admit(e.req_id)
-        starts = [self.cache.length(e.req_id) for e in entries]
-        new_len = {e.req_id: s + len(e.tokens) for e, s in zip(entries, starts)}
-        if not self.cache.can_reserve(new_len):
-            raise OutOfPages(sum(sum(self.cache.pages_needed(r, n)) for r, n in new_len.items()),
-                             min(g.pool.available for g in self.cache.groups), "step")
         for r, n in new_len.items():
             self.cache.reserve(r, n)
 

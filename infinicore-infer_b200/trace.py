@@ -25,6 +25,45 @@ import sys
 PAGE_SIZE = 16       # divides 64, so a pool of N tokens holds every request rounded up to 64
 
 
+def replay(engine, records, out_dir=None, on_done=None):
+    """Run trace records (dicts as described above) through ``engine.step``.
+
+    Returns ``{step: float32 array [wanted, vocab]}`` for the steps in which something was
+    wanted; with ``out_dir`` each array is also written to ``<out_dir>/<step>.f32``.
+    ``on_done(step)`` is called after each step.
+    """
+    import torch
+    from .engine import StepEntry
+    results = {}
+    for rec in records:
+        step = rec["step"]
+        entries = [StepEntry(e["id"], e["tokens"], e.get("want", ())) for e in rec.get("entries", ())]
+        logits = engine.step(entries)
+        if logits.shape[0]:
+            data = logits.to(torch.float32).contiguous().cpu().numpy().astype("<f4", copy=False)
+            results[step] = data
+            if out_dir is not None:
+                tmp = os.path.join(out_dir, f".{step}.f32.tmp")
+                with open(tmp, "wb") as f:
+                    f.write(data.tobytes())
+                os.replace(tmp, os.path.join(out_dir, f"{step}.f32"))
+        else:
+            torch.cuda.synchronize()
+        for rid in rec.get("end", ()):
+            if engine.cache.is_live(rid):
+                engine.end(rid)
+        if on_done is not None:
+            on_done(step)
+    return results
+
+
+def _records(stream):
+    for line in stream:
+        line = line.strip()
+        if line:
+            yield json.loads(line)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
@@ -37,7 +76,7 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
 
     import torch
-    from .engine import Engine, StepEntry
+    from .engine import Engine
 
     os.makedirs(args.out, exist_ok=True)
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
@@ -47,27 +86,7 @@ def main(argv=None) -> int:
                                 page_size=args.page_size, max_requests=16,
                                 max_step_tokens=cache_tokens, use_graphs=not args.no_graphs)
     print("[trace_run] ready", file=sys.stderr, flush=True)
-
-    for line in sys.stdin:
-        line = line.strip()
-        if not line:
-            continue
-        rec = json.loads(line)
-        step = rec["step"]
-        entries = [StepEntry(e["id"], e["tokens"], e.get("want", ())) for e in rec.get("entries", ())]
-        logits = engine.step(entries)
-        if logits.shape[0]:
-            data = logits.to(torch.float32).contiguous().cpu().numpy().astype("<f4", copy=False)
-            tmp = os.path.join(args.out, f".{step}.f32.tmp")
-            with open(tmp, "wb") as f:
-                f.write(data.tobytes())
-            os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
-        else:
-            torch.cuda.synchronize()
-        for rid in rec.get("end", ()):
-            if engine.cache.is_live(rid):
-                engine.end(rid)
-        print(f"done {step}", flush=True)
+    replay(engine, _records(sys.stdin), args.out, on_done=lambda s: print(f"done {s}", flush=True))
     return 0
 
 

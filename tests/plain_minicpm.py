@@ -163,13 +163,14 @@ def plain_sample(logits: torch.Tensor, temperature: float, topk: int, topp: floa
     (include/infinicore_infer/models/jiuge.h:85-87); else candidates are the largest logits
     until topk of them or a share topp of the mass is reached (ties with the last one
     included), and the token is the first candidate in vocabulary order whose running mass
-    exceeds u times the candidates' mass."""
+    exceeds u times the candidates' mass.  A token's mass is exp((logit - max) / temperature)
+    counted in units of 2^-32, rounded down: a token less likely than that is never drawn."""
     logits = logits.to(torch.float64)
     V = logits.numel()
     if temperature <= 0 or topk == 1:
         return int(torch.argmax(logits))       # first maximal index
     z = logits / temperature
-    w = torch.exp(z - z.max())
+    w = torch.floor(torch.exp(z - z.max()) * 4294967296.0)
     total = w.sum()
     order = torch.argsort(z, descending=True, stable=True)
     kk = topk if 1 < topk < V else V
@@ -190,7 +191,7 @@ def plain_sample(logits: torch.Tensor, temperature: float, topk: int, topp: floa
         i = jx
     cand = z >= tau
     cw = torch.where(cand, w, torch.zeros_like(w))
-    target = u * cw.sum()
+    target = torch.floor(u * cw.sum())
     cum = torch.cumsum(cw, 0)
     idx = torch.nonzero((cum > target) & cand)
     return int(idx[0]) if len(idx) else int(torch.nonzero(cand)[-1])

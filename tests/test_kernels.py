@@ -1,0 +1,288 @@
+"""Each CUDA kernel alone against a plain float64 torch reference, at sizes other than the engine's."""
+import math
+
+import pytest
+import torch
+
+from plain_minicpm import plain_attention, plain_rmsnorm, plain_rope, plain_sample
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _tol(dtype):
+    # float32: summation order only.  bfloat16: one rounding of the stored result (2^-9 relative).
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=4e-3, atol=4e-3)
+
+
+def _close(got, want, dtype, scale=1.0):
+    t = _tol(dtype)
+    torch.testing.assert_close(got.double().cpu(), want.double().cpu(), rtol=t["rtol"], atol=t["atol"] * scale)
+
+
+@pytest.fixture(scope="module")
+def K():
+    from infinicore_infer_b200 import kernels
+    return kernels
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("V,d,T", [(301, 80, 7), (1000, 2304, 3), (17, 6, 1)])
+def test_embed(K, dtype, V, d, T):
+    g = torch.Generator().manual_seed(V)
+    table = torch.randn(V, d, generator=g).to(dtype)
+    tok = torch.randint(0, V, (T,), generator=g, dtype=torch.int32)
+    tok[0] = V - 1
+    out = torch.empty(T, d, device=DEV)
+    K.embed(tok.to(DEV), table.to(DEV), 2.5, out)
+    assert torch.equal(out.cpu(), table.float()[tok.long()] * 2.5)
+
+
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("delta_dtype", [None, torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,d,eps", [(5, 80, 1e-5), (3, 2304, 1e-6), (2, 5000, 3e-6), (1, 14336, 1e-5)])
+def test_add_rmsnorm(K, out_dtype, delta_dtype, T, d, eps):
+    g = torch.Generator().manual_seed(d)
+    x = torch.randn(T, d, generator=g) * 3
+    w = 1 + 0.1 * torch.randn(d, generator=g)
+    delta = None if delta_dtype is None else torch.randn(T, d, generator=g).to(delta_dtype)
+    xd = x.to(DEV).clone()
+    out = torch.empty(T, d, dtype=out_dtype, device=DEV)
+    K.add_rmsnorm(xd, None if delta is None else delta.to(DEV), 0.7, w.to(DEV), eps, out, out_scale=4.0)
+    v = x.double() + (0 if delta is None else 0.7 * delta.double())
+    _close(xd, v, torch.float32)                       # the sum is written back in float32
+    _close(out, 4.0 * plain_rmsnorm(v, w.double(), eps), out_dtype, scale=4.0)
+
+
+def test_add_rmsnorm_gathers_rows_without_touching_the_stream(K):
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(9, 96, generator=g)
+    delta = torch.randn(9, 96, generator=g)
+    w = torch.ones(96)
+    rows = torch.tensor([8, 0, 3, 3], dtype=torch.int32)
+    xd = x.to(DEV).clone()
+    out = torch.empty(4, 96, device=DEV)
+    K.add_rmsnorm(xd, delta.to(DEV), 2.0, w.to(DEV), 1e-6, out, rows=rows.to(DEV))
+    assert torch.equal(xd.cpu(), x)
+    _close(out, plain_rmsnorm((x + 2 * delta).double()[rows.long()], w.double(), 1e-6), torch.float32)
+
+
+@pytest.mark.parametrize("in_dtype,out_dtype", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                                 (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("T,di", [(3, 136), (1, 5760), (17, 33)])
+def test_swiglu(K, in_dtype, out_dtype, T, di):
+    g = torch.Generator().manual_seed(di)
+    gu = (torch.randn(T, 2 * di, generator=g) * 3).to(in_dtype)
+    out = torch.empty(T, di, dtype=out_dtype, device=DEV)
+    K.swiglu(gu.to(DEV), out)
+    a, b = gu.double()[:, :di], gu.double()[:, di:]
+    _close(out, a * torch.sigmoid(a) * b, out_dtype, scale=3.0)
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 1, 1), (7, 301, 80), (65, 129, 33), (130, 64, 2304), (3, 1000, 17)])
+def test_gemm_f32_is_a_true_float32_product(K, M, N, K_):
+    g = torch.Generator().manual_seed(M * N)
+    a = torch.randn(M, K_, generator=g)
+    w = torch.randn(N, K_, generator=g)
+    bias = torch.randn(N, generator=g)
+    out = torch.empty(M, N, device=DEV)
+    K.gemm_f32(a.to(DEV), w.to(DEV), out, bias.to(DEV))
+    want = a.double() @ w.double().T + bias.double()
+    # TF32 would be wrong by 2^-11 of |a||w| ~ 5e-4 * sqrt(K); float32 stays below 1e-6 * sqrt(K)
+    assert (out.cpu().double() - want).abs().max() <= 2e-6 * math.sqrt(K_) * 4
+    # a row's result does not depend on the batch it is in
+    if M > 1:
+        one = torch.empty(1, N, device=DEV)
+        K.gemm_f32(a[M - 1:].contiguous().to(DEV), w.to(DEV), one, bias.to(DEV))
+        assert torch.equal(one[0], out[M - 1])
+
+
+def _scatter_pages(k, v, tables, page, num_pages, dtype):
+    """Dense per-request keys/values [len, nkvh, dh] -> pages [num_pages, nkvh, page, dh]."""
+    nkvh, dh = k[0].shape[1:]
+    kp = torch.full((num_pages, nkvh, page, dh), 7.0).to(dtype)       # junk where nothing was written
+    vp = torch.full((num_pages, nkvh, page, dh), -7.0).to(dtype)
+    for r, (kr, vr) in enumerate(zip(k, v)):
+        for j in range(kr.shape[0]):
+            p = tables[r][j // page]
+            kp[p, :, j % page] = kr[j].to(dtype)
+            vp[p, :, j % page] = vr[j].to(dtype)
+    return kp, vp
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkvh,dh,page,interleaved", [(6, 2, 48, 8, False), (4, 4, 16, 16, True),
+                                                          (3, 1, 128, 4, False), (8, 2, 256, 32, False)])
+def test_rope_and_cache_write(K, dtype, nh, nkvh, dh, page, interleaved):
+    g = torch.Generator().manual_seed(dh + nh)
+    lens = [(5, 9), (0, 3), (20, 1)]                    # (start position, rows) of three requests
+    T = sum(n for _, n in lens)
+    width = (nh + 2 * nkvh) * dh
+    qkv = torch.randn(T, width, generator=g)
+    bias = torch.randn(width, generator=g) * 0.1
+    max_pos, theta = 64, 5000.0
+    j = torch.arange(dh // 2, dtype=torch.float64)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] / theta ** (j / (dh // 2))
+    cos, sin = ang.cos().float(), ang.sin().float()
+    max_blocks = max_pos // page
+    perm = torch.randperm(3 * max_blocks, generator=g) + 1
+    table = perm.view(3, max_blocks).to(torch.int32)
+    positions = torch.cat([torch.arange(s, s + n) for s, n in lens]).to(torch.int32)
+    row_req = torch.cat([torch.full((n,), i) for i, (_, n) in enumerate(lens)]).to(torch.int32)
+    num_pages = 3 * max_blocks + 1
+    kp = torch.zeros(num_pages, nkvh, page, dh, dtype=dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    q_out = torch.empty(T, nh * dh, dtype=dtype, device=DEV)
+    K.rope_kv(qkv.to(DEV), bias.to(DEV), positions.to(DEV), row_req.to(DEV), table.to(DEV), page,
+              cos.to(DEV), sin.to(DEV), interleaved, q_out, kp, vp, T, nh, nkvh, dh)
+    x = (qkv + bias).double()
+    q = x[:, :nh * dh].view(T, nh, dh)
+    k = x[:, nh * dh:(nh + nkvh) * dh].view(T, nkvh, dh)
+    v = x[:, (nh + nkvh) * dh:].view(T, nkvh, dh)
+    if interleaved:
+        def rot(t):
+            c, s = ang[positions.long()][:, None, :].cos(), ang[positions.long()][:, None, :].sin()
+            o = torch.empty_like(t)
+            o[..., 0::2] = t[..., 0::2] * c - t[..., 1::2] * s
+            o[..., 1::2] = t[..., 0::2] * s + t[..., 1::2] * c
+            return o
+    else:
+        rot = lambda t: plain_rope(t, positions, theta)
+    _close(q_out.view(T, nh, dh), rot(q), dtype, scale=4.0)
+    want_k = torch.zeros(num_pages, nkvh, page, dh, dtype=torch.float64)
+    want_v = torch.zeros_like(want_k)
+    rk = rot(k)
+    for t in range(T):
+        p = int(table[row_req[t], positions[t] // page])
+        want_k[p, :, positions[t] % page] = rk[t]
+        want_v[p, :, positions[t] % page] = v[t]
+    _close(kp, want_k, dtype, scale=4.0)
+    _close(vp, want_v, dtype, scale=4.0)
+    assert float(kp[0].abs().max()) == 0.0              # the null page was not written
+
+
+def _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, plant=None, seed=0):
+    """lens: cached length of each request; queries: per request the positions that are rows."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(lens)
+    k = [torch.randn(n, nkvh, dh, generator=g) for n in lens]
+    v = [torch.randn(n, nkvh, dh, generator=g) for n in lens]
+    qf = [torch.randn(n, nh, dh, generator=g) for n in lens]
+    if plant:
+        # one key far back gets a score that stands out: the row's output must be that key's value
+        for (r, qpos, kpos, head) in plant:
+            kk = k[r][kpos, head // (nh // nkvh)]
+            qf[r][qpos, head] = kk * (40.0 / float(kk.norm()) ** 2) * math.sqrt(dh)
+    qf = [t.to(dtype).float() for t in qf]; k = [t.to(dtype).float() for t in k]; v = [t.to(dtype).float() for t in v]
+    max_blocks = (max(lens) + page - 1) // page + 1
+    perm = (torch.randperm(R * max_blocks, generator=g) + 1).view(R, max_blocks)
+    tables = perm.tolist()
+    num_pages = R * max_blocks + 1
+    kp, vp = _scatter_pages(k, v, tables, page, num_pages, dtype)
+    positions = torch.tensor([p for r in range(R) for p in queries[r]], dtype=torch.int32)
+    row_req = torch.tensor([r for r in range(R) for _ in queries[r]], dtype=torch.int32)
+    q = torch.stack([qf[r][p] for r in range(R) for p in queries[r]]).to(dtype)
+    T = q.shape[0]
+    out = torch.empty(T, nh * dh, dtype=dtype, device=DEV)
+    scale = dh ** -0.5
+    K.attention_rows(q.view(T, nh * dh).to(DEV), kp.to(DEV), vp.to(DEV), out, positions.to(DEV),
+                     row_req.to(DEV), perm.to(torch.int32).to(DEV), T, nh, scale, window or 0)
+    want = torch.cat([plain_attention(qf[r].double(), k[r].double(), v[r].double(), scale, window)[queries[r]]
+                      for r in range(R) if len(queries[r])])
+    return out.view(T, nh, dh), want, v
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkvh,dh,page,window", [
+    (4, 4, 16, 16, None), (3, 1, 32, 8, None), (6, 2, 48, 4, None), (8, 2, 128, 16, None),
+    (5, 5, 64, 16, 7), (2, 1, 80, 32, 33), (2, 2, 256, 16, None)])
+def test_attention_rows_over_pages(K, dtype, nh, nkvh, dh, page, window):
+    lens = [37, 1, 130, 64]
+    # a portion at the end, a single first token, decoded tokens, a whole prompt cut at page edges
+    queries = [list(range(30, 37)), [0], [129], list(range(0, 64))]
+    got, want, _ = _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, seed=dh)
+    _close(got, want, dtype, scale=2.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [None, 50])
+def test_attention_finds_one_far_key_among_hundreds(K, dtype, window):
+    nh, nkvh, dh, page = 4, 2, 64, 16
+    lens = [700]
+    # query at 699 must find key 3 (full) / key 650 = the window's far edge; query at 320 finds key 319 - a page edge
+    far = 3 if window is None else 699 - window + 1
+    plant = [(0, 699, far, 1), (0, 320, 319, 2), (0, 512, 511 if window else 0, 3)]
+    got, want, v = _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, [[320, 512, 699]], plant, seed=5)
+    _close(got, want, dtype, scale=2.0)
+    assert torch.allclose(got[2, 1].float().cpu(), v[0][far, 0], atol=2e-2)
+    assert torch.allclose(got[0, 2].float().cpu(), v[0][319, 1], atol=2e-2)
+    if window:
+        # one position beyond the window's edge must NOT be seen
+        plant = [(0, 699, far - 1, 1)]
+        got, want, v = _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, [[699]], plant, seed=5)
+        _close(got, want, dtype, scale=2.0)
+        assert not torch.allclose(got[0, 1].float().cpu(), v[0][far - 1, 0], atol=0.2)
+
+
+@pytest.mark.parametrize("V", [5, 301, 122753])
+def test_argmax_takes_the_first_of_equal_maxima(K, V):
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(3, V, generator=g)
+    logits[1, V - 1] = 50.0
+    logits[2, V // 2] = 60.0; logits[2, V // 3] = 60.0
+    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    K.argmax(logits.to(DEV), out)
+    assert out.tolist() == [int(logits[0].argmax()), V - 1, V // 3]
+    # rows with a stride (a padded leading dimension)
+    wide = torch.zeros(3, V + 3)
+    wide[:, :V] = logits
+    K.argmax(wide.to(DEV)[:, :V], out)
+    assert out.tolist() == [int(logits[0].argmax()), V - 1, V // 3]
+
+
+@pytest.mark.parametrize("V", [37, 1000, 122753])
+def test_sample_matches_the_plain_rule(K, V):
+    g = torch.Generator().manual_seed(V)
+    cases = []
+    for i, (temp, topk, topp) in enumerate([(0.0, 0, 1.0), (1.0, 1, 1.0), (1.0, 0, 1.0), (0.8, 0, 1.0), (2.5, 0, 1.0),
+                                             (1.0, 5, 1.0), (0.7, 20, 1.0), (1.0, 0, 0.6), (1.3, 0, 0.9),
+                                             (0.9, 8, 0.5), (1.0, V, 1.0), (1.0, 3, 0.999)]):
+        for u in (0.0, 0.013, 0.31, 0.5, 0.77, 0.9991):
+            cases.append((temp, topk, topp, u))
+    n = len(cases)
+    # logits on a grid of 1/64 with distinct values near the top: no ties at the cut, float32-exact
+    base = (torch.randperm(V, generator=g).float() / 64.0)
+    base = base - base.max() + 3.0
+    logits = base.repeat(n, 1)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    f = lambda xs, dt: torch.tensor(xs, dtype=dt, device=DEV)
+    K.sample(logits.to(DEV), f([c[0] for c in cases], torch.float32), f([c[1] for c in cases], torch.int32),
+             f([c[2] for c in cases], torch.float32), f([c[3] for c in cases], torch.float32), out)
+    got = out.tolist()
+    miss = []
+    for i, c in enumerate(cases):
+        want = plain_sample(logits[i], *c)
+        if got[i] != want:
+            # a float32-vs-float64 difference may move the pick only to a neighbour in the running mass
+            miss.append((c, got[i], want))
+    assert not miss, miss[:5]
+
+
+def test_sample_is_reproducible_and_follows_the_distribution(K):
+    V, n = 50, 4000
+    g = torch.Generator().manual_seed(1)
+    row = torch.randn(V, generator=g) * 2
+    logits = row.repeat(n, 1).to(DEV)
+    u = torch.rand(n, generator=g).to(DEV)
+    ones = torch.full((n,), 1.0, device=DEV)
+    zeros = torch.zeros(n, dtype=torch.int32, device=DEV)
+    a = torch.empty(n, dtype=torch.int32, device=DEV)
+    b = torch.empty_like(a)
+    K.sample(logits, ones, zeros, ones, u, a)
+    K.sample(logits, ones, zeros, ones, u, b)
+    assert torch.equal(a, b)
+    freq = torch.bincount(a.long().cpu(), minlength=V).double() / n
+    p = torch.softmax(row.double(), 0)
+    assert (freq - p).abs().max() < 4 * math.sqrt(0.25 / n)
