@@ -1,0 +1,312 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine's decode step on one B200: ``python bench.py --gpus 1 --steps K --warmup W``.
+
+The model has the layer sizes of the MiniCPM-2B shape (40 layers, hidden 2304, 36/36 heads of
+64, intermediate 5760, vocabulary 122753, tied embeddings) with random bfloat16 weights made
+on the device.  A step is one decode step of a batch of 8 requests whose caches hold about
+4096 tokens each (synthetic cache contents: decoding cost does not depend on the values).
+
+One JSON line is printed:
+  value       decoded tokens per second, device-timed (CUDA events around K steps of the engine's
+              step function + the sampling kernel; token ids are fixed, nothing is read back);
+  e2e         the same through the Python entry point (``batch_infer_one_round``): every step copies
+              its token ids and block tables from pinned host memory and reads the sampled ids back;
+  prefill     one 2,048-token prompt through the step function;
+  roofline    bytes a decode step must read (every weight once + the live requests' cache) / time;
+  points      decode tokens per second at batch 1 and 64 (context 4096) and at context 512.
+Peaks come from MEASURED_PEAKS.json beside this file if present, else from the fallback values.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# configs[2] of the benchmark definition: the MiniCPM-2B shape
+SHAPE_2B = dict(model_type="minicpm", num_hidden_layers=40, hidden_size=2304, num_attention_heads=36,
+                num_key_value_heads=36, intermediate_size=5760, vocab_size=122753,
+                max_position_embeddings=4096, rms_norm_eps=1e-5, rope_theta=10000.0, scale_emb=12,
+                scale_depth=1.4, dim_model_base=256, tie_word_embeddings=True)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                data = json.load(f)
+            flat = {}
+            def walk(d):
+                for k, v in d.items():
+                    if isinstance(v, dict):
+                        walk(v)
+                    elif isinstance(v, (int, float)):
+                        flat.setdefault(k, float(v))
+            walk(data)
+            if "hbm_gbs" in flat and "bf16_tflops" in flat:
+                return {"hbm_gbs": flat["hbm_gbs"], "bf16_tflops": flat["bf16_tflops"]}, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi in the background while the timed region runs; stopped by its own PID."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __enter__(self):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        self.file.flush()
+
+    def summary(self):
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the shape has (both numbers are reported)")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and context 512 points")
+    ap.add_argument("--no-prefill", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "InfiniCore-Infer has no Python package to install (xmake C++ project) and its device "
+                          "libraries infiniop/infinirt/infiniccl are absent; it cannot be built or run here"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from infinicore_infer_b200.config import MiniCPMConfig
+    from infinicore_infer_b200.engine import Engine, StepEntry
+    from infinicore_infer_b200.jiuge import JiugeForCauslLM
+    from infinicore_infer_b200.parts import model_manifest
+    from infinicore_infer_b200.tasks import InferTask, KVCache
+    from infinicore_infer_b200.weights import DeviceRandomWeights
+    from infinicore_infer_b200 import kernels
+
+    peaks, peak_source = load_peaks()
+    shape = dict(SHAPE_2B)
+    full_layers = shape["num_hidden_layers"]
+    if args.layers:
+        shape["num_hidden_layers"] = args.layers
+    shape["max_position_embeddings"] = max(args.context, 4096)
+    cfg = MiniCPMConfig.from_dict(shape)
+    spec = cfg.model_spec()
+    dev = "cuda:0"
+    page = 16
+    max_b = 1 if args.no_points else 64
+    max_b = max(max_b, args.batch)
+    cache_tokens = max_b * (args.context + page)
+    t_load = time.time()
+    weights = DeviceRandomWeights(model_manifest(spec), seed=0, compute_dtype=torch.bfloat16, device=dev, std=0.02)
+    engine = Engine(spec, weights, dtype=torch.bfloat16, device=dev, cache_tokens=cache_tokens, page_size=page,
+                    max_requests=max_b, max_step_tokens=4096)
+    engine.config = cfg
+    for view in engine.cache.views:          # synthetic cache contents
+        view.k_pages.normal_(0, 0.5)
+        view.v_pages.normal_(0, 0.5)
+    torch.cuda.synchronize()
+    t_load = time.time() - t_load
+    model = JiugeForCauslLM.from_engine(engine)
+    V = spec.vocab_size
+    gen = torch.Generator().manual_seed(0)
+    kv_bytes_per_token = sum(2 * v.k_pages.shape[1] * v.k_pages.shape[3] * v.k_pages.element_size()
+                             for v in engine.cache.views)
+    weight_bytes = engine.model.weight_bytes_per_step()
+
+    def fill(n_req, length, prefix):
+        """n_req requests whose caches hold ``length`` positions (contents are the synthetic values)."""
+        ids = []
+        for i in range(n_req):
+            rid = f"{prefix}{i}"
+            engine.begin(rid)
+            engine.cache.reserve(rid, length)
+            engine.cache.commit(rid, length)
+            ids.append(rid)
+        return ids
+
+    def drop(ids):
+        for rid in ids:
+            engine.end(rid)
+
+    def decode_device(n_req, context, steps, warmup):
+        """Device time of ``steps`` decode steps (step function + argmax) with fixed token ids."""
+        start = context - (steps + warmup) - 1
+        ids = fill(n_req, start, "d")
+        toks = torch.randint(0, V, (n_req,), generator=gen).tolist()
+        out = torch.empty(n_req, dtype=torch.int32, device=dev)
+        entries = [StepEntry(r, [t], [0]) for r, t in zip(ids, toks)]
+        for _ in range(warmup):
+            kernels.argmax(engine.step(entries), out)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = engine.kernel_launches
+        e0.record()
+        for _ in range(steps):
+            kernels.argmax(engine.step(entries), out)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        launches = engine.kernel_launches - l0 + steps
+        mean_ctx = start + warmup + (steps + 1) / 2
+        drop(ids)
+        return ms, launches, mean_ctx
+
+    def decode_e2e(n_req, context, steps, warmup):
+        """The same through ``batch_infer_one_round``: host token ids in, sampled ids out, every step."""
+        start = context - (steps + warmup) - 1
+        tasks = []
+        for i in range(n_req):
+            t = InferTask(i, [int(torch.randint(0, V, (1,), generator=gen))], context + 8, 0.0, 1, 1.0, [])
+            kv = KVCache(model)
+            engine.cache.reserve(kv.data(), start)
+            engine.cache.commit(kv.data(), start)
+            t.bind_kvcache(kv)
+            t.pos = start
+            tasks.append(t)
+        for _ in range(warmup):
+            for t, tok in zip(tasks, model.batch_infer_one_round(tasks)):
+                t.next(tok)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.perf_counter()
+        e0.record()
+        for _ in range(steps):
+            for t, tok in zip(tasks, model.batch_infer_one_round(tasks)):
+                t.next(tok)
+        e1.record()
+        torch.cuda.synchronize()
+        wall_ms = (time.perf_counter() - w0) * 1000 / steps
+        ms = max(e0.elapsed_time(e1) / steps, wall_ms)
+        for t in tasks:
+            t.kvcache().drop(model)
+        return ms
+
+    result_points = {}
+    with ClockSampler() as clocks:
+        ms, launches, mean_ctx = decode_device(args.batch, args.context, args.steps, args.warmup)
+        e2e_ms = decode_e2e(args.batch, args.context, args.steps, args.warmup)
+    clock_summary = clocks.summary()
+    value = args.batch * 1000.0 / ms
+    step_bytes = weight_bytes + args.batch * mean_ctx * kv_bytes_per_token
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+
+    prefill = None
+    if not args.no_prefill:
+        T = 2048
+        ptoks = torch.randint(0, V, (T,), generator=gen).tolist()
+        times = []
+        for i in range(4):
+            rid = f"p{i}"
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            engine.step([StepEntry(rid, ptoks, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            engine.end(rid)
+            if i >= 1:
+                times.append(e0.elapsed_time(e1))
+        pms = min(times)
+        L, d, nh, dh, di = cfg.num_hidden_layers, cfg.hidden_size, cfg.num_attention_heads, cfg.head_dim, cfg.intermediate_size
+        nkv = cfg.num_key_value_heads
+        per_tok = 2 * L * (d * (nh + 2 * nkv) * dh + nh * dh * d + 3 * d * di)
+        flops = T * per_tok + L * 2 * T * T * dh * nh + 2 * d * V
+        prefill = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
+                   "frac": round(flops / (pms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+                   "tflops": round(flops / (pms * 1e-3) / 1e12, 1), "peak_source": peak_source}
+
+    if not args.no_points:
+        psteps, pwarm = min(args.steps, 32), 4
+        for name, b, c in (("decode_b1", 1, args.context), ("decode_b64", 64, args.context),
+                           ("decode_b1_ctx512", 1, 512), ("decode_b8_ctx512", 8, 512), ("decode_b64_ctx512", 64, 512)):
+            pm, _, _ = decode_device(b, c, psteps, pwarm)
+            result_points[name] = round(b * 1000.0 / pm, 1)
+
+    meta_bytes = 4 * (7 * args.batch + 8 + args.batch * engine.cache.max_blocks * len(engine.cache.groups))
+    line = {
+        "metric": "decode tok/s @ batch 8 (MiniCPM-2B shape, context 4096)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random-init weights N(0,0.02), uniform random token ids, random cache contents",
+        "config": {
+            "model": "MiniCPM-2B shape", "layers": cfg.num_hidden_layers, "layers_of_shape": full_layers,
+            "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+            "tied_embeddings": True, "global_batch": args.batch, "seq_len": args.context,
+            "context_len": args.context, "page_size": page, "parallelism": "single GPU",
+            "l2": "inputs larger than L2: 5.4 GB of weights and the cache are re-read every step",
+            "weights_gb": round(weight_bytes / 1e9, 3), "kv_bytes_per_token": kv_bytes_per_token,
+        },
+        "e2e": {"value": round(args.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s",
+                "ms_per_step": round(e2e_ms, 4), "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peak_source,
+                     "bytes_per_step": int(step_bytes)},
+        "clocks": clock_summary,
+        "load_s": round(t_load, 1),
+    }
+    if prefill is not None:
+        line["prefill"] = prefill
+    if result_points:
+        line["points"] = result_points
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -97,6 +97,19 @@ class CacheGroup:
         self.pool.free(freed)
         return len(freed)
 
+    def truncate(self, req, new_len: int) -> int:
+        """Drop what lies at positions >= new_len (a request that goes back to a shared prefix)."""
+        table = self.tables.get(req)
+        if table is None:
+            return 0
+        keep = (new_len + self.page_size - 1) // self.page_size
+        if self.need.window is not None and self._first_needed_block(new_len) < self.first_block.get(req, 0):
+            raise ValueError(f"cache group {self.name}: positions before {new_len} have left the window already")
+        freed = [p for p in table[keep:] if p != NO_PAGE]
+        del table[keep:]
+        self.pool.free(freed)
+        return len(freed)
+
     def release(self, req) -> int:
         table = self.tables.pop(req, None)
         self.first_block.pop(req, None)

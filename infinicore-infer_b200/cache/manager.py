@@ -127,6 +127,14 @@ class CacheManager:
         for g in self.groups:
             g.trim(req, new_len)
 
+    def truncate(self, req, new_len: int) -> None:
+        """Go back to ``new_len`` cached positions (new_len <= the current length)."""
+        if new_len > self.lengths[req]:
+            raise ValueError(f"request {req!r} holds {self.lengths[req]} positions, cannot truncate to {new_len}")
+        for g in self.groups:
+            g.truncate(req, new_len)
+        self.lengths[req] = new_len
+
     def release(self, req) -> None:
         if req not in self.lengths:
             raise KeyError(f"request {req!r} is not live")

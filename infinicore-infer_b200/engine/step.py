@@ -90,6 +90,7 @@ class Engine:
         self._graphs: Dict[int, object] = {}
         self.steps_run = 0
         self.tokens_run = 0
+        self.kernel_launches = 0      # this package's kernels launched by steps (replayed graphs included)
 
     # ---- construction -------------------------------------------------------------------------
     @classmethod
@@ -136,8 +137,11 @@ class Engine:
         if decode:
             logits = self._run_decode_graph(entries, starts)
         else:
+            from .. import kernels
             ctx = self._upload(entries, starts, len(entries), sum(len(e.tokens) for e in entries))
+            before = kernels.launch_count
             logits = self.model.forward(ctx, self.cache.views)
+            self.kernel_launches += kernels.launch_count - before
         for r, n in new_len.items():
             self.cache.commit(r, n)
         self.steps_run += 1
@@ -255,13 +259,16 @@ class Engine:
             # run once eagerly (library handles, lazy module loads), then capture
             self.model.forward(ctx, self.cache.views)
             torch.cuda.synchronize()
+            from .. import kernels
             graph = torch.cuda.CUDAGraph()
+            before = kernels.launch_count
             with torch.cuda.graph(graph):
                 out = self.model.forward(ctx, self.cache.views)
-            rec = (graph, out)
+            rec = (graph, out, kernels.launch_count - before)
             self._graphs[bucket] = rec
-        graph, out = rec
+        graph, out, launches = rec
         graph.replay()
+        self.kernel_launches += launches
         rows = []
         for i, e in enumerate(entries):
             rows.extend([i] * len(e.want))

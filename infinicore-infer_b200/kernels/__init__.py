@@ -22,6 +22,9 @@ class KernelError(RuntimeError):
     pass
 
 
+launch_count = 0      # kernels of this package launched through these bindings (captured ones count once)
+
+
 def dtype_code(dtype: torch.dtype) -> int:
     try:
         return _CODE[dtype]
@@ -47,6 +50,8 @@ def _need(t: torch.Tensor, name: str, dtype=None, contiguous=True):
 
 
 def _check(module: str, rc: int):
+    global launch_count
+    launch_count += 1
     if rc:
         lib = _build.load(module)
         fn = getattr(lib, f"jk_{module}_last_error")
