@@ -115,6 +115,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the shape has (both numbers are reported)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and context 512 points")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
+                    help="run a few steps between cudaProfilerStart/Stop (for ncu --profile-from-start off) and exit")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -234,6 +236,30 @@ def main():
         for t in tasks:
             t.kvcache().drop(model)
         return ms
+
+    if args.profile:
+        if args.profile == "decode":
+            ids = fill(args.batch, args.context - 16, "q")
+            entries = [StepEntry(r, [1], [0]) for r in ids]
+            out = torch.empty(args.batch, dtype=torch.int32, device=dev)
+            for _ in range(3):
+                kernels.argmax(engine.step(entries), out)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            for _ in range(2):
+                kernels.argmax(engine.step(entries), out)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        else:
+            ptoks = torch.randint(0, V, (2048,), generator=gen).tolist()
+            engine.step([StepEntry("w", ptoks, [2047])]); engine.end("w")
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            engine.step([StepEntry("w", ptoks, [2047])])
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        print(json.dumps({"profiled": args.profile, "layers": cfg.num_hidden_layers}))
+        return 0
 
     result_points = {}
     with ClockSampler() as clocks:

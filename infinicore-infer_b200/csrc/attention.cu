@@ -146,3 +146,506 @@ JK_EXPORT int jk_attention_rows(const void *q, const void *k_pages, const void *
     JK_CHECK_LAUNCH("attention_rows");
     return JK_OK;
 }
+
+// =======================================================================================
+// bfloat16 fast paths.  Both read the same pages and block tables as the row kernel above
+// and compute the same function; they differ in how the work is cut.
+// =======================================================================================
+
+// ---------------------------------------------------------------------------------------
+// Decode kernel: for rows of requests that bring few rows (a decoded token, a short
+// portion).  Work item = (row, key/value head, split of the key range).  The `HG` query heads
+// of a key/value head that one block handles share every key and value it loads.  A group
+// of LPR lanes owns one key at a time: each lane loads 16 bytes of the key row (coalesced:
+// the groups of a warp read consecutive rows), the group's partial dot products are summed
+// with shuffles, and every group keeps its own running (max, sum, accumulator), so nothing
+// synchronises inside the loop.  Groups, warps and splits are merged at the end with the
+// usual rule  acc = sum_i exp(m_i - M) acc_i,  l = sum_i exp(m_i - M) l_i.
+// The split partials go to scratch memory and a second kernel merges them.
+// ---------------------------------------------------------------------------------------
+struct DecodeArgs {
+    const __nv_bfloat16 *q;        // [T, nh, dh]
+    const __nv_bfloat16 *k_pages;  // [pages, nkvh, page_size, dh]
+    const __nv_bfloat16 *v_pages;
+    __nv_bfloat16 *out;            // [T, nh, dh]
+    float *part_acc;               // [nrows, nh, splits, dh]
+    float *part_ml;                // [nrows, nh, splits, 2]
+    const int *rows;               // [nrows] row indices, or null for 0..nrows-1
+    const int *positions;
+    const int *row_req;
+    const int *block_table;
+    int nrows, nh, nkvh, dh, page_size, max_blocks, window, splits;
+    float scale_log2;              // softmax scale * log2(e)
+};
+
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_UNROLL = 4;      // keys a group has in flight
+
+template <int LPR, int HG>         // lanes per key row, query heads per block
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attention_decode_kernel(DecodeArgs a) {
+    constexpr int GROUPS = DEC_WARPS * 32 / LPR;
+    const int split = blockIdx.x;
+    const int g = a.nh / a.nkvh;
+    const int hgroups = (g + HG - 1) / HG;
+    const int hk = blockIdx.y / hgroups;
+    const int h0 = hk * g + (blockIdx.y % hgroups) * HG;        // first query head of this block
+    const int nheads = min(HG, hk * g + g - h0);
+    const int ri = blockIdx.z;
+    const int t = a.rows ? a.rows[ri] : ri;
+    const int pos = a.positions[t];
+    const int *bt = a.block_table + (size_t)a.row_req[t] * a.max_blocks;
+    const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+    const int nkeys = pos - lo + 1;
+    int chunk = (nkeys + a.splits - 1) / a.splits;
+    chunk = (chunk + GROUPS - 1) / GROUPS * GROUPS;
+    const int k_begin = lo + split * chunk;
+    const int k_end = min(pos + 1, k_begin + chunk);             // exclusive
+
+    const int lane_in = threadIdx.x % LPR;                       // which 16 bytes of the row
+    const int group = threadIdx.x / LPR;
+    const int dh = a.dh;
+    const bool lane_ok = lane_in * 8 < dh;
+    const size_t head_off = (size_t)hk * a.page_size * dh + lane_in * 8;
+    const size_t page_stride = (size_t)a.nkvh * a.page_size * dh;
+
+    float qf[HG][8];
+#pragma unroll
+    for (int hh = 0; hh < HG; ++hh) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) qf[hh][e] = 0.f;
+        if (hh < nheads && lane_ok) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(a.q + ((size_t)t * a.nh + h0 + hh) * dh + lane_in * 8);
+            const __nv_bfloat162 *p2 = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(p2[e]);
+                qf[hh][2 * e] = f.x * a.scale_log2;
+                qf[hh][2 * e + 1] = f.y * a.scale_log2;
+            }
+        }
+    }
+    float m[HG], l[HG], acc[HG][8];
+#pragma unroll
+    for (int hh = 0; hh < HG; ++hh) {
+        m[hh] = -INFINITY; l[hh] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[hh][e] = 0.f;
+    }
+
+    // The trip count is the same for every thread of the block and no thread skips a shuffle:
+    // a key beyond the range scores -inf and so weighs exactly zero.
+    for (int base = k_begin; base < k_end; base += GROUPS * DEC_UNROLL) {
+        uint4 kr[DEC_UNROLL], vr[DEC_UNROLL];
+        bool ok[DEC_UNROLL];
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) {
+            const int j = base + group + u * GROUPS;
+            ok[u] = j < k_end;
+            kr[u] = make_uint4(0, 0, 0, 0); vr[u] = make_uint4(0, 0, 0, 0);
+            if (ok[u] && lane_ok) {
+                const size_t off = (size_t)bt[j / a.page_size] * page_stride + head_off + (size_t)(j % a.page_size) * dh;
+                kr[u] = *reinterpret_cast<const uint4 *>(a.k_pages + off);
+                vr[u] = *reinterpret_cast<const uint4 *>(a.v_pages + off);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) {
+            float kf[8], vf[8];
+            {
+                const __nv_bfloat162 *k2 = reinterpret_cast<const __nv_bfloat162 *>(&kr[u]);
+                const __nv_bfloat162 *v2 = reinterpret_cast<const __nv_bfloat162 *>(&vr[u]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 fk = __bfloat1622float2(k2[e]), fv = __bfloat1622float2(v2[e]);
+                    kf[2 * e] = fk.x; kf[2 * e + 1] = fk.y; vf[2 * e] = fv.x; vf[2 * e + 1] = fv.y;
+                }
+            }
+#pragma unroll
+            for (int hh = 0; hh < HG; ++hh) {
+                float s = 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s = fmaf(qf[hh][e], kf[e], s);
+#pragma unroll
+                for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (!ok[u]) s = -INFINITY;
+                const float m_new = fmaxf(m[hh], s);
+                const float m_use = m_new == -INFINITY ? 0.f : m_new;
+                const float corr = exp2f(m[hh] - m_use);
+                const float p = exp2f(s - m_use);
+                l[hh] = l[hh] * corr + p;
+                m[hh] = m_new;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[hh][e] = fmaf(p, vf[e], acc[hh][e] * corr);
+            }
+        }
+    }
+
+    // merge the groups of this block
+    extern __shared__ float dec_smem[];
+    float *s_ml = dec_smem;                                   // [GROUPS][HG][2]
+    float *s_acc = dec_smem + GROUPS * HG * 2;                // [GROUPS][HG][LPR*8]
+#pragma unroll
+    for (int hh = 0; hh < HG; ++hh) {
+        if (lane_in == 0) {
+            s_ml[(group * HG + hh) * 2] = m[hh];
+            s_ml[(group * HG + hh) * 2 + 1] = l[hh];
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s_acc[((size_t)group * HG + hh) * (LPR * 8) + lane_in * 8 + e] = acc[hh][e];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nheads * dh; i += blockDim.x) {
+        const int hh = i / dh, e = i - hh * dh;
+        float M = -INFINITY;
+        for (int gi = 0; gi < GROUPS; ++gi) M = fmaxf(M, s_ml[(gi * HG + hh) * 2]);
+        float L = 0.f, A = 0.f;
+        if (M > -INFINITY) {
+            for (int gi = 0; gi < GROUPS; ++gi) {
+                const float w = exp2f(s_ml[(gi * HG + hh) * 2] - M);
+                L += w * s_ml[(gi * HG + hh) * 2 + 1];
+                A += w * s_acc[((size_t)gi * HG + hh) * (LPR * 8) + e];
+            }
+        }
+        const size_t slot = ((size_t)ri * a.nh + h0 + hh) * a.splits + split;
+        if (a.splits == 1) {
+            a.out[((size_t)t * a.nh + h0 + hh) * dh + e] = __float2bfloat16_rn(A / L);
+        } else {
+            a.part_acc[slot * dh + e] = A;
+            if (e == 0) { a.part_ml[slot * 2] = M; a.part_ml[slot * 2 + 1] = L; }
+        }
+    }
+}
+
+// One block per (query head, row): merge the splits' partial results.
+__global__ void attention_combine_kernel(DecodeArgs a) {
+    const int h = blockIdx.x, ri = blockIdx.y;
+    const int t = a.rows ? a.rows[ri] : ri;
+    const size_t base = ((size_t)ri * a.nh + h) * a.splits;
+    float M = -INFINITY;
+    for (int s = 0; s < a.splits; ++s) M = fmaxf(M, a.part_ml[(base + s) * 2]);
+    float L = 0.f;
+    for (int s = 0; s < a.splits; ++s) {
+        const float ms = a.part_ml[(base + s) * 2];
+        if (ms > -INFINITY) L += exp2f(ms - M) * a.part_ml[(base + s) * 2 + 1];
+    }
+    for (int e = threadIdx.x; e < a.dh; e += blockDim.x) {
+        float A = 0.f;
+        for (int s = 0; s < a.splits; ++s) {
+            const float ms = a.part_ml[(base + s) * 2];
+            if (ms > -INFINITY) A += exp2f(ms - M) * a.part_acc[(base + s) * a.dh + e];
+        }
+        a.out[((size_t)t * a.nh + h) * a.dh + e] = __float2bfloat16_rn(A / L);
+    }
+}
+
+template <int LPR, int HG>
+static int launch_decode(const DecodeArgs &a, cudaStream_t stream) {
+    constexpr int GROUPS = DEC_WARPS * 32 / LPR;
+    const int g = a.nh / a.nkvh;
+    const int hgroups = (g + HG - 1) / HG;
+    dim3 grid(a.splits, a.nkvh * hgroups, a.nrows);
+    const size_t smem = (size_t)GROUPS * HG * (2 + LPR * 8) * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<LPR, HG>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_decode: %s", cudaGetErrorString(e));
+    }
+    attention_decode_kernel<LPR, HG><<<grid, DEC_WARPS * 32, smem, stream>>>(a);
+    JK_CHECK_LAUNCH("attention_decode");
+    if (a.splits > 1) {
+        attention_combine_kernel<<<dim3(a.nh, a.nrows), 64, 0, stream>>>(a);
+        JK_CHECK_LAUNCH("attention_combine");
+    }
+    return JK_OK;
+}
+
+// Scratch floats that `jk_attention_decode` needs for (nrows, nh, dh, splits).
+JK_EXPORT long long jk_attention_decode_scratch_floats(int nrows, int nh, int dh, int splits) {
+    if (splits <= 1) return 0;
+    return (long long)nrows * nh * splits * (dh + 2);
+}
+
+JK_EXPORT int jk_attention_decode(const void *q, const void *k_pages, const void *v_pages, void *out,
+                                  float *scratch, const int *rows, int nrows, const int *positions,
+                                  const int *row_req, const int *block_table, int max_blocks,
+                                  int page_size, int nh, int nkvh, int dh, float scale, int window,
+                                  int splits, cudaStream_t stream) {
+    if (nrows == 0) return JK_OK;
+    JK_REQUIRE(nrows > 0 && nh > 0 && nkvh > 0 && nh % nkvh == 0, "attention_decode: rows %d heads %d/%d", nrows, nh, nkvh);
+    JK_REQUIRE(dh % 8 == 0 && dh >= 8 && dh <= 256, "attention_decode: head size %d (takes multiples of 8 up to 256)", dh);
+    JK_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "attention_decode: page size %d, blocks %d, window %d",
+               page_size, max_blocks, window);
+    JK_REQUIRE(splits >= 1 && splits <= 256, "attention_decode: %d splits", splits);
+    JK_REQUIRE(splits == 1 || scratch != nullptr, "attention_decode: %d splits need scratch memory", splits);
+    JK_REQUIRE(nrows <= 65535, "attention_decode: %d rows exceed one launch", nrows);
+    DecodeArgs a{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_pages, (const __nv_bfloat16 *)v_pages,
+                 (__nv_bfloat16 *)out, scratch,
+                 scratch ? scratch + (size_t)nrows * nh * splits * dh : nullptr,
+                 rows, positions, row_req, block_table,
+                 nrows, nh, nkvh, dh, page_size, max_blocks, window, splits,
+                 scale * 1.4426950408889634f};
+    const int g = nh / nkvh;
+    const int lanes = dh / 8;
+#define DEC_DISPATCH_HG(LPR)                                         \
+    do {                                                             \
+        if (g == 1) return launch_decode<LPR, 1>(a, stream);         \
+        if (g == 2) return launch_decode<LPR, 2>(a, stream);         \
+        if (g == 3) return launch_decode<LPR, 3>(a, stream);         \
+        return launch_decode<LPR, 4>(a, stream);                     \
+    } while (0)
+    if (lanes <= 2) DEC_DISPATCH_HG(2);
+    if (lanes <= 4) DEC_DISPATCH_HG(4);
+    if (lanes <= 8) DEC_DISPATCH_HG(8);
+    if (lanes <= 16) DEC_DISPATCH_HG(16);
+    DEC_DISPATCH_HG(32);
+#undef DEC_DISPATCH_HG
+}
+
+// ---------------------------------------------------------------------------------------
+// Prefill kernel: for requests that bring many rows.  Work item = (tile of 64 query rows of
+// one request, query head); 4 warps of 16 rows.  Keys and values are gathered page by page
+// into shared memory with cp.async (two buffers), scores and weighted values run on the
+// tensor cores (mma.sync m16n8k16, bfloat16 in, float32 out), the softmax is the online one
+// in float32 registers.  Rows beyond the request's end repeat its last row and are not stored.
+// Shared rows are padded by 16 bytes, which makes every ldmatrix conflict-free for any head
+// size that is a multiple of 16.
+// ---------------------------------------------------------------------------------------
+struct PrefillArgs {
+    const __nv_bfloat16 *q;
+    const __nv_bfloat16 *k_pages;
+    const __nv_bfloat16 *v_pages;
+    __nv_bfloat16 *out;
+    const int *tiles;        // [ntiles][2]: batch entry, first row of the tile (row index in the step)
+    const int *req_start;    // [nreq + 1]
+    const int *req_pos;      // [nreq]
+    const int *block_table;  // [nreq, max_blocks]
+    int ntiles, nh, nkvh, page_size, max_blocks, window;
+    float scale_log2;
+};
+
+constexpr int PF_BM = 64;
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void *smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void *smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned *>(&v);
+}
+
+template <int DH, int BN>
+__global__ void __launch_bounds__(128)
+attention_prefill_kernel(PrefillArgs a) {
+    constexpr int STRIDE = DH + 8;            // elements per shared row
+    constexpr int CH = DH / 8;                // 16-byte chunks per row
+    extern __shared__ __align__(16) unsigned char pf_smem[];
+    __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(pf_smem);
+    __nv_bfloat16 *Ks = Qs + PF_BM * STRIDE;              // [2][BN][STRIDE]
+    __nv_bfloat16 *Vs = Ks + 2 * BN * STRIDE;             // [2][BN][STRIDE]
+
+    const int tile = a.ntiles - 1 - blockIdx.x;           // later tiles see more keys: start them first
+    const int h = blockIdx.y;
+    const int hk = h / (a.nh / a.nkvh);
+    const int r = a.tiles[2 * tile];
+    const int row0 = a.tiles[2 * tile + 1];
+    const int nrows = min(PF_BM, a.req_start[r + 1] - row0);
+    const int p0 = a.req_pos[r] + (row0 - a.req_start[r]);   // position of the tile's first row
+    const int p_last = p0 + nrows - 1;
+    const int lo = (a.window > 0 && p0 - a.window + 1 > 0) ? p0 - a.window + 1 : 0;
+    const int *bt = a.block_table + (size_t)r * a.max_blocks;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t page_stride = (size_t)a.nkvh * a.page_size * DH;
+    const size_t head_off = (size_t)hk * a.page_size * DH;
+
+    // the query tile
+    for (int c = tid; c < PF_BM * CH; c += 128) {
+        const int row = c / CH, ch = c - row * CH;
+        const int rr = min(row, nrows - 1);
+        cp_async16(Qs + row * STRIDE + ch * 8, a.q + ((size_t)(row0 + rr) * a.nh + h) * DH + ch * 8);
+    }
+    auto load_kv = [&](int kv0, int buf) {
+        __nv_bfloat16 *kd = Ks + buf * BN * STRIDE, *vd = Vs + buf * BN * STRIDE;
+        for (int c = tid; c < BN * CH; c += 128) {
+            const int row = c / CH, ch = c - row * CH;
+            const int key = kv0 + row;
+            if (key <= p_last) {
+                const size_t off = (size_t)bt[key / a.page_size] * page_stride + head_off +
+                                   (size_t)(key % a.page_size) * DH + ch * 8;
+                cp_async16(kd + row * STRIDE + ch * 8, a.k_pages + off);
+                cp_async16(vd + row * STRIDE + ch * 8, a.v_pages + off);
+            } else {
+                *reinterpret_cast<uint4 *>(kd + row * STRIDE + ch * 8) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4 *>(vd + row * STRIDE + ch * 8) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    const int kv_first = lo / BN * BN;
+    load_kv(kv_first, 0);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // query fragments stay in registers
+    unsigned qf[DH / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < DH / 16; ++kk)
+        ldmatrix_x4(qf[kk], Qs + (warp * 16 + (lane & 15)) * STRIDE + kk * 16 + (lane >> 4) * 8);
+
+    const int row_a = warp * 16 + (lane >> 2), row_b = row_a + 8;
+    const int pos_a = p0 + min(row_a, nrows - 1), pos_b = p0 + min(row_b, nrows - 1);
+    const int lo_a = a.window > 0 ? pos_a - a.window + 1 : 0, lo_b = a.window > 0 ? pos_b - a.window + 1 : 0;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    float o[DH / 8][4];
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+
+    int buf = 0;
+    for (int kv0 = kv_first; kv0 <= p_last; kv0 += BN, buf ^= 1) {
+        if (kv0 + BN <= p_last) load_kv(kv0 + BN, buf ^ 1);       // prefetch the next tile
+        cp_async_commit();
+
+        const __nv_bfloat16 *kt = Ks + buf * BN * STRIDE, *vt = Vs + buf * BN * STRIDE;
+        float s[BN / 8][4];
+#pragma unroll
+        for (int i = 0; i < BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+#pragma unroll
+            for (int n2 = 0; n2 < BN / 16; ++n2) {
+                unsigned b[4];
+                ldmatrix_x4(b, kt + (n2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * STRIDE + kk * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16(s[2 * n2], qf[kk], b[0], b[1]);
+                mma_bf16(s[2 * n2 + 1], qf[kk], b[2], b[3]);
+            }
+        }
+        // scale, mask, running maximum
+        const bool all_visible = (kv0 + BN - 1 <= p0) && (a.window == 0 || kv0 >= p_last - a.window + 1);
+        float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < BN / 8; ++i) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float v = s[i][c] * a.scale_log2;
+                if (!all_visible) {
+                    const int j = kv0 + i * 8 + 2 * (lane & 3) + (c & 1);
+                    const bool ok = c < 2 ? (j <= pos_a && j >= lo_a) : (j <= pos_b && j >= lo_b);
+                    if (!ok) v = -INFINITY;
+                }
+                s[i][c] = v;
+                if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+        const float use_a = mn_a == -INFINITY ? 0.f : mn_a, use_b = mn_b == -INFINITY ? 0.f : mn_b;
+        const float corr_a = exp2f(m_a - use_a), corr_b = exp2f(m_b - use_b);
+        m_a = mn_a; m_b = mn_b;
+        float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+        for (int i = 0; i < BN / 8; ++i) {
+            s[i][0] = exp2f(s[i][0] - use_a); s[i][1] = exp2f(s[i][1] - use_a);
+            s[i][2] = exp2f(s[i][2] - use_b); s[i][3] = exp2f(s[i][3] - use_b);
+            sum_a += s[i][0] + s[i][1]; sum_b += s[i][2] + s[i][3];
+        }
+        l_a = l_a * corr_a + sum_a; l_b = l_b * corr_b + sum_b;
+#pragma unroll
+        for (int i = 0; i < DH / 8; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
+        // weighted values
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks) {
+            unsigned p[4];
+            p[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+            p[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+            p[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+            p[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+            for (int d2 = 0; d2 < DH / 16; ++d2) {
+                unsigned b[4];
+                ldmatrix_x4_trans(b, vt + (ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * STRIDE + d2 * 16 + (lane >> 4) * 8);
+                mma_bf16(o[2 * d2], p, b[0], b[1]);
+                mma_bf16(o[2 * d2 + 1], p, b[2], b[3]);
+            }
+        }
+        cp_async_wait<0>();
+        __syncthreads();
+    }
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    const float inv_a = 1.f / l_a, inv_b = 1.f / l_b;
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) {
+        const int col = i * 8 + 2 * (lane & 3);
+        if (row_a < nrows)
+            *reinterpret_cast<__nv_bfloat162 *>(a.out + ((size_t)(row0 + row_a) * a.nh + h) * DH + col) =
+                __floats2bfloat162_rn(o[i][0] * inv_a, o[i][1] * inv_a);
+        if (row_b < nrows)
+            *reinterpret_cast<__nv_bfloat162 *>(a.out + ((size_t)(row0 + row_b) * a.nh + h) * DH + col) =
+                __floats2bfloat162_rn(o[i][2] * inv_b, o[i][3] * inv_b);
+    }
+}
+
+template <int DH, int BN>
+static int launch_prefill(const PrefillArgs &a, cudaStream_t stream) {
+    const size_t smem = (size_t)(PF_BM + 4 * BN) * (DH + 8) * sizeof(__nv_bfloat16);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DH, BN>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_prefill: %s", cudaGetErrorString(e));
+    }
+    attention_prefill_kernel<DH, BN><<<dim3(a.ntiles, a.nh), 128, smem, stream>>>(a);
+    JK_CHECK_LAUNCH("attention_prefill");
+    return JK_OK;
+}
+
+// Head sizes the tensor-core kernel is built for; others go to the row kernel.
+JK_EXPORT int jk_attention_prefill_supports(int dh) {
+    return dh == 16 || dh == 32 || dh == 48 || dh == 64 || dh == 80 || dh == 96 || dh == 128 || dh == 256;
+}
+
+JK_EXPORT int jk_attention_prefill(const void *q, const void *k_pages, const void *v_pages, void *out,
+                                   const int *tiles, int ntiles, const int *req_start, const int *req_pos,
+                                   const int *block_table, int max_blocks, int page_size, int nh, int nkvh,
+                                   int dh, float scale, int window, cudaStream_t stream) {
+    if (ntiles == 0) return JK_OK;
+    JK_REQUIRE(ntiles > 0 && nh > 0 && nkvh > 0 && nh % nkvh == 0, "attention_prefill: tiles %d heads %d/%d", ntiles, nh, nkvh);
+    JK_REQUIRE(nh <= 65535, "attention_prefill: %d heads exceed one launch", nh);
+    JK_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "attention_prefill: page size %d, blocks %d, window %d",
+               page_size, max_blocks, window);
+    PrefillArgs a{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_pages, (const __nv_bfloat16 *)v_pages,
+                  (__nv_bfloat16 *)out, tiles, req_start, req_pos, block_table,
+                  ntiles, nh, nkvh, page_size, max_blocks, window, scale * 1.4426950408889634f};
+    switch (dh) {
+        case 16: return launch_prefill<16, 64>(a, stream);
+        case 32: return launch_prefill<32, 64>(a, stream);
+        case 48: return launch_prefill<48, 64>(a, stream);
+        case 64: return launch_prefill<64, 64>(a, stream);
+        case 80: return launch_prefill<80, 64>(a, stream);
+        case 96: return launch_prefill<96, 64>(a, stream);
+        case 128: return launch_prefill<128, 64>(a, stream);
+        case 256: return launch_prefill<256, 32>(a, stream);
+        default: JK_FAIL(JK_UNSUPPORTED, "attention_prefill: head size %d has no tensor-core kernel", dh);
+    }
+}

@@ -20,7 +20,7 @@ import torch
 
 from ..cache import CacheManager, OutOfPages
 from ..config import read_config
-from ..parts import Model, Runtime, StepContext, cache_needs, model_manifest
+from ..parts import SHORT_ROWS, TILE_ROWS, Model, Runtime, StepContext, cache_needs, model_manifest
 from ..weights import FileWeights, check_manifest
 
 
@@ -54,6 +54,8 @@ class _Layout:
         self.req_start = o; o += _align(B + 1)
         self.req_pos = o; o += _align(B)
         self.slot_ids = o; o += _align(B)
+        self.short_rows = o; o += _align(T)
+        self.tiles = o; o += _align(2 * (T // TILE_ROWS + B))
         self.tables = []
         for _ in range(n_groups):
             self.tables.append(o); o += _align(B * max_blocks)
@@ -80,7 +82,7 @@ class Engine:
                                   spec.max_positions, dtype=dtype, device=self.device)
         self.max_requests = max_requests
         self.max_step_tokens = max_step_tokens
-        self.use_graphs = use_graphs
+        self.use_graphs = use_graphs and self.model.graph_safe
         n_groups, mb = len(self.cache.groups), self.cache.max_blocks
         cap = _Layout(max_step_tokens, max_requests, n_groups, mb).total
         self._meta_dev = torch.zeros(cap, dtype=torch.int32, device=self.device)
@@ -205,6 +207,17 @@ class Engine:
             host[lay.row_req + row] = i
             row += 1
             req_start.append(row)
+        short_rows: List[int] = []
+        tiles: List[int] = []
+        for i in range(nB):
+            r0, r1 = req_start[i], req_start[i + 1]
+            if r1 - r0 <= SHORT_ROWS:
+                short_rows.extend(range(r0, r1))
+            else:
+                for t0 in range(r0, r1, TILE_ROWS):
+                    tiles.extend((i, t0))
+        host[lay.short_rows: lay.short_rows + len(short_rows)] = short_rows
+        host[lay.tiles: lay.tiles + len(tiles)] = tiles
         n_want = len(want_rows)
         if pad_to:                       # a captured step computes logits for every row
             want_rows = list(range(nT))
@@ -226,6 +239,9 @@ class Engine:
         ctx.host_req_pos = list(starts) + [0] * (nB - B)
         ctx.host_slot_ids = list(slots) + [0] * (nB - B)
         ctx.n_want = n_want if not pad_to else nT
+        ctx.n_short, ctx.n_tiles = len(short_rows), len(tiles) // 2
+        ctx.short_rows = None if ctx.n_short == nT else self._meta_dev[lay.short_rows: lay.short_rows + ctx.n_short]
+        ctx.tiles = self._meta_dev[lay.tiles: lay.tiles + len(tiles)]
         return ctx
 
     def _context(self, lay: _Layout, n_want: int) -> StepContext:
@@ -252,13 +268,18 @@ class Engine:
         bucket = self._bucket(B)
         if bucket > self.max_requests:
             bucket = B
-        ctx = self._upload(entries, starts, B, B, pad_to=bucket)
-        ctx.decode_only = True
         rec = self._graphs.get(bucket)
         if rec is None:
-            # run once eagerly (library handles, lazy module loads), then capture
-            self.model.forward(ctx, self.cache.views)
+            # Warm up (library handles, lazy module loads) on a batch of padding rows only: they touch
+            # the null page and slot 0, so a mixer whose state update is not idempotent sees the real
+            # step exactly once, at the replay below.
+            dummy = self._upload([], [], 0, 0, pad_to=bucket)
+            dummy.decode_only = True
+            self.model.forward(dummy, self.cache.views)
             torch.cuda.synchronize()
+        ctx = self._upload(entries, starts, B, B, pad_to=bucket)
+        ctx.decode_only = True
+        if rec is None:
             from .. import kernels
             graph = torch.cuda.CUDAGraph()
             before = kernels.launch_count

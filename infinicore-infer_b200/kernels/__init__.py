@@ -194,6 +194,72 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
     return out
 
 
+def attention_decode_splits(nrows: int, nkvh: int, group: int, max_positions: int, sms: int = 148) -> int:
+    """How many ways the decode kernel cuts each row's key range: enough blocks to fill the GPU a few
+    times over, no split shorter than 64 keys at the longest context.  It depends on the batch's size
+    only (not on the lengths), so a captured step keeps its grid."""
+    blocks = max(1, nrows * nkvh * ((group + 3) // 4 if group > 4 else 1))
+    want = -(-4 * sms // blocks)
+    return max(1, min(want, 32, -(-max_positions // 64)))
+
+
+def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                     rows: Optional[torch.Tensor], nrows: int, positions: torch.Tensor, row_req: torch.Tensor,
+                     block_table: torch.Tensor, nh: int, scale: float, window: int, splits: int,
+                     scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bfloat16 attention of rows that bring few queries per request (decoded tokens, short portions):
+    the key range of every (row, key/value head) is cut into ``splits`` blocks whose partial results
+    a second kernel merges.  ``rows`` lists the rows to work on (None: rows 0..nrows-1)."""
+    for name, t in (("q", q), ("k_pages", k_pages), ("v_pages", v_pages), ("out", out)):
+        _need(t, name, torch.bfloat16)
+    _need(positions, "positions", torch.int32); _need(row_req, "row_req", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    _, nkvh, page_size, dh = k_pages.shape
+    lib = _build.load("attention")
+    lib.jk_attention_decode_scratch_floats.restype = ctypes.c_longlong
+    need = lib.jk_attention_decode_scratch_floats(_c_int(nrows), _c_int(nh), _c_int(dh), _c_int(splits))
+    if need and scratch is None:
+        scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    if need:
+        _need(scratch, "scratch", torch.float32)
+        if scratch.numel() < need:
+            raise KernelError(f"attention_decode: scratch holds {scratch.numel()} floats, {need} needed")
+    _check("attention", lib.jk_attention_decode(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch if need else None), _ptr(rows), _c_int(nrows),
+        _ptr(positions), _ptr(row_req), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size),
+        _c_int(nh), _c_int(nkvh), _c_int(dh), _c_float(scale), _c_int(window or 0), _c_int(splits), _stream()))
+    if need and splits > 1:
+        global launch_count
+        launch_count += 1          # the merge kernel
+    return out
+
+
+def attention_prefill_supports(dh: int) -> bool:
+    return bool(_build.load("attention").jk_attention_prefill_supports(_c_int(dh)))
+
+
+def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                      tiles: torch.Tensor, ntiles: int, req_start: torch.Tensor, req_pos: torch.Tensor,
+                      block_table: torch.Tensor, nh: int, scale: float, window: int = 0) -> torch.Tensor:
+    """bfloat16 tensor-core attention of requests that bring many rows: ``tiles[i] = (batch entry, first
+    row)`` names 64-row tiles of query rows."""
+    for name, t in (("q", q), ("k_pages", k_pages), ("v_pages", v_pages), ("out", out)):
+        _need(t, name, torch.bfloat16)
+    for name, t in (("tiles", tiles), ("req_start", req_start), ("req_pos", req_pos), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    _, nkvh, page_size, dh = k_pages.shape
+    if tiles.numel() < 2 * ntiles:
+        raise KernelError("attention_prefill: the tile list is shorter than ntiles")
+    lib = _build.load("attention")
+    _check("attention", lib.jk_attention_prefill(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), _c_int(ntiles), _ptr(req_start), _ptr(req_pos),
+        _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size), _c_int(nh), _c_int(nkvh), _c_int(dh),
+        _c_float(scale), _c_int(window or 0), _stream()))
+    return out
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     _need(logits, "logits", torch.float32, contiguous=False); _need(out, "out", torch.int32)
     n, v = logits.shape

@@ -63,6 +63,28 @@ class Attention:
                         pos.interleaved if pos else False, q, view.k_pages, view.v_pages,
                         T, s.num_heads, s.num_kv_heads, s.head_dim, write_cache=writes_cache)
         o = rt.empty(T, s.num_heads * s.head_dim)
-        kernels.attention_rows(q, view.k_pages, view.v_pages, o, ctx.positions, ctx.row_req, table, T,
-                               s.num_heads, s.softmax_scale, s.window or 0)
+        self._attend(q, o, view, table, ctx)
         return rt.linear(o, self.w_o, out_dtype=torch.float32)
+
+    def _attend(self, q, o, view, table, ctx) -> None:
+        """float32: one warp per (row, head), the same arithmetic whatever the batch.  bfloat16: rows of
+        requests with few rows go to the split-key decode kernel, 64-row tiles of the others to the
+        tensor-core kernel; head sizes that kernel is not built for take the row kernel."""
+        from .. import kernels
+        s, T = self.spec, ctx.ntok
+        fast = (self.runtime.dtype == torch.bfloat16 and not self.runtime.plain_attention
+                and (ctx.n_short or ctx.n_tiles) and s.head_dim % 8 == 0 and s.head_dim <= 256)
+        if fast and ctx.n_tiles and not kernels.attention_prefill_supports(s.head_dim):
+            fast = False
+        if not fast:
+            kernels.attention_rows(q, view.k_pages, view.v_pages, o, ctx.positions, ctx.row_req, table, T,
+                                   s.num_heads, s.softmax_scale, s.window or 0)
+            return
+        if ctx.n_tiles:
+            kernels.attention_prefill(q, view.k_pages, view.v_pages, o, ctx.tiles, ctx.n_tiles, ctx.req_start,
+                                      ctx.req_pos, table, s.num_heads, s.softmax_scale, s.window or 0)
+        if ctx.n_short:
+            splits = kernels.attention_decode_splits(ctx.n_short, s.num_kv_heads, s.num_heads // s.num_kv_heads,
+                                                     s.window or (s.position.max_positions if s.position else 1 << 20))
+            kernels.attention_decode(q, view.k_pages, view.v_pages, o, ctx.short_rows, ctx.n_short, ctx.positions,
+                                     ctx.row_req, table, s.num_heads, s.softmax_scale, s.window or 0, splits)

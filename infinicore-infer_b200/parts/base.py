@@ -64,6 +64,7 @@ class Runtime:
             raise ValueError(f"the engine runs in float32 or bfloat16, not {dtype}")
         self.dtype = dtype
         self.device = torch.device(device)
+        self.plain_attention = False      # True: bfloat16 attention through the row kernel too
 
     def empty(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
@@ -85,6 +86,10 @@ class Runtime:
         return out
 
 
+SHORT_ROWS = 8      # a request with at most this many rows in a step counts as "few rows"
+TILE_ROWS = 64      # rows per tile of the others
+
+
 @dataclass
 class StepContext:
     """One step's batch, as the parts see it.
@@ -104,6 +109,12 @@ class StepContext:
     block_tables: List[torch.Tensor]  # per cache group: int32 [nreq, max_blocks]
     want_rows: torch.Tensor         # int32 [n_want] rows whose logits are wanted
     n_want: int
+    # Work lists for mixers that treat few-row and many-row requests differently: the rows of
+    # requests that bring at most SHORT_ROWS rows, and 64-row tiles (batch entry, first row) of the rest.
+    short_rows: Optional[torch.Tensor] = None     # int32 [n_short]; None means rows 0..n_short-1
+    n_short: int = 0
+    tiles: Optional[torch.Tensor] = None          # int32 [n_tiles, 2]
+    n_tiles: int = 0
     host_req_start: List[int] = field(default_factory=list)
     host_req_pos: List[int] = field(default_factory=list)
     host_slot_ids: List[int] = field(default_factory=list)

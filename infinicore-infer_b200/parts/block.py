@@ -35,6 +35,12 @@ class PreNormBlock:
         self.ffn_norm = build("norm", spec.ffn_norm, spec.ffn_norm_prefix)
         self.feed_forward = build("feed_forward", spec.feed_forward, spec.ffn_prefix)
 
+    @property
+    def graph_safe(self) -> bool:
+        """False if a part reads the step's host-side lists: its work cannot be replayed from a graph."""
+        parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+        return all(getattr(p, "graph_safe", True) for p in parts)
+
     def weight_bytes(self) -> int:
         """Bytes of weights one pass over this block reads."""
         parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)

@@ -59,11 +59,15 @@ class Model:
         self.layers = [part_class("block", layer)(layer, weights, spec.layer_prefix.format(i), runtime)
                        for i, layer in enumerate(spec.layers)]
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(layer, "graph_safe", True) for layer in self.layers)
+
     def weight_bytes_per_step(self) -> int:
         """Bytes of weights one decode step reads: every matrix of every run entry, the output matrix."""
         total = self.lm_head.numel() * self.lm_head.element_size()
         for e in self.spec.order:
-            total += self.layers[e.layer].weight_bytes()
+            total += getattr(self.layers[e.layer], "weight_bytes", lambda: 0)()
         return total
 
     def forward(self, ctx: StepContext, views) -> torch.Tensor:

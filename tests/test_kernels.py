@@ -163,8 +163,10 @@ def test_rope_and_cache_write(K, dtype, nh, nkvh, dh, page, interleaved):
     assert float(kp[0].abs().max()) == 0.0              # the null page was not written
 
 
-def _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, plant=None, seed=0):
-    """lens: cached length of each request; queries: per request the positions that are rows."""
+def _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, plant=None, seed=0, impl="rows", splits=1):
+    """lens: cached length of each request; queries: per request the positions that are rows.
+    impl: "rows" (one warp per row and head), "decode" (split keys), "prefill" (tensor cores; the
+    positions of a request must be consecutive)."""
     g = torch.Generator().manual_seed(seed)
     R = len(lens)
     k = [torch.randn(n, nkvh, dh, generator=g) for n in lens]
@@ -185,19 +187,38 @@ def _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, plant=N
     row_req = torch.tensor([r for r in range(R) for _ in queries[r]], dtype=torch.int32)
     q = torch.stack([qf[r][p] for r in range(R) for p in queries[r]]).to(dtype)
     T = q.shape[0]
-    out = torch.empty(T, nh * dh, dtype=dtype, device=DEV)
+    out = torch.full((T, nh * dh), 55.0, dtype=dtype, device=DEV)
     scale = dh ** -0.5
-    K.attention_rows(q.view(T, nh * dh).to(DEV), kp.to(DEV), vp.to(DEV), out, positions.to(DEV),
-                     row_req.to(DEV), perm.to(torch.int32).to(DEV), T, nh, scale, window or 0)
+    bt = perm.to(torch.int32).to(DEV)
+    qd, kd, vd = q.view(T, nh * dh).to(DEV), kp.to(DEV), vp.to(DEV)
+    if impl == "rows":
+        K.attention_rows(qd, kd, vd, out, positions.to(DEV), row_req.to(DEV), bt, T, nh, scale, window or 0)
+    elif impl == "decode":
+        # work on a shuffled list of all rows, to show that the list is honoured
+        rows = torch.randperm(T, generator=g).to(torch.int32).to(DEV)
+        K.attention_decode(qd, kd, vd, out, rows, T, positions.to(DEV), row_req.to(DEV), bt, nh, scale,
+                           window or 0, splits)
+    else:
+        starts = [0]
+        for r in range(R):
+            assert list(queries[r]) == list(range(queries[r][0], queries[r][0] + len(queries[r]))) if len(queries[r]) else True
+            starts.append(starts[-1] + len(queries[r]))
+        tiles = [(r, t0) for r in range(R) for t0 in range(starts[r], starts[r + 1], 64)]
+        req_pos = [queries[r][0] if len(queries[r]) else 0 for r in range(R)]
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        K.attention_prefill(qd, kd, vd, out, i32(tiles).flatten(), len(tiles), i32(starts), i32(req_pos), bt, nh,
+                            scale, window or 0)
     want = torch.cat([plain_attention(qf[r].double(), k[r].double(), v[r].double(), scale, window)[queries[r]]
                       for r in range(R) if len(queries[r])])
     return out.view(T, nh, dh), want, v
 
 
+SHAPES = [(4, 4, 16, 16, None), (3, 1, 32, 8, None), (6, 2, 48, 4, None), (8, 2, 128, 16, None),
+          (5, 5, 64, 16, 7), (2, 1, 80, 32, 33), (2, 2, 256, 16, None), (16, 1, 64, 16, None), (10, 2, 96, 5, 70)]
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nh,nkvh,dh,page,window", [
-    (4, 4, 16, 16, None), (3, 1, 32, 8, None), (6, 2, 48, 4, None), (8, 2, 128, 16, None),
-    (5, 5, 64, 16, 7), (2, 1, 80, 32, 33), (2, 2, 256, 16, None)])
+@pytest.mark.parametrize("nh,nkvh,dh,page,window", SHAPES[:7])
 def test_attention_rows_over_pages(K, dtype, nh, nkvh, dh, page, window):
     lens = [37, 1, 130, 64]
     # a portion at the end, a single first token, decoded tokens, a whole prompt cut at page edges
@@ -206,24 +227,51 @@ def test_attention_rows_over_pages(K, dtype, nh, nkvh, dh, page, window):
     _close(got, want, dtype, scale=2.0)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("splits", [1, 2, 5, 32])
+@pytest.mark.parametrize("nh,nkvh,dh,page,window", SHAPES)
+def test_attention_decode_kernel_with_split_keys(K, nh, nkvh, dh, page, window, splits):
+    lens = [37, 1, 300, 64, 2]
+    queries = [list(range(30, 37)), [0], [299], [62, 63], [0, 1]]
+    got, want, _ = _attention_case(K, torch.bfloat16, nh, nkvh, dh, page, window, lens, queries, seed=dh,
+                                   impl="decode", splits=splits)
+    _close(got, want, torch.bfloat16, scale=2.0)
+
+
+@pytest.mark.parametrize("nh,nkvh,dh,page,window", [s for s in SHAPES if s[2] != 256] + [(2, 2, 256, 16, None), (4, 2, 64, 16, 100)])
+def test_attention_prefill_kernel_on_tensor_cores(K, nh, nkvh, dh, page, window):
+    # a whole prompt of several tiles with a ragged end; a portion that starts mid-page far into the
+    # context; a portion of exactly one tile; a short one
+    lens = [150, 333, 64, 40]
+    queries = [list(range(0, 150)), list(range(203, 333)), list(range(0, 64)), list(range(31, 40))]
+    got, want, _ = _attention_case(K, torch.bfloat16, nh, nkvh, dh, page, window, lens, queries, seed=dh, impl="prefill")
+    _close(got, want, torch.bfloat16, scale=2.0)
+
+
+@pytest.mark.parametrize("impl,dtype", [("rows", torch.float32), ("rows", torch.bfloat16), ("decode", torch.bfloat16),
+                                         ("prefill", torch.bfloat16)])
 @pytest.mark.parametrize("window", [None, 50])
-def test_attention_finds_one_far_key_among_hundreds(K, dtype, window):
+def test_attention_finds_one_far_key_among_hundreds(K, impl, dtype, window):
     nh, nkvh, dh, page = 4, 2, 64, 16
     lens = [700]
-    # query at 699 must find key 3 (full) / key 650 = the window's far edge; query at 320 finds key 319 - a page edge
+    # the query at 699 must find key 3 (or, with a window, the key at the window's far edge); the query
+    # at 320 the key at 319, across a page's edge
     far = 3 if window is None else 699 - window + 1
-    plant = [(0, 699, far, 1), (0, 320, 319, 2), (0, 512, 511 if window else 0, 3)]
-    got, want, v = _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, [[320, 512, 699]], plant, seed=5)
+    plant = [(0, 699, far, 1), (0, 320, 319, 2)]
+    if impl == "prefill":
+        queries, i699, i320 = [list(range(300, 700))], 399, 20
+    else:
+        queries, i699, i320 = [[320, 512, 699]], 2, 0
+    kw = dict(impl=impl, splits=3) if impl != "rows" else {}
+    got, want, v = _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, plant, seed=5, **kw)
     _close(got, want, dtype, scale=2.0)
-    assert torch.allclose(got[2, 1].float().cpu(), v[0][far, 0], atol=2e-2)
-    assert torch.allclose(got[0, 2].float().cpu(), v[0][319, 1], atol=2e-2)
+    assert torch.allclose(got[i699, 1].float().cpu(), v[0][far, 0], atol=2e-2)
+    assert torch.allclose(got[i320, 2].float().cpu(), v[0][319, 1], atol=2e-2)
     if window:
         # one position beyond the window's edge must NOT be seen
         plant = [(0, 699, far - 1, 1)]
-        got, want, v = _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, [[699]], plant, seed=5)
+        got, want, v = _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, plant, seed=5, **kw)
         _close(got, want, dtype, scale=2.0)
-        assert not torch.allclose(got[0, 1].float().cpu(), v[0][far - 1, 0], atol=0.2)
+        assert not torch.allclose(got[i699, 1].float().cpu(), v[0][far - 1, 0], atol=0.2)
 
 
 @pytest.mark.parametrize("V", [5, 301, 122753])

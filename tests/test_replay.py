@@ -77,8 +77,11 @@ def test_whole_tail_and_portions_agree_with_the_plain_implementation(tiny_models
             got = run(eng, steps)
             check(got, "r", want, TOL[dtype], f"{name} {dtype} {what} n={n}")
             results[what] = np.stack([got[("r", p)] for p in range(n)])
-        # the ways of cutting agree with one another far more closely than with the plain implementation
-        cut_tol = 1e-5 if dtype == "float32" else 1e-2
+        # The ways of cutting agree with one another.  float32: every kernel adds in the same order
+        # whatever the batch, so they agree to the last bits.  bfloat16: a portion runs on the
+        # tensor-core tile kernel and a decoded token on the split-key kernel, two evaluations that
+        # round independently, so they agree as well as each agrees with the plain implementation.
+        cut_tol = 1e-5 if dtype == "float32" else TOL[dtype]
         for what in ("tail", "portions"):
             assert np.abs(results[what] - results["whole"]).max() <= cut_tol * np.abs(want).max(), (name, dtype, what, n)
         assert not eng.cache.lengths and all(g.pool.in_use == 0 for g in eng.cache.groups)
