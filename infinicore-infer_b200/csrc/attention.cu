@@ -174,14 +174,28 @@ struct DecodeArgs {
     const int *positions;
     const int *row_req;
     const int *block_table;
-    int nrows, nh, nkvh, dh, page_size, max_blocks, window, splits;
+    int nrows, nh, nkvh, dh, page_size, max_blocks, window, splits, page_shift;
     float scale_log2;              // softmax scale * log2(e)
 };
 
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_UNROLL = 4;      // keys a group has in flight
 
-template <int LPR, int HG>         // lanes per key row, query heads per block
+__device__ __forceinline__ float fast_exp2(float x) {     // 2^x to 22 bits; 2^-inf = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void bf16x8_to_float(const uint4 &raw, float (&f)[8]) {
+    const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        f[2 * e] = __uint_as_float(w[e] << 16);
+        f[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+    }
+}
+
+template <int LPR, int HG, bool POW2>   // lanes per key row, query heads per block, page size a power of two
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_kernel(DecodeArgs a) {
     constexpr int GROUPS = DEC_WARPS * 32 / LPR;
@@ -234,7 +248,8 @@ attention_decode_kernel(DecodeArgs a) {
     }
 
     // The trip count is the same for every thread of the block and no thread skips a shuffle:
-    // a key beyond the range scores -inf and so weighs exactly zero.
+    // a key beyond the range scores -inf and so weighs exactly zero.  DEC_UNROLL keys are in flight
+    // per group and share one update of the running maximum.
     for (int base = k_begin; base < k_end; base += GROUPS * DEC_UNROLL) {
         uint4 kr[DEC_UNROLL], vr[DEC_UNROLL];
         bool ok[DEC_UNROLL];
@@ -244,40 +259,55 @@ attention_decode_kernel(DecodeArgs a) {
             ok[u] = j < k_end;
             kr[u] = make_uint4(0, 0, 0, 0); vr[u] = make_uint4(0, 0, 0, 0);
             if (ok[u] && lane_ok) {
-                const size_t off = (size_t)bt[j / a.page_size] * page_stride + head_off + (size_t)(j % a.page_size) * dh;
+                const int blk = POW2 ? (j >> a.page_shift) : (j / a.page_size);
+                const int in_page = POW2 ? (j & (a.page_size - 1)) : (j - blk * a.page_size);
+                const size_t off = (size_t)bt[blk] * page_stride + head_off + (size_t)in_page * dh;
                 kr[u] = *reinterpret_cast<const uint4 *>(a.k_pages + off);
                 vr[u] = *reinterpret_cast<const uint4 *>(a.v_pages + off);
             }
         }
+        float sc[HG][DEC_UNROLL];
 #pragma unroll
         for (int u = 0; u < DEC_UNROLL; ++u) {
-            float kf[8], vf[8];
-            {
-                const __nv_bfloat162 *k2 = reinterpret_cast<const __nv_bfloat162 *>(&kr[u]);
-                const __nv_bfloat162 *v2 = reinterpret_cast<const __nv_bfloat162 *>(&vr[u]);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 fk = __bfloat1622float2(k2[e]), fv = __bfloat1622float2(v2[e]);
-                    kf[2 * e] = fk.x; kf[2 * e + 1] = fk.y; vf[2 * e] = fv.x; vf[2 * e + 1] = fv.y;
-                }
-            }
+            float kf[8];
+            bf16x8_to_float(kr[u], kf);
 #pragma unroll
             for (int hh = 0; hh < HG; ++hh) {
                 float s = 0.f;
 #pragma unroll
                 for (int e = 0; e < 8; ++e) s = fmaf(qf[hh][e], kf[e], s);
-#pragma unroll
-                for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (!ok[u]) s = -INFINITY;
-                const float m_new = fmaxf(m[hh], s);
-                const float m_use = m_new == -INFINITY ? 0.f : m_new;
-                const float corr = exp2f(m[hh] - m_use);
-                const float p = exp2f(s - m_use);
-                l[hh] = l[hh] * corr + p;
-                m[hh] = m_new;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) acc[hh][e] = fmaf(p, vf[e], acc[hh][e] * corr);
+                sc[hh][u] = s;
             }
+        }
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) {
+#pragma unroll
+            for (int u = 0; u < DEC_UNROLL; ++u) {
+#pragma unroll
+                for (int o = LPR / 2; o > 0; o >>= 1) sc[hh][u] += __shfl_xor_sync(0xffffffffu, sc[hh][u], o);
+                if (!ok[u]) sc[hh][u] = -INFINITY;
+            }
+            float m_new = m[hh];
+#pragma unroll
+            for (int u = 0; u < DEC_UNROLL; ++u) m_new = fmaxf(m_new, sc[hh][u]);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float corr = fast_exp2(m[hh] - m_use);
+            m[hh] = m_new;
+            float psum = 0.f;
+#pragma unroll
+            for (int u = 0; u < DEC_UNROLL; ++u) { sc[hh][u] = fast_exp2(sc[hh][u] - m_use); psum += sc[hh][u]; }
+            l[hh] = l[hh] * corr + psum;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[hh][e] *= corr;
+        }
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) {
+            float vf[8];
+            bf16x8_to_float(vr[u], vf);
+#pragma unroll
+            for (int hh = 0; hh < HG; ++hh)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[hh][e] = fmaf(sc[hh][u], vf[e], acc[hh][e]);
         }
     }
 
@@ -339,7 +369,7 @@ __global__ void attention_combine_kernel(DecodeArgs a) {
     }
 }
 
-template <int LPR, int HG>
+template <int LPR, int HG, bool POW2>
 static int launch_decode(const DecodeArgs &a, cudaStream_t stream) {
     constexpr int GROUPS = DEC_WARPS * 32 / LPR;
     const int g = a.nh / a.nkvh;
@@ -347,11 +377,11 @@ static int launch_decode(const DecodeArgs &a, cudaStream_t stream) {
     dim3 grid(a.splits, a.nkvh * hgroups, a.nrows);
     const size_t smem = (size_t)GROUPS * HG * (2 + LPR * 8) * sizeof(float);
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<LPR, HG>,
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<LPR, HG, POW2>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_decode: %s", cudaGetErrorString(e));
     }
-    attention_decode_kernel<LPR, HG><<<grid, DEC_WARPS * 32, smem, stream>>>(a);
+    attention_decode_kernel<LPR, HG, POW2><<<grid, DEC_WARPS * 32, smem, stream>>>(a);
     JK_CHECK_LAUNCH("attention_decode");
     if (a.splits > 1) {
         attention_combine_kernel<<<dim3(a.nh, a.nrows), 64, 0, stream>>>(a);
@@ -383,16 +413,19 @@ JK_EXPORT int jk_attention_decode(const void *q, const void *k_pages, const void
                  (__nv_bfloat16 *)out, scratch,
                  scratch ? scratch + (size_t)nrows * nh * splits * dh : nullptr,
                  rows, positions, row_req, block_table,
-                 nrows, nh, nkvh, dh, page_size, max_blocks, window, splits,
+                 nrows, nh, nkvh, dh, page_size, max_blocks, window, splits, 0,
                  scale * 1.4426950408889634f};
+    const bool pow2 = (page_size & (page_size - 1)) == 0;
+    while ((1 << a.page_shift) < page_size) ++a.page_shift;
     const int g = nh / nkvh;
     const int lanes = dh / 8;
+#define DEC_DISPATCH_P2(LPR, HG) return pow2 ? launch_decode<LPR, HG, true>(a, stream) : launch_decode<LPR, HG, false>(a, stream)
 #define DEC_DISPATCH_HG(LPR)                                         \
     do {                                                             \
-        if (g == 1) return launch_decode<LPR, 1>(a, stream);         \
-        if (g == 2) return launch_decode<LPR, 2>(a, stream);         \
-        if (g == 3) return launch_decode<LPR, 3>(a, stream);         \
-        return launch_decode<LPR, 4>(a, stream);                     \
+        if (g == 1) DEC_DISPATCH_P2(LPR, 1);                         \
+        if (g == 2) DEC_DISPATCH_P2(LPR, 2);                         \
+        if (g == 3) DEC_DISPATCH_P2(LPR, 3);                         \
+        DEC_DISPATCH_P2(LPR, 4);                                     \
     } while (0)
     if (lanes <= 2) DEC_DISPATCH_HG(2);
     if (lanes <= 4) DEC_DISPATCH_HG(4);
@@ -400,6 +433,7 @@ JK_EXPORT int jk_attention_decode(const void *q, const void *k_pages, const void
     if (lanes <= 16) DEC_DISPATCH_HG(16);
     DEC_DISPATCH_HG(32);
 #undef DEC_DISPATCH_HG
+#undef DEC_DISPATCH_P2
 }
 
 // ---------------------------------------------------------------------------------------

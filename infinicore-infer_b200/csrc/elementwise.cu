@@ -189,11 +189,13 @@ struct RopeKvArgs {
     void *q_out;
     void *k_pages;
     void *v_pages;
-    int ld_qkv, nh, nkvh, dh, page_size, max_blocks, interleaved, write_cache;
+    int ld_qkv, nh, nkvh, dh, page_size, max_blocks, interleaved, write_cache, heads_per_block;
 };
 
 template <typename TI, typename TO>
 __global__ void rope_kv_kernel(RopeKvArgs a) {
+    // blockIdx.x: token row; blockIdx.y: a chunk of `heads_per_block` heads out of the row's
+    // nh query heads, nkvh key heads and nkvh value heads (in that order)
     const int t = blockIdx.x;
     const int pos = a.positions[t];
     const int half = a.dh / 2;
@@ -206,38 +208,28 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
         slot = ((size_t)page * a.nkvh * a.page_size + (pos % a.page_size)) * a.dh;
     }
     const size_t head_stride = (size_t)a.page_size * a.dh;
-    // rotated heads: queries, then keys
-    const int nrot = a.write_cache ? (a.nh + a.nkvh) : a.nh;
-    for (int i = threadIdx.x; i < nrot * half; i += blockDim.x) {
-        const int h = i / half, j = i - h * half;
-        const int e0 = a.interleaved ? 2 * j : j;
-        const int e1 = a.interleaved ? 2 * j + 1 : j + half;
+    const int total_heads = a.write_cache ? a.nh + 2 * a.nkvh : a.nh;
+    const int h_begin = blockIdx.y * a.heads_per_block;
+    const int h_end = min(total_heads, h_begin + a.heads_per_block);
+    for (int i = threadIdx.x; i < (h_end - h_begin) * half; i += blockDim.x) {
+        const int h = h_begin + i / half, j = i % half;
+        const bool rotated = h < a.nh + a.nkvh;             // value heads are copied as they are
+        const int e0 = (a.interleaved && rotated) ? 2 * j : j;
+        const int e1 = (a.interleaved && rotated) ? 2 * j + 1 : j + half;
         float x0 = to_f32(src[h * a.dh + e0]), x1 = to_f32(src[h * a.dh + e1]);
         if (a.bias) { x0 += a.bias[h * a.dh + e0]; x1 += a.bias[h * a.dh + e1]; }
         float y0 = x0, y1 = x1;
-        if (cs) {
+        if (cs && rotated) {
             const float c = cs[j], s = sn[j];
             y0 = x0 * c - x1 * s;
             y1 = x0 * s + x1 * c;
         }
-        if (h < a.nh) {
-            TO *q = (TO *)a.q_out + ((size_t)t * a.nh + h) * a.dh;
-            q[e0] = from_f32<TO>(y0);
-            q[e1] = from_f32<TO>(y1);
-        } else {
-            TO *k = (TO *)a.k_pages + slot + (size_t)(h - a.nh) * head_stride;
-            k[e0] = from_f32<TO>(y0);
-            k[e1] = from_f32<TO>(y1);
-        }
-    }
-    if (a.write_cache) {
-        const int vbase = (a.nh + a.nkvh) * a.dh;
-        for (int i = threadIdx.x; i < a.nkvh * a.dh; i += blockDim.x) {
-            const int h = i / a.dh, e = i - h * a.dh;
-            float v = to_f32(src[vbase + i]);
-            if (a.bias) v += a.bias[vbase + i];
-            ((TO *)a.v_pages)[slot + (size_t)h * head_stride + e] = from_f32<TO>(v);
-        }
+        TO *dst;
+        if (h < a.nh) dst = (TO *)a.q_out + ((size_t)t * a.nh + h) * a.dh;
+        else if (h < a.nh + a.nkvh) dst = (TO *)a.k_pages + slot + (size_t)(h - a.nh) * head_stride;
+        else dst = (TO *)a.v_pages + slot + (size_t)(h - a.nh - a.nkvh) * head_stride;
+        dst[e0] = from_f32<TO>(y0);
+        dst[e1] = from_f32<TO>(y1);
     }
 }
 
@@ -254,15 +246,22 @@ JK_EXPORT int jk_rope_kv(const void *qkv, int in_dtype, int ld_qkv, const float 
                "rope_kv: cache write asked for without pages");
     JK_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "rope_kv: one of cos/sin is null");
     RopeKvArgs a{qkv, bias, positions, row_req, block_table, cos_table, sin_table, q_out, k_pages,
-                 v_pages, ld_qkv, nh, nkvh, dh, page_size, max_blocks, interleaved, write_cache};
-    const int work = (nh + nkvh) * dh / 2;
+                 v_pages, ld_qkv, nh, nkvh, dh, page_size, max_blocks, interleaved, write_cache, 0};
+    // few rows: cut each row's heads over several blocks so that the GPU is not left to ntok blocks
+    const int total_heads = write_cache ? nh + 2 * nkvh : nh;
+    int chunks = 1;
+    while (ntok * chunks < 296 && chunks * 2 <= total_heads) chunks *= 2;
+    a.heads_per_block = (total_heads + chunks - 1) / chunks;
+    const dim3 grid(ntok, (total_heads + a.heads_per_block - 1) / a.heads_per_block);
+    JK_REQUIRE(grid.y <= 65535, "rope_kv: too many head chunks");
+    const int work = a.heads_per_block * dh / 2;
     const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
     if (in_dtype == JK_F32 && out_dtype == JK_F32)
-        rope_kv_kernel<float, float><<<ntok, threads, 0, stream>>>(a);
+        rope_kv_kernel<float, float><<<grid, threads, 0, stream>>>(a);
     else if (in_dtype == JK_F32 && out_dtype == JK_BF16)
-        rope_kv_kernel<float, __nv_bfloat16><<<ntok, threads, 0, stream>>>(a);
+        rope_kv_kernel<float, __nv_bfloat16><<<grid, threads, 0, stream>>>(a);
     else if (in_dtype == JK_BF16 && out_dtype == JK_BF16)
-        rope_kv_kernel<__nv_bfloat16, __nv_bfloat16><<<ntok, threads, 0, stream>>>(a);
+        rope_kv_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, 0, stream>>>(a);
     else
         JK_FAIL(JK_UNSUPPORTED, "rope_kv: dtypes %d -> %d", in_dtype, out_dtype);
     JK_CHECK_LAUNCH("rope_kv");

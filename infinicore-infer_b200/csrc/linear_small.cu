@@ -1,0 +1,204 @@
+// Matrix products for steps of few rows (decoding): out[M, N] = act[M, K] * W[N, K]^T, M <= 16.
+//
+// With so few rows the product is a stream of weights: every byte of W is read once and used
+// for M multiply-adds, so the kernel is built around the loads.  The roles of the tensor-core
+// operands are swapped: 16 rows of W (16 output features) are the A operand of
+// mma.sync.m16n8k16 and up to 8 rows of activations are the B operand.  Because a dot product
+// does not care in which order its terms are added, the k index is permuted so that every
+// thread's operand registers come straight out of ONE 16-byte load: thread (g, t) of a warp
+// loads W[n0 + g][k0 + 8t .. k0 + 8t + 7] and W[n0 + g + 8][same], and the activations are laid
+// out in shared memory as [k / 8][row][8] so that its B registers are one conflict-free 16-byte
+// load as well.  No shuffle, no ldmatrix, no staging of weights in shared memory.
+//
+// A block's 8 warps are split into (tiles of 16 features) x (slices of K); the slices' partial
+// sums meet in shared memory and the first slice's warp runs the epilogue:
+//   EPI_F32     out[m, n] = acc                       (float32; the residual add and the next
+//                                                      norm are the consumer's)
+//   EPI_SWIGLU  out[m, n] = silu(gate) * up           (bfloat16; the warp computes features n
+//                                                      and N + n of a [2N, K] matrix together)
+// The library is asked for the same products when M is larger (the reference sends all of its
+// products to a library: src/models/inference_context.cpp:59-79).
+#include "common.cuh"
+
+JK_DEFINE_ERROR_BUFFER(jk_linear_small)
+
+enum { EPI_F32 = 0, EPI_SWIGLU = 1 };
+
+struct SmallLinearArgs {
+    const __nv_bfloat16 *act;   // [M, K]
+    const __nv_bfloat16 *w;     // [N, K]  (EPI_SWIGLU: [2N, K], gate rows then up rows)
+    void *out;                  // EPI_F32: float [M, ldo]; EPI_SWIGLU: bfloat16 [M, ldo]
+    int M, N, K, ldo, ksplit, n_units;
+};
+
+constexpr int SL_WARPS = 8;
+constexpr int SL_UNROLL = 4;    // 32-wide k blocks in flight per warp
+
+__device__ __forceinline__ uint4 ld_stream(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int MT, int EPI>      // MT: tiles of 8 activation rows (1 or 2)
+__global__ void __launch_bounds__(SL_WARPS * 32)
+small_linear_kernel(SmallLinearArgs a) {
+    constexpr int NW = EPI == EPI_SWIGLU ? 2 : 1;          // weight tiles a warp streams together
+    extern __shared__ __align__(16) unsigned char sl_smem[];
+    uint4 *act_s = reinterpret_cast<uint4 *>(sl_smem);                    // [K / 8][MT * 8] units of 8 bf16
+    float *red_s = reinterpret_cast<float *>(sl_smem + (size_t)(a.K / 8) * MT * 8 * 16);   // [SL_WARPS][NW][MT][4][32]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+
+    // activations into shared memory, [k / 8][row][8]; rows beyond M are zero
+    const int units = a.K / 8;
+    for (int i = threadIdx.x; i < units * MT * 8; i += blockDim.x) {
+        const int kb = i / (MT * 8), row = i - kb * (MT * 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < a.M) v = *reinterpret_cast<const uint4 *>(a.act + (size_t)row * a.K + kb * 8);
+        act_s[i] = v;
+    }
+    __syncthreads();
+
+    const int tiles_per_unit = SL_WARPS / a.ksplit;
+    const int tile_in_unit = warp / a.ksplit, kslice = warp - tile_in_unit * a.ksplit;
+    const int kblocks = a.K / 32;
+    const int per_slice = (kblocks + a.ksplit - 1) / a.ksplit;
+    const int kb_begin = min(kblocks, kslice * per_slice), kb_end = min(kblocks, kb_begin + per_slice);
+
+    for (int unit = blockIdx.x; unit < a.n_units; unit += gridDim.x) {
+        const int n0 = (unit * tiles_per_unit + tile_in_unit) * 16;
+        float acc[NW][MT][4];
+#pragma unroll
+        for (int w = 0; w < NW; ++w)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) acc[w][m][0] = acc[w][m][1] = acc[w][m][2] = acc[w][m][3] = 0.f;
+        if (n0 < a.N) {
+            // rows of W this thread loads (clamped inside the matrix; clamped rows are not stored)
+            const __nv_bfloat16 *wr[NW][2];
+#pragma unroll
+            for (int w = 0; w < NW; ++w) {
+                wr[w][0] = a.w + ((size_t)w * a.N + min(n0 + g, a.N - 1)) * a.K + t * 8;
+                wr[w][1] = a.w + ((size_t)w * a.N + min(n0 + g + 8, a.N - 1)) * a.K + t * 8;
+            }
+            for (int kb0 = kb_begin; kb0 < kb_end; kb0 += SL_UNROLL) {
+                uint4 wv[SL_UNROLL][NW][2];
+#pragma unroll
+                for (int u = 0; u < SL_UNROLL; ++u) {
+                    const int kb = min(kb0 + u, kb_end - 1);         // a repeated block is masked below
+#pragma unroll
+                    for (int w = 0; w < NW; ++w) {
+                        wv[u][w][0] = ld_stream(wr[w][0] + kb * 32);
+                        wv[u][w][1] = ld_stream(wr[w][1] + kb * 32);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < SL_UNROLL; ++u) {
+                    if (kb0 + u >= kb_end) break;
+                    const int kb = kb0 + u;
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        const uint4 b = act_s[(kb * 4 + t) * (MT * 8) + m * 8 + g];
+#pragma unroll
+                        for (int w = 0; w < NW; ++w) {
+                            mma16816(acc[w][m], wv[u][w][0].x, wv[u][w][1].x, wv[u][w][0].y, wv[u][w][1].y, b.x, b.y);
+                            mma16816(acc[w][m], wv[u][w][0].z, wv[u][w][1].z, wv[u][w][0].w, wv[u][w][1].w, b.z, b.w);
+                        }
+                    }
+                }
+            }
+        }
+        // partial sums of the K slices meet in shared memory
+        if (a.ksplit > 1) {
+#pragma unroll
+            for (int w = 0; w < NW; ++w)
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        red_s[(((warp * NW + w) * MT + m) * 4 + c) * 32 + lane] = acc[w][m][c];
+            __syncthreads();
+            if (kslice == 0) {
+                for (int s = 1; s < a.ksplit; ++s)
+#pragma unroll
+                    for (int w = 0; w < NW; ++w)
+#pragma unroll
+                        for (int m = 0; m < MT; ++m)
+#pragma unroll
+                            for (int c = 0; c < 4; ++c)
+                                acc[w][m][c] += red_s[((((warp + s) * NW + w) * MT + m) * 4 + c) * 32 + lane];
+            }
+        }
+        if (kslice == 0 && n0 < a.N) {
+            // accumulator element c of tile m: feature n0 + g (+8 for c >= 2), row m*8 + 2t + (c & 1)
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int n = n0 + g + (c >> 1) * 8, row = m * 8 + 2 * t + (c & 1);
+                    if (n < a.N && row < a.M) {
+                        if (EPI == EPI_F32) {
+                            reinterpret_cast<float *>(a.out)[(size_t)row * a.ldo + n] = acc[0][m][c];
+                        } else {
+                            const float gate = acc[0][m][c], up = acc[NW - 1][m][c];
+                            reinterpret_cast<__nv_bfloat16 *>(a.out)[(size_t)row * a.ldo + n] =
+                                __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+                        }
+                    }
+                }
+        }
+        if (a.ksplit > 1) __syncthreads();
+    }
+}
+
+template <int MT, int EPI>
+static int launch_small(const SmallLinearArgs &a, int ctas, size_t smem, cudaStream_t stream) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(small_linear_kernel<MT, EPI>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "linear_small: %s", cudaGetErrorString(e));
+    }
+    small_linear_kernel<MT, EPI><<<ctas, SL_WARPS * 32, smem, stream>>>(a);
+    JK_CHECK_LAUNCH("linear_small");
+    return JK_OK;
+}
+
+// Does this kernel take the product?  (M rows, K a multiple of 32, the activations fit in shared memory.)
+JK_EXPORT int jk_linear_small_supports(int M, int N, int K) {
+    if (M < 1 || M > 16 || N < 1 || K < 32 || K % 32) return 0;
+    const int MT = M <= 8 ? 1 : 2;
+    const size_t smem = (size_t)(K / 8) * MT * 8 * 16 + (size_t)SL_WARPS * 2 * MT * 4 * 32 * sizeof(float);
+    return smem <= 200 * 1024;
+}
+
+JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, int N, int K, int ldo,
+                              int epilogue, int sms, cudaStream_t stream) {
+    JK_REQUIRE(jk_linear_small_supports(M, N, K), "linear_small: M %d N %d K %d is outside what the kernel takes "
+               "(1..16 rows, K a multiple of 32)", M, N, K);
+    JK_REQUIRE(epilogue == EPI_F32 || epilogue == EPI_SWIGLU, "linear_small: epilogue %d", epilogue);
+    JK_REQUIRE(ldo >= N, "linear_small: output stride %d < N %d", ldo, N);
+    const int MT = M <= 8 ? 1 : 2;
+    const int tiles = (N + 15) / 16;
+    if (sms <= 0) sms = 148;
+    // slices of K per tile: enough warps in flight to cover the memory latency when N is small
+    int ksplit = 1;
+    while (ksplit < SL_WARPS && tiles * ksplit < sms * SL_WARPS * 2 && (K / 32) / (ksplit * 2) >= 4) ksplit *= 2;
+    const int tiles_per_unit = SL_WARPS / ksplit;
+    SmallLinearArgs a{(const __nv_bfloat16 *)act, (const __nv_bfloat16 *)w, out, M, N, K, ldo, ksplit,
+                      (tiles + tiles_per_unit - 1) / tiles_per_unit};
+    const int NW = epilogue == EPI_SWIGLU ? 2 : 1;
+    const size_t smem = (size_t)(K / 8) * MT * 8 * 16 + (size_t)SL_WARPS * NW * MT * 4 * 32 * sizeof(float);
+    const int per_sm = smem > 100 * 1024 ? 1 : (smem > 64 * 1024 ? 2 : 3);
+    const int ctas = a.n_units < sms * per_sm ? a.n_units : sms * per_sm;
+    if (MT == 1 && epilogue == EPI_F32) return launch_small<1, EPI_F32>(a, ctas, smem, stream);
+    if (MT == 2 && epilogue == EPI_F32) return launch_small<2, EPI_F32>(a, ctas, smem, stream);
+    if (MT == 1) return launch_small<1, EPI_SWIGLU>(a, ctas, smem, stream);
+    return launch_small<2, EPI_SWIGLU>(a, ctas, smem, stream);
+}

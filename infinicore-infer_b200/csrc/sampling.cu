@@ -66,10 +66,51 @@ argmax_kernel(const float *__restrict__ logits, long long ld, int V, int *__rest
     if (threadIdx.x == 0) out[blockIdx.x] = idx;
 }
 
-JK_EXPORT int jk_argmax(const float *logits, long long ld, int nrows, int V, int *out,
+// Two stages for few rows of a large vocabulary: blocks take chunks of a row, then one block per row
+// picks among the chunks' winners (the lowest index among equals in both stages).
+constexpr int ARGMAX_CHUNK = 8192;
+
+__global__ void __launch_bounds__(256)
+argmax_chunks_kernel(const float *__restrict__ logits, long long ld, int V, ArgMax *__restrict__ part) {
+    __shared__ ArgMax scratch[33];
+    const int r = blockIdx.y, c = blockIdx.x;
+    const int lo = c * ARGMAX_CHUNK, n = min(ARGMAX_CHUNK, V - lo);
+    const int idx = block_argmax(logits + (size_t)r * ld + lo, n, scratch);
+    if (threadIdx.x == 0) part[(size_t)r * gridDim.x + c] = ArgMax{logits[(size_t)r * ld + lo + idx], lo + idx};
+}
+
+__global__ void argmax_merge_kernel(const ArgMax *__restrict__ part, int nchunks, int *__restrict__ out) {
+    const int r = blockIdx.x;
+    ArgMax best{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < nchunks; i += 32) best = better(best, part[(size_t)r * nchunks + i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    if (threadIdx.x == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
+// Bytes of scratch that `jk_argmax` wants for this shape (0: it runs in one stage).
+JK_EXPORT long long jk_argmax_scratch_bytes(int nrows, int V) {
+    const int chunks = (V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+    if (chunks < 2 || nrows * 1 >= 148 * 2) return 0;
+    return (long long)nrows * chunks * sizeof(ArgMax);
+}
+
+JK_EXPORT int jk_argmax(const float *logits, long long ld, int nrows, int V, int *out, void *scratch,
                         cudaStream_t stream) {
     if (nrows == 0) return JK_OK;
     JK_REQUIRE(nrows > 0 && V > 0 && ld >= V, "argmax: rows %d, vocabulary %d, stride %lld", nrows, V, ld);
+    if (scratch != nullptr && jk_argmax_scratch_bytes(nrows, V) > 0) {
+        const int chunks = (V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+        JK_REQUIRE(nrows <= 65535, "argmax: %d rows exceed one launch", nrows);
+        argmax_chunks_kernel<<<dim3(chunks, nrows), 256, 0, stream>>>(logits, ld, V, (ArgMax *)scratch);
+        JK_CHECK_LAUNCH("argmax_chunks");
+        argmax_merge_kernel<<<nrows, 32, 0, stream>>>((const ArgMax *)scratch, chunks, out);
+        JK_CHECK_LAUNCH("argmax_merge");
+        return JK_OK;
+    }
     argmax_kernel<<<nrows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, out);
     JK_CHECK_LAUNCH("argmax");
     return JK_OK;

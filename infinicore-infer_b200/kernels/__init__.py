@@ -174,6 +174,40 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional
     return out
 
 
+EPI_F32, EPI_SWIGLU = 0, 1
+
+
+def linear_small_supports(m: int, n: int, k: int) -> bool:
+    """Whether the weight-streaming kernel for steps of few rows takes this product."""
+    return bool(_build.load("linear_small").jk_linear_small_supports(_c_int(m), _c_int(n), _c_int(k)))
+
+
+def linear_small(act: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_F32) -> torch.Tensor:
+    """out = act @ w^T for at most 16 rows of bfloat16 activations.  EPI_F32: float32 out [M, N].
+    EPI_SWIGLU: w is [2N, K] (gate rows, then up rows) and out is bfloat16 [M, N] = silu(gate) * up."""
+    _need(act, "act", torch.bfloat16); _need(w, "w", torch.bfloat16)
+    _need(out, "out", torch.float32 if epilogue == EPI_F32 else torch.bfloat16)
+    m, k = act.shape
+    n = w.shape[0] // (2 if epilogue == EPI_SWIGLU else 1)
+    if w.shape[1] != k or tuple(out.shape) != (m, n):
+        raise KernelError(f"linear_small: act {tuple(act.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    lib = _build.load("linear_small")
+    _check("linear_small", lib.jk_linear_small(_ptr(act), _ptr(w), _ptr(out), _c_int(m), _c_int(n), _c_int(k),
+                                               _c_int(out.stride(0)), _c_int(epilogue), _c_int(_sm_count(act.device)),
+                                               _stream()))
+    return out
+
+
+_SMS = {}
+
+
+def _sm_count(device) -> int:
+    key = str(device)
+    if key not in _SMS:
+        _SMS[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SMS[key]
+
+
 def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                    positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor, ntok: int,
                    nh: int, scale: float, window: int = 0) -> torch.Tensor:
@@ -195,12 +229,12 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
 
 
 def attention_decode_splits(nrows: int, nkvh: int, group: int, max_positions: int, sms: int = 148) -> int:
-    """How many ways the decode kernel cuts each row's key range: enough blocks to fill the GPU a few
-    times over, no split shorter than 64 keys at the longest context.  It depends on the batch's size
+    """How many ways the decode kernel cuts each row's key range: enough blocks to fill the GPU many
+    times over, no split shorter than 128 keys at the longest context.  It depends on the batch's size
     only (not on the lengths), so a captured step keeps its grid."""
     blocks = max(1, nrows * nkvh * ((group + 3) // 4 if group > 4 else 1))
-    want = -(-4 * sms // blocks)
-    return max(1, min(want, 32, -(-max_positions // 64)))
+    want = -(-16 * sms // blocks)          # several waves of blocks, so that the last wave's idle SMs matter little
+    return max(1, min(want, 32, -(-max_positions // 128)))
 
 
 def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
@@ -266,7 +300,11 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     if logits.stride(1) != 1:
         raise KernelError("argmax: rows must be contiguous")
     lib = _build.load("sampling")
-    _check("sampling", lib.jk_argmax(_ptr(logits), _c_ll(logits.stride(0)), _c_int(n), _c_int(v), _ptr(out), _stream()))
+    lib.jk_argmax_scratch_bytes.restype = ctypes.c_longlong
+    need = lib.jk_argmax_scratch_bytes(_c_int(n), _c_int(v))
+    scratch = torch.empty(need, dtype=torch.uint8, device=logits.device) if need else None
+    _check("sampling", lib.jk_argmax(_ptr(logits), _c_ll(logits.stride(0)), _c_int(n), _c_int(v), _ptr(out),
+                                     _ptr(scratch), _stream()))
     return out
 
 

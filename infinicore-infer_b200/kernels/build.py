@@ -25,6 +25,7 @@ MODULES: Dict[str, List[str]] = {
     "elementwise": ["elementwise.cu"],
     "attention": ["attention.cu"],
     "sampling": ["sampling.cu"],
+    "linear_small": ["linear_small.cu"],
 }
 HEADERS = ["common.cuh"]
 

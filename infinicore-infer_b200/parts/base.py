@@ -65,6 +65,7 @@ class Runtime:
         self.dtype = dtype
         self.device = torch.device(device)
         self.plain_attention = False      # True: bfloat16 attention through the row kernel too
+        self.library_products_only = False   # True: every bfloat16 product goes to the library
 
     def empty(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
@@ -77,6 +78,11 @@ class Runtime:
             out = self.empty(h.shape[0], weight.shape[0], dtype=torch.float32)
             return kernels.gemm_f32(h, weight, out, bias)
         out_dtype = out_dtype or torch.bfloat16
+        m, k = h.shape
+        if (out_dtype == torch.float32 and bias is None and m <= 16 and not self.library_products_only
+                and kernels.linear_small_supports(m, weight.shape[0], k)):
+            out = self.empty(m, weight.shape[0], dtype=torch.float32)
+            return kernels.linear_small(h, weight, out)
         if out_dtype == torch.bfloat16:
             out = torch.mm(h, weight.t())
         else:
@@ -84,6 +90,19 @@ class Runtime:
         if bias is not None:
             out += bias.to(out.dtype)
         return out
+
+
+    def gate_up_swiglu(self, h: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+        """silu(h @ Wg^T) * (h @ Wu^T) for the fused [gate | up] matrix -> [T, intermediate]."""
+        from .. import kernels
+        m, k = h.shape
+        di = w_gate_up.shape[0] // 2
+        act = self.empty(m, di)
+        if (self.dtype == torch.bfloat16 and m <= 16 and not self.library_products_only
+                and kernels.linear_small_supports(m, di, k)):
+            return kernels.linear_small(h, w_gate_up, act, kernels.EPI_SWIGLU)
+        gu = self.linear(h, w_gate_up, out_dtype=torch.float32)
+        return kernels.swiglu(gu, act)
 
 
 SHORT_ROWS = 8      # a request with at most this many rows in a step counts as "few rows"

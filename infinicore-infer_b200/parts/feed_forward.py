@@ -32,9 +32,6 @@ class SwiGLU:
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
-        from .. import kernels
         rt = self.runtime
-        gu = rt.linear(h, self.w_gate_up, out_dtype=torch.float32)
-        act = rt.empty(h.shape[0], self.spec.intermediate_size)
-        kernels.swiglu(gu, act)
+        act = rt.gate_up_swiglu(h, self.w_gate_up)
         return rt.linear(act, self.w_down, out_dtype=torch.float32)

@@ -334,3 +334,38 @@ def test_sample_is_reproducible_and_follows_the_distribution(K):
     freq = torch.bincount(a.long().cpu(), minlength=V).double() / n
     p = torch.softmax(row.double(), 0)
     assert (freq - p).abs().max() < 4 * math.sqrt(0.25 / n)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K_", [(48, 64), (301, 96), (2304, 2304), (1000, 5760), (6912, 2304), (17, 32)])
+def test_linear_small_streams_weights_for_few_rows(K, M, N, K_):
+    g = torch.Generator().manual_seed(M * N + K_)
+    act = torch.randn(M, K_, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+    assert K.linear_small_supports(M, N, K_)
+    out = torch.full((M, N), 9.0, device=DEV)
+    K.linear_small(act.to(DEV), w.to(DEV), out)
+    want = act.double() @ w.double().T
+    torch.testing.assert_close(out.double().cpu(), want, rtol=1e-4, atol=1e-4)      # float32 accumulation of bf16 products
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("N,K_", [(136, 96), (5760, 2304), (50, 64)])
+def test_linear_small_with_swiglu_epilogue(K, M, N, K_):
+    g = torch.Generator().manual_seed(M + N + K_)
+    act = torch.randn(M, K_, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * N, K_, generator=g) * 2 / math.sqrt(K_)).to(torch.bfloat16)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    K.linear_small(act.to(DEV), w.to(DEV), out, K.EPI_SWIGLU)
+    gu = act.double() @ w.double().T
+    want = gu[:, :N] * torch.sigmoid(gu[:, :N]) * gu[:, N:]
+    _close(out, want, torch.bfloat16, scale=2.0)
+
+
+def test_linear_small_refuses_what_it_cannot_take(K):
+    assert not K.linear_small_supports(17, 64, 64)
+    assert not K.linear_small_supports(4, 64, 80)       # K must be a multiple of 32
+    assert not K.linear_small_supports(16, 64, 1 << 20)
+    with pytest.raises(K.KernelError, match="outside what the kernel takes"):
+        K.linear_small(torch.zeros(4, 80, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 80, dtype=torch.bfloat16, device=DEV),
+                       torch.zeros(4, 8, device=DEV))
