@@ -163,6 +163,13 @@ JK_EXPORT int jk_attention_rows(const void *q, const void *k_pages, const void *
 // usual rule  acc = sum_i exp(m_i - M) acc_i,  l = sum_i exp(m_i - M) l_i.
 // The split partials go to scratch memory and a second kernel merges them.
 // ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
 struct DecodeArgs {
     const __nv_bfloat16 *q;        // [T, nh, dh]
     const __nv_bfloat16 *k_pages;  // [pages, nkvh, page_size, dh]
@@ -179,7 +186,8 @@ struct DecodeArgs {
 };
 
 constexpr int DEC_WARPS = 4;
-constexpr int DEC_UNROLL = 4;      // keys a group has in flight
+constexpr int DEC_UNROLL = 4;      // keys a group handles per stage
+constexpr int DEC_STAGES = 4;      // stages of keys and values in flight per thread
 
 __device__ __forceinline__ float fast_exp2(float x) {     // 2^x to 22 bits; 2^-inf = 0
     float y;
@@ -247,10 +255,40 @@ attention_decode_kernel(DecodeArgs a) {
         for (int e = 0; e < 8; ++e) acc[hh][e] = 0.f;
     }
 
-    // The trip count is the same for every thread of the block and no thread skips a shuffle:
-    // a key beyond the range scores -inf and so weighs exactly zero.  DEC_UNROLL keys are in flight
-    // per group and share one update of the running maximum.
-    for (int base = k_begin; base < k_end; base += GROUPS * DEC_UNROLL) {
+    // Keys and values travel through a ring in shared memory that is private to each thread: the
+    // thread that issues a 16-byte cp.async is the one that later reads it, so nothing but the
+    // thread's own cp.async.wait_group orders them, and DEC_STAGES stages stay in flight whatever
+    // the register budget.  The trip count is the same for every thread of the block and no thread
+    // skips a shuffle: a key beyond the range scores -inf and so weighs exactly zero.
+    extern __shared__ __align__(16) float dec_smem[];
+    uint4 *ring = reinterpret_cast<uint4 *>(dec_smem);          // [DEC_STAGES][DEC_UNROLL][2][threads]
+    const int nthreads = DEC_WARPS * 32;
+    const int n_iter = (k_end - k_begin + GROUPS * DEC_UNROLL - 1) / (GROUPS * DEC_UNROLL);
+    auto issue = [&](int it) {
+        if (it < n_iter) {
+            const int base = k_begin + it * GROUPS * DEC_UNROLL;
+            uint4 *slot = ring + (size_t)(it % DEC_STAGES) * DEC_UNROLL * 2 * nthreads + threadIdx.x;
+#pragma unroll
+            for (int u = 0; u < DEC_UNROLL; ++u) {
+                const int j = base + group + u * GROUPS;
+                if (j < k_end && lane_ok) {
+                    const int blk = POW2 ? (j >> a.page_shift) : (j / a.page_size);
+                    const int in_page = POW2 ? (j & (a.page_size - 1)) : (j - blk * a.page_size);
+                    const size_t off = (size_t)bt[blk] * page_stride + head_off + (size_t)in_page * dh;
+                    cp_async16(slot + (u * 2) * nthreads, a.k_pages + off);
+                    cp_async16(slot + (u * 2 + 1) * nthreads, a.v_pages + off);
+                }
+            }
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int s0 = 0; s0 < DEC_STAGES - 1; ++s0) issue(s0);
+    for (int it = 0; it < n_iter; ++it) {
+        issue(it + DEC_STAGES - 1);
+        cp_async_wait<DEC_STAGES - 1>();
+        const int base = k_begin + it * GROUPS * DEC_UNROLL;
+        const uint4 *slot = ring + (size_t)(it % DEC_STAGES) * DEC_UNROLL * 2 * nthreads + threadIdx.x;
         uint4 kr[DEC_UNROLL], vr[DEC_UNROLL];
         bool ok[DEC_UNROLL];
 #pragma unroll
@@ -259,11 +297,8 @@ attention_decode_kernel(DecodeArgs a) {
             ok[u] = j < k_end;
             kr[u] = make_uint4(0, 0, 0, 0); vr[u] = make_uint4(0, 0, 0, 0);
             if (ok[u] && lane_ok) {
-                const int blk = POW2 ? (j >> a.page_shift) : (j / a.page_size);
-                const int in_page = POW2 ? (j & (a.page_size - 1)) : (j - blk * a.page_size);
-                const size_t off = (size_t)bt[blk] * page_stride + head_off + (size_t)in_page * dh;
-                kr[u] = *reinterpret_cast<const uint4 *>(a.k_pages + off);
-                vr[u] = *reinterpret_cast<const uint4 *>(a.v_pages + off);
+                kr[u] = slot[(u * 2) * nthreads];
+                vr[u] = slot[(u * 2 + 1) * nthreads];
             }
         }
         float sc[HG][DEC_UNROLL];
@@ -311,8 +346,8 @@ attention_decode_kernel(DecodeArgs a) {
         }
     }
 
-    // merge the groups of this block
-    extern __shared__ float dec_smem[];
+    // merge the groups of this block (the ring's memory is free once every thread has left the loop)
+    __syncthreads();
     float *s_ml = dec_smem;                                   // [GROUPS][HG][2]
     float *s_acc = dec_smem + GROUPS * HG * 2;                // [GROUPS][HG][LPR*8]
 #pragma unroll
@@ -375,7 +410,9 @@ static int launch_decode(const DecodeArgs &a, cudaStream_t stream) {
     const int g = a.nh / a.nkvh;
     const int hgroups = (g + HG - 1) / HG;
     dim3 grid(a.splits, a.nkvh * hgroups, a.nrows);
-    const size_t smem = (size_t)GROUPS * HG * (2 + LPR * 8) * sizeof(float);
+    const size_t merge_bytes = (size_t)GROUPS * HG * (2 + LPR * 8) * sizeof(float);
+    const size_t ring_bytes = (size_t)DEC_STAGES * DEC_UNROLL * 2 * DEC_WARPS * 32 * sizeof(uint4);
+    const size_t smem = merge_bytes > ring_bytes ? merge_bytes : ring_bytes;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<LPR, HG, POW2>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -460,12 +497,6 @@ struct PrefillArgs {
 
 constexpr int PF_BM = 64;
 
-__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
 __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void *smem) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);

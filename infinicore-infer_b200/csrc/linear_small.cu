@@ -8,9 +8,9 @@
 // thread's operand registers come straight out of ONE 16-byte load: thread (g, t) of a warp
 // loads W[n0 + g][k0 + 8t .. k0 + 8t + 7] and W[n0 + g + 8][same], and the activations are laid
 // out in shared memory as [k / 8][row][8] so that its B registers are one conflict-free 16-byte
-// load as well.  No shuffle, no ldmatrix, no staging of weights in shared memory.
+// load as well.  No shuffle, no ldmatrix, no transposition of weights.
 //
-// A block's 8 warps are split into (tiles of 16 features) x (slices of K); the slices' partial
+// A block's 4 warps are split into (tiles of 16 features) x (slices of K); the slices' partial
 // sums meet in shared memory and the first slice's warp runs the epilogue:
 //   EPI_F32     out[m, n] = acc                       (float32; the residual add and the next
 //                                                      norm are the consumer's)
@@ -31,15 +31,17 @@ struct SmallLinearArgs {
     int M, N, K, ldo, ksplit, n_units;
 };
 
-constexpr int SL_WARPS = 8;
-constexpr int SL_UNROLL = 4;    // 32-wide k blocks in flight per warp
+constexpr int SL_MAX_WARPS = 4;
+constexpr int SL_RING = 256;        // ring bytes per thread: 16 loads of 16 bytes in flight
+constexpr int SL_RING_SMALL = 128;  // when the activations take most of the shared memory
 
-__device__ __forceinline__ uint4 ld_stream(const void *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
 __device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -47,19 +49,55 @@ __device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int MT, int EPI>      // MT: tiles of 8 activation rows (1 or 2)
-__global__ void __launch_bounds__(SL_WARPS * 32)
+// The weights a thread needs travel through a ring in shared memory that is private to the thread
+// (it issues the 16-byte cp.async and it reads the result), DEPTH blocks of 32 k ahead of the
+// tensor-core instructions that consume them, across the boundaries of tiles.  The first blocks
+// are on their way before the activations are staged.
+template <int MT, int EPI, int RING>      // MT: tiles of 8 activation rows (1 or 2); RING: ring bytes per thread
+__global__ void __launch_bounds__(SL_MAX_WARPS * 32)
 small_linear_kernel(SmallLinearArgs a) {
     constexpr int NW = EPI == EPI_SWIGLU ? 2 : 1;          // weight tiles a warp streams together
+    constexpr int DEPTH = RING / (NW * 2 * 16);
     extern __shared__ __align__(16) unsigned char sl_smem[];
-    uint4 *act_s = reinterpret_cast<uint4 *>(sl_smem);                    // [K / 8][MT * 8] units of 8 bf16
-    float *red_s = reinterpret_cast<float *>(sl_smem + (size_t)(a.K / 8) * MT * 8 * 16);   // [SL_WARPS][NW][MT][4][32]
+    const int nthreads = blockDim.x, nwarps = blockDim.x >> 5;
+    uint4 *act_s = reinterpret_cast<uint4 *>(sl_smem);                          // [K / 8][MT * 8] units of 8 bf16
+    uint4 *ring = act_s + (size_t)(a.K / 8) * MT * 8;                           // [DEPTH][NW][2][threads]
+    float *red_s = reinterpret_cast<float *>(ring + (size_t)DEPTH * NW * 2 * nthreads);   // [warps][NW][MT][4][32]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
 
+    const int tiles_per_unit = nwarps / a.ksplit;
+    const int tile_in_unit = warp / a.ksplit, kslice = warp - tile_in_unit * a.ksplit;
+    const int kblocks = a.K / 32;
+    const int per_slice = (kblocks + a.ksplit - 1) / a.ksplit;
+    const int kb_begin = min(kblocks, kslice * per_slice), kb_end = min(kblocks, kb_begin + per_slice);
+    const int nkb = kb_end - kb_begin;
+    const int my_units = blockIdx.x < a.n_units ? (a.n_units - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+    const int total_items = my_units * nkb;                  // (unit, k block) pairs of this warp, in order
+
+    auto issue = [&](int q) {
+        if (q < total_items) {
+            const int ui = q / nkb, kb = kb_begin + (q - ui * nkb);
+            const int n0 = ((blockIdx.x + ui * gridDim.x) * tiles_per_unit + tile_in_unit) * 16;
+            if (n0 < a.N) {
+                uint4 *slot = ring + (size_t)(q % DEPTH) * NW * 2 * nthreads + threadIdx.x;
+#pragma unroll
+                for (int w = 0; w < NW; ++w) {
+                    // rows are clamped inside the matrix; what a clamped row yields is not stored
+                    const size_t r0 = (size_t)w * a.N + min(n0 + g, a.N - 1), r1 = (size_t)w * a.N + min(n0 + g + 8, a.N - 1);
+                    cp_async16(slot + (w * 2) * nthreads, a.w + r0 * a.K + kb * 32 + t * 8);
+                    cp_async16(slot + (w * 2 + 1) * nthreads, a.w + r1 * a.K + kb * 32 + t * 8);
+                }
+            }
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int q = 0; q < DEPTH - 1; ++q) issue(q);
+
     // activations into shared memory, [k / 8][row][8]; rows beyond M are zero
     const int units = a.K / 8;
-    for (int i = threadIdx.x; i < units * MT * 8; i += blockDim.x) {
+    for (int i = threadIdx.x; i < units * MT * 8; i += nthreads) {
         const int kb = i / (MT * 8), row = i - kb * (MT * 8);
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row < a.M) v = *reinterpret_cast<const uint4 *>(a.act + (size_t)row * a.K + kb * 8);
@@ -67,50 +105,29 @@ small_linear_kernel(SmallLinearArgs a) {
     }
     __syncthreads();
 
-    const int tiles_per_unit = SL_WARPS / a.ksplit;
-    const int tile_in_unit = warp / a.ksplit, kslice = warp - tile_in_unit * a.ksplit;
-    const int kblocks = a.K / 32;
-    const int per_slice = (kblocks + a.ksplit - 1) / a.ksplit;
-    const int kb_begin = min(kblocks, kslice * per_slice), kb_end = min(kblocks, kb_begin + per_slice);
-
-    for (int unit = blockIdx.x; unit < a.n_units; unit += gridDim.x) {
-        const int n0 = (unit * tiles_per_unit + tile_in_unit) * 16;
+    int q = 0;
+    for (int ui = 0; ui < my_units; ++ui) {
+        const int n0 = ((blockIdx.x + ui * gridDim.x) * tiles_per_unit + tile_in_unit) * 16;
         float acc[NW][MT][4];
 #pragma unroll
         for (int w = 0; w < NW; ++w)
 #pragma unroll
             for (int m = 0; m < MT; ++m) acc[w][m][0] = acc[w][m][1] = acc[w][m][2] = acc[w][m][3] = 0.f;
-        if (n0 < a.N) {
-            // rows of W this thread loads (clamped inside the matrix; clamped rows are not stored)
-            const __nv_bfloat16 *wr[NW][2];
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++q) {
+            issue(q + DEPTH - 1);
+            cp_async_wait<DEPTH - 1>();
+            if (n0 < a.N) {
+                const uint4 *slot = ring + (size_t)(q % DEPTH) * NW * 2 * nthreads + threadIdx.x;
+                uint4 wv[NW][2];
 #pragma unroll
-            for (int w = 0; w < NW; ++w) {
-                wr[w][0] = a.w + ((size_t)w * a.N + min(n0 + g, a.N - 1)) * a.K + t * 8;
-                wr[w][1] = a.w + ((size_t)w * a.N + min(n0 + g + 8, a.N - 1)) * a.K + t * 8;
-            }
-            for (int kb0 = kb_begin; kb0 < kb_end; kb0 += SL_UNROLL) {
-                uint4 wv[SL_UNROLL][NW][2];
+                for (int w = 0; w < NW; ++w) { wv[w][0] = slot[(w * 2) * nthreads]; wv[w][1] = slot[(w * 2 + 1) * nthreads]; }
 #pragma unroll
-                for (int u = 0; u < SL_UNROLL; ++u) {
-                    const int kb = min(kb0 + u, kb_end - 1);         // a repeated block is masked below
+                for (int m = 0; m < MT; ++m) {
+                    const uint4 b = act_s[(kb * 4 + t) * (MT * 8) + m * 8 + g];
 #pragma unroll
                     for (int w = 0; w < NW; ++w) {
-                        wv[u][w][0] = ld_stream(wr[w][0] + kb * 32);
-                        wv[u][w][1] = ld_stream(wr[w][1] + kb * 32);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < SL_UNROLL; ++u) {
-                    if (kb0 + u >= kb_end) break;
-                    const int kb = kb0 + u;
-#pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        const uint4 b = act_s[(kb * 4 + t) * (MT * 8) + m * 8 + g];
-#pragma unroll
-                        for (int w = 0; w < NW; ++w) {
-                            mma16816(acc[w][m], wv[u][w][0].x, wv[u][w][1].x, wv[u][w][0].y, wv[u][w][1].y, b.x, b.y);
-                            mma16816(acc[w][m], wv[u][w][0].z, wv[u][w][1].z, wv[u][w][0].w, wv[u][w][1].w, b.z, b.w);
-                        }
+                        mma16816(acc[w][m], wv[w][0].x, wv[w][1].x, wv[w][0].y, wv[w][1].y, b.x, b.y);
+                        mma16816(acc[w][m], wv[w][0].z, wv[w][1].z, wv[w][0].w, wv[w][1].w, b.z, b.w);
                     }
                 }
             }
@@ -158,14 +175,22 @@ small_linear_kernel(SmallLinearArgs a) {
     }
 }
 
-template <int MT, int EPI>
-static int launch_small(const SmallLinearArgs &a, int ctas, size_t smem, cudaStream_t stream) {
+static size_t small_linear_smem(int K, int MT, int warps, int ring) {
+    return (size_t)(K / 8) * MT * 8 * 16 + (size_t)ring * warps * 32 + (size_t)warps * 2 * MT * 4 * 32 * sizeof(float);
+}
+// The deep ring unless the activations leave too little room for it.
+static int small_linear_ring(int K, int MT, int warps) {
+    return small_linear_smem(K, MT, warps, SL_RING) <= 100 * 1024 ? SL_RING : SL_RING_SMALL;
+}
+
+template <int MT, int EPI, int RING>
+static int launch_small(const SmallLinearArgs &a, int ctas, int warps, size_t smem, cudaStream_t stream) {
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(small_linear_kernel<MT, EPI>,
+        cudaError_t e = cudaFuncSetAttribute(small_linear_kernel<MT, EPI, RING>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "linear_small: %s", cudaGetErrorString(e));
     }
-    small_linear_kernel<MT, EPI><<<ctas, SL_WARPS * 32, smem, stream>>>(a);
+    small_linear_kernel<MT, EPI, RING><<<ctas, warps * 32, smem, stream>>>(a);
     JK_CHECK_LAUNCH("linear_small");
     return JK_OK;
 }
@@ -174,8 +199,7 @@ static int launch_small(const SmallLinearArgs &a, int ctas, size_t smem, cudaStr
 JK_EXPORT int jk_linear_small_supports(int M, int N, int K) {
     if (M < 1 || M > 16 || N < 1 || K < 32 || K % 32) return 0;
     const int MT = M <= 8 ? 1 : 2;
-    const size_t smem = (size_t)(K / 8) * MT * 8 * 16 + (size_t)SL_WARPS * 2 * MT * 4 * 32 * sizeof(float);
-    return smem <= 200 * 1024;
+    return small_linear_smem(K, MT, 4, small_linear_ring(K, MT, 4)) <= 200 * 1024;
 }
 
 JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, int N, int K, int ldo,
@@ -187,18 +211,26 @@ JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, 
     const int MT = M <= 8 ? 1 : 2;
     const int tiles = (N + 15) / 16;
     if (sms <= 0) sms = 148;
-    // slices of K per tile: enough warps in flight to cover the memory latency when N is small
-    int ksplit = 1;
-    while (ksplit < SL_WARPS && tiles * ksplit < sms * SL_WARPS * 2 && (K / 32) / (ksplit * 2) >= 4) ksplit *= 2;
-    const int tiles_per_unit = SL_WARPS / ksplit;
+    // Blocks of 4 warps, several per SM; a block works on one tile of 16 features at a time with its
+    // warps on slices of K (short chains, and the work is cut finely enough to balance over the SMs).
+    const int warps = 4;
+    int ksplit = warps;
+    while (ksplit > 1 && (K / 32) / ksplit < 2) ksplit /= 2;
+    const int tiles_per_unit = warps / ksplit;
     SmallLinearArgs a{(const __nv_bfloat16 *)act, (const __nv_bfloat16 *)w, out, M, N, K, ldo, ksplit,
                       (tiles + tiles_per_unit - 1) / tiles_per_unit};
-    const int NW = epilogue == EPI_SWIGLU ? 2 : 1;
-    const size_t smem = (size_t)(K / 8) * MT * 8 * 16 + (size_t)SL_WARPS * NW * MT * 4 * 32 * sizeof(float);
-    const int per_sm = smem > 100 * 1024 ? 1 : (smem > 64 * 1024 ? 2 : 3);
+    const int ring = small_linear_ring(K, MT, warps);
+    const size_t smem = small_linear_smem(K, MT, warps, ring);
+    int per_sm = (int)((220 * 1024) / (smem + 1024));
+    if (per_sm > 6) per_sm = 6;
+    if (per_sm < 1) per_sm = 1;
     const int ctas = a.n_units < sms * per_sm ? a.n_units : sms * per_sm;
-    if (MT == 1 && epilogue == EPI_F32) return launch_small<1, EPI_F32>(a, ctas, smem, stream);
-    if (MT == 2 && epilogue == EPI_F32) return launch_small<2, EPI_F32>(a, ctas, smem, stream);
-    if (MT == 1) return launch_small<1, EPI_SWIGLU>(a, ctas, smem, stream);
-    return launch_small<2, EPI_SWIGLU>(a, ctas, smem, stream);
+#define SL_LAUNCH(MT_, EPI_)                                                                            \
+    return ring == SL_RING ? launch_small<MT_, EPI_, SL_RING>(a, ctas, warps, smem, stream)             \
+                           : launch_small<MT_, EPI_, SL_RING_SMALL>(a, ctas, warps, smem, stream)
+    if (MT == 1 && epilogue == EPI_F32) SL_LAUNCH(1, EPI_F32);
+    if (MT == 2 && epilogue == EPI_F32) SL_LAUNCH(2, EPI_F32);
+    if (MT == 1) SL_LAUNCH(1, EPI_SWIGLU);
+    SL_LAUNCH(2, EPI_SWIGLU);
+#undef SL_LAUNCH
 }

@@ -342,6 +342,9 @@ def test_linear_small_streams_weights_for_few_rows(K, M, N, K_):
     g = torch.Generator().manual_seed(M * N + K_)
     act = torch.randn(M, K_, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+    if M > 8 and K_ > 5000:          # 16 rows of 5760 activations leave no room in shared memory
+        assert not K.linear_small_supports(M, N, K_)
+        return
     assert K.linear_small_supports(M, N, K_)
     out = torch.full((M, N), 9.0, device=DEV)
     K.linear_small(act.to(DEV), w.to(DEV), out)
