@@ -714,3 +714,58 @@ JK_EXPORT int jk_attention_prefill(const void *q, const void *k_pages, const voi
         default: JK_FAIL(JK_UNSUPPORTED, "attention_prefill: head size %d has no tensor-core kernel", dh);
     }
 }
+
+// =======================================================================================
+// The decode kernel for callers that cannot allocate: the scratch for the split partials is an
+// array in the library's own image (see attention_static_scratch.h for who needs this and for the
+// rules of use).  Nothing above this line is changed by it.
+// =======================================================================================
+#include "attention_static_scratch.h"
+#include <mutex>
+
+static __device__ __align__(256) float g_static_scratch[JK_STATIC_SCRATCH_FLOATS];
+
+// In host code `g_static_scratch` is only a handle for the symbol, not an address a kernel could
+// use; the device address is looked up once per device and kept here.
+constexpr int JK_MAX_DEVICES = 64;
+static float *g_static_scratch_addr[JK_MAX_DEVICES] = {};
+static std::mutex g_static_scratch_mutex;
+
+static int static_scratch_address(float **out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    JK_REQUIRE(dev >= 0 && dev < JK_MAX_DEVICES, "attention_decode_static: device %d is beyond the %d this library tracks",
+               dev, JK_MAX_DEVICES);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_addr[dev] == nullptr) {
+        // first call on this device (it is the current one): ask the runtime where the array lives here
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            JK_FAIL(JK_CUDA_ERROR, "attention_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_static_scratch_addr[dev] = static_cast<float *>(p);
+    }
+    *out = g_static_scratch_addr[dev];
+    return JK_OK;
+}
+
+JK_EXPORT int jk_attention_decode_static(const void *q, const void *k_pages, const void *v_pages, void *out,
+                                         const int *rows, int nrows, const int *positions, const int *row_req,
+                                         const int *block_table, int max_blocks, int page_size, int nh, int nkvh,
+                                         int dh, float scale, int window, int splits, cudaStream_t stream) {
+    if (nrows == 0) return JK_OK;
+    JK_REQUIRE(nrows > 0 && nh > 0 && dh > 0 && splits >= 1, "attention_decode_static: rows %d heads %d head size %d splits %d",
+               nrows, nh, dh, splits);
+    const long long need = jk_attention_decode_scratch_floats(nrows, nh, dh, splits);
+    JK_REQUIRE(need <= (long long)JK_STATIC_SCRATCH_FLOATS,
+               "attention_decode_static: %d rows x %d heads x %d splits of head size %d need %lld floats of scratch, "
+               "the built-in array holds %d; use fewer splits or rows, or jk_attention_decode with your own scratch",
+               nrows, nh, splits, dh, need, (int)JK_STATIC_SCRATCH_FLOATS);
+    float *scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    // every partial slot that the merge kernel reads is written by the split kernel of this same call,
+    // so what an earlier call left in the array needs no clearing
+    return jk_attention_decode(q, k_pages, v_pages, out, need ? scratch : nullptr, rows, nrows, positions, row_req,
+                               block_table, max_blocks, page_size, nh, nkvh, dh, scale, window, splits, stream);
+}

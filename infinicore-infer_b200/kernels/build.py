@@ -27,7 +27,7 @@ MODULES: Dict[str, List[str]] = {
     "sampling": ["sampling.cu"],
     "linear_small": ["linear_small.cu"],
 }
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "attention_static_scratch.h"]
 
 # -use_fast_math is deliberately absent: expf, division and sqrt stay accurate.
 NVCC_FLAGS = [
