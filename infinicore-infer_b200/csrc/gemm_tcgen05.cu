@@ -1,0 +1,339 @@
+// Matrix products for steps of many rows (prefill): C[M, N] = A[M, K] * W[N, K]^T on the
+// 5th-generation tensor cores of sm_100a, with the layer's elementwise work in the epilogue.
+//
+//   operands   bfloat16, both K-major (A rows are tokens, W rows are output features), brought
+//              into shared memory by TMA (cp.async.bulk.tensor.2d) as 128-byte-swizzled tiles of
+//              [rows][64] through a ring of STAGES stages guarded by full/empty mbarriers;
+//   product    tcgen05.mma.cta_group::1.kind::f16, M = 128, N = BN, K = 16 per instruction, issued
+//              by one elected thread, float32 accumulator in tensor memory (BN columns x 128 lanes);
+//              tcgen05.commit hands a finished stage back to the TMA warp and the finished
+//              accumulator to the epilogue;
+//   epilogue   four warps read the accumulator with tcgen05.ld (each warp its quarter of the
+//              lanes; a thread holds 32 consecutive columns of one row) and apply one of
+//                EPI_F32       out[m, n]  = acc                      float32
+//                EPI_BF16      out[m, n]  = acc                      bfloat16
+//                EPI_RESIDUAL  out[m, n] += scale * acc              float32, in place (the residual stream)
+//                EPI_SWIGLU    out[m, n]  = silu(acc[n]) * acc[N+n]  bfloat16; W is [2N, K], gate rows then
+//                                                                    up rows, and a tile holds BN/2 of each.
+// Rows, columns and the K range that a tile has beyond the matrices are zero-filled by TMA and
+// never stored.  Warp roles: warp 0 TMA, warp 1 MMA (and owner of the tensor-memory allocation),
+// warps 2..5 epilogue.  Every wait on an mbarrier is bounded; a wait that runs out records a code in
+// `status`, the roles drain what is in flight, tensor memory is freed and the kernel returns.
+//
+// (The reference sends these products to a library: src/models/inference_context.cpp:59-79; the
+// residual add is its beta = 1, the SwiGLU a separate operator, jiuge.cpp:236-249.)
+#include "common.cuh"
+
+#include <cuda.h>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+JK_DEFINE_ERROR_BUFFER(jk_gemm_tcgen05)
+
+enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3 };
+
+constexpr int TG_BM = 128, TG_BK = 64, TG_STAGES = 4, TG_THREADS = 192;
+constexpr unsigned TG_SPIN_LIMIT = 1u << 20;      // polls of one wait before it gives up
+
+struct TgArgs {
+    void *out;
+    int M, N, K, ldo;
+    float scale;
+    int *status;       // device word: 0, or the code of the wait that ran out
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit is reached (the caller records where and drains).
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity) {
+    for (unsigned i = 0; i < TG_SPIN_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *smem, const CUtensorMap *map, unsigned long long *bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(unsigned *slot, unsigned columns) {      // one whole warp
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(slot)), "r"(columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned addr, unsigned columns) {     // the same warp
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(addr), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(unsigned tmem_c, unsigned long long adesc, unsigned long long bdesc,
+                                          unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
+                 ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned addr, unsigned (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile [rows][64 bf16] written by TMA with the
+// 128-byte swizzle: rows are 128 bytes, groups of 8 rows are 1024 bytes apart (stride byte offset),
+// the leading byte offset is unused for swizzled K-major tiles (1), version 1, layout type 2.
+__device__ __forceinline__ unsigned long long smem_desc_sw128(const void *tile) {
+    const unsigned long long addr = smem_u32(tile);
+    return ((addr & 0x3FFFFull) >> 4) | (1ull << 16) | ((1024ull >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = bn.
+__host__ __device__ constexpr unsigned instr_desc_bf16(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(TG_BM >> 4) << 24);
+}
+
+template <int BN> struct TgSmem {
+    __nv_bfloat16 a[TG_STAGES][TG_BM * TG_BK];       // 16 KB each, 1024-byte aligned
+    __nv_bfloat16 b[TG_STAGES][BN * TG_BK];
+    unsigned long long full[TG_STAGES], empty[TG_STAGES], acc_full;
+    unsigned tmem_base;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(TG_THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, TgArgs a) {
+    extern __shared__ unsigned char tg_raw[];
+    TgSmem<BN> &s = *reinterpret_cast<TgSmem<BN> *>((reinterpret_cast<uintptr_t>(tg_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TG_BM;
+    // EPI_SWIGLU: the tile's B rows are BN/2 gate rows and the BN/2 up rows that belong to them
+    const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? BN / 2 : BN);
+    const int nk = (a.K + TG_BK - 1) / TG_BK;
+    constexpr unsigned STAGE_BYTES = (TG_BM + BN) * TG_BK * sizeof(__nv_bfloat16);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < TG_STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
+        mbar_init(&s.acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(&s.tmem_base, BN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = s.tmem_base;
+    int failed = 0;
+
+    if (warp == 0) {
+        // ---- TMA producer ----
+        if (lane == 0) {
+            for (int i = 0; i < nk; ++i) {
+                const int st = i % TG_STAGES;
+                if (i >= TG_STAGES && !mbar_wait(&s.empty[st], ((i / TG_STAGES) - 1) & 1)) { failed = 1; break; }
+                mbar_expect_tx(&s.full[st], STAGE_BYTES);
+                tma_load_2d(s.a[st], &map_a, &s.full[st], i * TG_BK, m0);
+                if (EPI == EPI_SWIGLU) {
+                    tma_load_2d(s.b[st], &map_w, &s.full[st], i * TG_BK, n0);
+                    tma_load_2d(s.b[st] + (BN / 2) * TG_BK, &map_w, &s.full[st], i * TG_BK, a.N + n0);
+                } else {
+                    tma_load_2d(s.b[st], &map_w, &s.full[st], i * TG_BK, n0);
+                }
+            }
+            if (failed) atomicExch(a.status, 1);
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        if (lane == 0) {
+            constexpr unsigned idesc = instr_desc_bf16(BN);
+            for (int i = 0; i < nk; ++i) {
+                const int st = i % TG_STAGES;
+                if (!mbar_wait(&s.full[st], (i / TG_STAGES) & 1)) { failed = 2; break; }
+                tc_fence_after();
+                const unsigned long long ad = smem_desc_sw128(s.a[st]), bd = smem_desc_sw128(s.b[st]);
+#pragma unroll
+                for (int k = 0; k < TG_BK / 16; ++k)      // 32 bytes further along K per instruction
+                    umma_bf16(tmem, ad + 2 * k, bd + 2 * k, idesc, (i | k) ? 1u : 0u);
+                umma_commit(&s.empty[st]);                 // the stage is free once these MMAs have read it
+            }
+            if (!failed) umma_commit(&s.acc_full);
+            else atomicExch(a.status, 2);
+        }
+    } else {
+        // ---- epilogue: warps 2..5, each owns the 32 lanes (rows) warp % 4 ----
+        const int quarter = warp & 3;
+        const int row = m0 + quarter * 32 + lane;
+        bool ready = mbar_wait(&s.acc_full, 0);
+        if (!ready) { failed = 3; if (lane == 0) atomicExch(a.status, 3); }
+        tc_fence_after();
+        if (ready) {
+            constexpr int OUT_COLS = EPI == EPI_SWIGLU ? BN / 2 : BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
+                unsigned v[32], u[32];
+                tmem_ld32(tmem + ((unsigned)(quarter * 32) << 16) + c0, v);
+                if (EPI == EPI_SWIGLU) tmem_ld32(tmem + ((unsigned)(quarter * 32) << 16) + BN / 2 + c0, u);
+                if (row >= a.M) continue;
+                const int col = n0 + c0;
+                if (EPI == EPI_F32 || EPI == EPI_RESIDUAL) {
+                    float *dst = reinterpret_cast<float *>(a.out) + (size_t)row * a.ldo + col;
+                    const bool vec = col + 32 <= a.N && (a.ldo & 3) == 0;
+                    if (vec) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                            if (EPI == EPI_RESIDUAL) {
+                                const float4 x = *reinterpret_cast<const float4 *>(dst + j);
+                                o = make_float4(x.x + a.scale * o.x, x.y + a.scale * o.y, x.z + a.scale * o.z, x.w + a.scale * o.w);
+                            }
+                            *reinterpret_cast<float4 *>(dst + j) = o;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col + j < a.N; ++j) {
+                            const float acc = __uint_as_float(v[j]);
+                            dst[j] = EPI == EPI_RESIDUAL ? dst[j] + a.scale * acc : acc;
+                        }
+                    }
+                } else {
+                    __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(a.out) + (size_t)row * a.ldo + col;
+                    float f[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float acc = __uint_as_float(v[j]);
+                        f[j] = EPI == EPI_SWIGLU ? acc / (1.f + expf(-acc)) * __uint_as_float(u[j]) : acc;
+                    }
+                    const bool vec = col + 32 <= a.N && (a.ldo & 7) == 0;
+                    if (vec) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 o;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(f[j], f[j + 1]), p1 = __floats2bfloat162_rn(f[j + 2], f[j + 3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(f[j + 4], f[j + 5]), p3 = __floats2bfloat162_rn(f[j + 6], f[j + 7]);
+                            o.x = *reinterpret_cast<unsigned *>(&p0); o.y = *reinterpret_cast<unsigned *>(&p1);
+                            o.z = *reinterpret_cast<unsigned *>(&p2); o.w = *reinterpret_cast<unsigned *>(&p3);
+                            *reinterpret_cast<uint4 *>(dst + j) = o;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col + j < a.N; ++j) dst[j] = __float2bfloat16_rn(f[j]);
+                    }
+                }
+            }
+        }
+    }
+    // A role that gave up leaves copies or MMAs in flight: give them a bounded time to land before
+    // the block's shared and tensor memory are released.
+    if (failed && lane == 0) {
+        for (int st = 0; st < TG_STAGES; ++st) mbar_wait(&s.full[st], 0);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem, BN);
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// Tensor maps are kept by (pointer, rows, cols, box rows): weights and step buffers come back with
+// the same addresses step after step.  (The reference keeps its operator descriptors in an LRU
+// cache keyed by shapes and strides: src/models/cache_manager.hpp:32-138.)
+static int tensor_map_2d(const void *ptr, int rows, int cols, int box_rows, CUtensorMap *out) {
+    using Key = std::tuple<const void *, int, int, int>;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    const Key key(ptr, rows, cols, box_rows);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return JK_OK; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: the driver has no cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(__nv_bfloat16)};
+    const cuuint32_t box[2] = {(cuuint32_t)TG_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: cuTensorMapEncodeTiled failed with %d", (int)r);
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = m;
+    *out = m;
+    return JK_OK;
+}
+
+template <int BN, int EPI>
+static int launch_tg(const CUtensorMap &ma, const CUtensorMap &mw, const TgArgs &a, cudaStream_t stream) {
+    const size_t smem = sizeof(TgSmem<BN>) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: %s", cudaGetErrorString(e));
+    const int out_cols = EPI == EPI_SWIGLU ? BN / 2 : BN;
+    dim3 grid((a.N + out_cols - 1) / out_cols, (a.M + TG_BM - 1) / TG_BM);
+    gemm_tcgen05_kernel<BN, EPI><<<grid, TG_THREADS, smem, stream>>>(ma, mw, a);
+    JK_CHECK_LAUNCH("gemm_tcgen05");
+    return JK_OK;
+}
+
+// K must keep rows 16-byte aligned for TMA; everything else is free.
+JK_EXPORT int jk_gemm_tcgen05_supports(int M, int N, int K) { return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0; }
+
+JK_EXPORT int jk_gemm_tcgen05(const void *act, const void *w, void *out, int M, int N, int K, int ldo, int epilogue,
+                              float scale, int *status, cudaStream_t stream) {
+    JK_REQUIRE(jk_gemm_tcgen05_supports(M, N, K), "gemm_tcgen05: M %d N %d K %d (K must be a multiple of 8)", M, N, K);
+    JK_REQUIRE(epilogue >= EPI_F32 && epilogue <= EPI_SWIGLU, "gemm_tcgen05: epilogue %d", epilogue);
+    JK_REQUIRE(ldo >= N && status != nullptr, "gemm_tcgen05: output stride %d < N %d, or no status word", ldo, N);
+    JK_REQUIRE((reinterpret_cast<uintptr_t>(act) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+               "gemm_tcgen05: operands must be 16-byte aligned");
+    const int w_rows = epilogue == EPI_SWIGLU ? 2 * N : N;
+    CUtensorMap ma, mw;
+    if (int rc = tensor_map_2d(act, M, K, TG_BM, &ma)) return rc;
+    TgArgs a{out, M, N, K, ldo, scale, status};
+    if (epilogue == EPI_SWIGLU) {
+        if (int rc = tensor_map_2d(w, w_rows, K, 128, &mw)) return rc;
+        return launch_tg<256, EPI_SWIGLU>(ma, mw, a, stream);
+    }
+    // a narrower tile when the matrix has few columns or wide tiles would leave most SMs idle
+    const int tiles_m = (M + TG_BM - 1) / TG_BM;
+    const bool narrow = N <= 128 || tiles_m * ((N + 255) / 256) < 120;
+    if (int rc = tensor_map_2d(w, w_rows, K, narrow ? 128 : 256, &mw)) return rc;
+#define TG_DISPATCH(BN_)                                                            \
+    switch (epilogue) {                                                             \
+        case EPI_F32: return launch_tg<BN_, EPI_F32>(ma, mw, a, stream);             \
+        case EPI_BF16: return launch_tg<BN_, EPI_BF16>(ma, mw, a, stream);           \
+        default: return launch_tg<BN_, EPI_RESIDUAL>(ma, mw, a, stream);             \
+    }
+    if (narrow) { TG_DISPATCH(128) }
+    TG_DISPATCH(256)
+#undef TG_DISPATCH
+}

@@ -198,6 +198,51 @@ def linear_small(act: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue
     return out
 
 
+TG_F32, TG_BF16, TG_RESIDUAL, TG_SWIGLU = 0, 1, 2, 3
+_tg_status = {}
+
+
+def gemm_status(device) -> torch.Tensor:
+    """The device word in which the tcgen05 product kernel records a wait that ran out (0: none)."""
+    key = str(device)
+    if key not in _tg_status:
+        _tg_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tg_status[key]
+
+
+def check_gemm_status(device) -> None:
+    """Read the status word (synchronises); raise if a kernel gave up waiting."""
+    key = str(device)
+    if key in _tg_status:
+        code = int(_tg_status[key].item())
+        if code:
+            _tg_status[key].zero_()
+            raise KernelError(f"gemm_tcgen05: a bounded wait ran out (role {code}: 1 TMA, 2 MMA, 3 epilogue); "
+                              "the step's results are not valid")
+
+
+def gemm_tcgen05_supports(m: int, n: int, k: int) -> bool:
+    return bool(_build.load("gemm_tcgen05").jk_gemm_tcgen05_supports(_c_int(m), _c_int(n), _c_int(k)))
+
+
+def gemm_tcgen05(act: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = TG_F32,
+                 scale: float = 1.0) -> torch.Tensor:
+    """out (op)= act @ w^T on the tcgen05 tensor cores, operands by TMA.  Epilogues: TG_F32 / TG_BF16 store,
+    TG_RESIDUAL ``out += scale * product`` (float32, in place), TG_SWIGLU ``w`` is [2N, K] (gate rows, up rows)
+    and ``out`` is bfloat16 [M, N] = silu(gate) * up."""
+    _need(act, "act", torch.bfloat16); _need(w, "w", torch.bfloat16)
+    _need(out, "out", torch.bfloat16 if epilogue in (TG_BF16, TG_SWIGLU) else torch.float32, contiguous=False)
+    m, k = act.shape
+    n = w.shape[0] // (2 if epilogue == TG_SWIGLU else 1)
+    if w.shape[1] != k or tuple(out.shape) != (m, n) or out.stride(1) != 1:
+        raise KernelError(f"gemm_tcgen05: act {tuple(act.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    lib = _build.load("gemm_tcgen05")
+    _check("gemm_tcgen05", lib.jk_gemm_tcgen05(_ptr(act), _ptr(w), _ptr(out), _c_int(m), _c_int(n), _c_int(k),
+                                               _c_int(out.stride(0)), _c_int(epilogue), _c_float(scale),
+                                               _ptr(gemm_status(act.device)), _stream()))
+    return out
+
+
 _SMS = {}
 
 

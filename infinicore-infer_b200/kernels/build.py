@@ -26,6 +26,7 @@ MODULES: Dict[str, List[str]] = {
     "attention": ["attention.cu"],
     "sampling": ["sampling.cu"],
     "linear_small": ["linear_small.cu"],
+    "gemm_tcgen05": ["gemm_tcgen05.cu"],
 }
 HEADERS = ["common.cuh", "attention_static_scratch.h"]
 

@@ -372,3 +372,51 @@ def test_linear_small_refuses_what_it_cannot_take(K):
     with pytest.raises(K.KernelError, match="outside what the kernel takes"):
         K.linear_small(torch.zeros(4, 80, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 80, dtype=torch.bfloat16, device=DEV),
                        torch.zeros(4, 8, device=DEV))
+
+
+TG_SHAPES = [(128, 256, 64), (128, 128, 128), (1, 8, 8), (300, 520, 200), (257, 100, 2304), (512, 6912, 2304), (2048, 2304, 5760)]
+
+
+@pytest.mark.parametrize("M,N,K_", TG_SHAPES)
+@pytest.mark.parametrize("epi", ["f32", "bf16", "residual"])
+def test_gemm_tcgen05_with_store_and_residual_epilogues(K, M, N, K_, epi):
+    g = torch.Generator().manual_seed(M + N + K_)
+    act = torch.randn(M, K_, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+    want = act.double() @ w.double().T
+    assert K.gemm_tcgen05_supports(M, N, K_)
+    if epi == "f32":
+        out = torch.full((M, N), 9.0, device=DEV)
+        K.gemm_tcgen05(act.to(DEV), w.to(DEV), out, K.TG_F32)
+        K.check_gemm_status(DEV)
+        torch.testing.assert_close(out.double().cpu(), want, rtol=1e-4, atol=1e-4)
+    elif epi == "bf16":
+        out = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=DEV)
+        K.gemm_tcgen05(act.to(DEV), w.to(DEV), out, K.TG_BF16)
+        K.check_gemm_status(DEV)
+        _close(out, want, torch.bfloat16, scale=2.0)
+    else:
+        x = torch.randn(M, N, generator=g)
+        out = x.to(DEV).clone()
+        K.gemm_tcgen05(act.to(DEV), w.to(DEV), out, K.TG_RESIDUAL, scale=0.7)
+        K.check_gemm_status(DEV)
+        torch.testing.assert_close(out.double().cpu(), x.double() + 0.7 * want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (300, 136, 96), (2048, 5760, 2304), (77, 520, 200)])
+def test_gemm_tcgen05_with_swiglu_epilogue(K, M, N, K_):
+    g = torch.Generator().manual_seed(M * 3 + N)
+    act = torch.randn(M, K_, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * N, K_, generator=g) * 2 / math.sqrt(K_)).to(torch.bfloat16)
+    out = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=DEV)
+    K.gemm_tcgen05(act.to(DEV), w.to(DEV), out, K.TG_SWIGLU)
+    K.check_gemm_status(DEV)
+    gu = act.double() @ w.double().T
+    _close(out, gu[:, :N] * torch.sigmoid(gu[:, :N]) * gu[:, N:], torch.bfloat16, scale=2.0)
+
+
+def test_gemm_tcgen05_refuses_rows_that_tma_cannot_address(K):
+    assert not K.gemm_tcgen05_supports(4, 4, 20)
+    with pytest.raises(K.KernelError, match="multiple of 8"):
+        K.gemm_tcgen05(torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV), torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV),
+                       torch.zeros(4, 4, device=DEV))
