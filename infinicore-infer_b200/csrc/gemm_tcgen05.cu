@@ -8,8 +8,12 @@
 //              by one elected thread, float32 accumulator in tensor memory (BN columns x 128 lanes);
 //              tcgen05.commit hands a finished stage back to the TMA warp and the finished
 //              accumulator to the epilogue;
+//   tiles      a block is persistent: it walks over output tiles with two accumulators in tensor
+//              memory, so that the epilogue of one tile runs while the next tile's products are issued;
 //   epilogue   four warps read the accumulator with tcgen05.ld (each warp its quarter of the
-//              lanes; a thread holds 32 consecutive columns of one row) and apply one of
+//              lanes; a thread holds 32 consecutive columns of one row), stage 32 rows x 128 bytes in
+//              swizzled shared memory and hand them to TMA (a store, or a reduce-add for the residual:
+//              the memory system does x += value, the SM never reads x) and apply one of
 //                EPI_F32       out[m, n]  = acc                      float32
 //                EPI_BF16      out[m, n]  = acc                      bfloat16
 //                EPI_RESIDUAL  out[m, n] += scale * acc              float32, in place (the residual stream)
@@ -41,6 +45,7 @@ struct TgArgs {
     int M, N, K, ldo;
     float scale;
     int *status;       // device word: 0, or the code of the wait that ran out
+    int direct;        // 1: the output's rows are not 16-byte aligned, store from registers instead of by TMA
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -98,6 +103,22 @@ __device__ __forceinline__ void tmem_ld32(unsigned addr, unsigned (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void *smem, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+                 ::"l"(map), "r"(smem_u32(smem)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, const void *smem, int c0, int c1) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];\n"
+                 ::"l"(map), "r"(smem_u32(smem)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
 // Shared-memory matrix descriptor of a K-major tile [rows][64 bf16] written by TMA with the
 // 128-byte swizzle: rows are 128 bytes, groups of 8 rows are 1024 bytes apart (stride byte offset),
 // the leading byte offset is unused for swizzled K-major tiles (1), version 1, layout type 2.
@@ -113,28 +134,37 @@ __host__ __device__ constexpr unsigned instr_desc_bf16(int bn) {
 template <int BN> struct TgSmem {
     __nv_bfloat16 a[TG_STAGES][TG_BM * TG_BK];       // 16 KB each, 1024-byte aligned
     __nv_bfloat16 b[TG_STAGES][BN * TG_BK];
-    unsigned long long full[TG_STAGES], empty[TG_STAGES], acc_full;
+    unsigned char stage_out[4][4096];                // per epilogue warp: 32 rows x 128 bytes, swizzled
+    unsigned long long full[TG_STAGES], empty[TG_STAGES], acc_full[2], acc_empty[2];
     unsigned tmem_base;
 };
 
+// One 16-byte piece of a staging row: piece `chunk` of row `row` sits at chunk ^ (row & 7), the
+// 128-byte swizzle that the output's tensor map undoes.
+__device__ __forceinline__ void stage_write(unsigned char *tile, int row, int chunk, uint4 v) {
+    *reinterpret_cast<uint4 *>(tile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
+}
+
 template <int BN, int EPI>
 __global__ void __launch_bounds__(TG_THREADS)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, TgArgs a) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_out, TgArgs a) {
     extern __shared__ unsigned char tg_raw[];
     TgSmem<BN> &s = *reinterpret_cast<TgSmem<BN> *>((reinterpret_cast<uintptr_t>(tg_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TG_BM;
-    // EPI_SWIGLU: the tile's B rows are BN/2 gate rows and the BN/2 up rows that belong to them
-    const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? BN / 2 : BN);
-    const int nk = (a.K + TG_BK - 1) / TG_BK;
+    // EPI_SWIGLU: a tile's B rows are BN/2 gate rows and the BN/2 up rows that belong to them
+    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? BN / 2 : BN;
     constexpr unsigned STAGE_BYTES = (TG_BM + BN) * TG_BK * sizeof(__nv_bfloat16);
+    const int tiles_n = (a.N + OUT_COLS - 1) / OUT_COLS;
+    const int num_tiles = tiles_n * ((a.M + TG_BM - 1) / TG_BM);
+    const int nk = (a.K + TG_BK - 1) / TG_BK;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < TG_STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
-        mbar_init(&s.acc_full, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&s.acc_full[i], 1); mbar_init(&s.acc_empty[i], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(&s.tmem_base, BN);
+    if (warp == 1) tmem_alloc(&s.tmem_base, 2 * BN);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -144,16 +174,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 0) {
         // ---- TMA producer ----
         if (lane == 0) {
-            for (int i = 0; i < nk; ++i) {
-                const int st = i % TG_STAGES;
-                if (i >= TG_STAGES && !mbar_wait(&s.empty[st], ((i / TG_STAGES) - 1) & 1)) { failed = 1; break; }
-                mbar_expect_tx(&s.full[st], STAGE_BYTES);
-                tma_load_2d(s.a[st], &map_a, &s.full[st], i * TG_BK, m0);
-                if (EPI == EPI_SWIGLU) {
+            int it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
+                const int m0 = (tile / tiles_n) * TG_BM, n0 = (tile % tiles_n) * OUT_COLS;
+                for (int i = 0; i < nk; ++i, ++it) {
+                    const int st = it % TG_STAGES;
+                    if (it >= TG_STAGES && !mbar_wait(&s.empty[st], ((it / TG_STAGES) - 1) & 1)) { failed = 1; break; }
+                    mbar_expect_tx(&s.full[st], STAGE_BYTES);
+                    tma_load_2d(s.a[st], &map_a, &s.full[st], i * TG_BK, m0);
                     tma_load_2d(s.b[st], &map_w, &s.full[st], i * TG_BK, n0);
-                    tma_load_2d(s.b[st] + (BN / 2) * TG_BK, &map_w, &s.full[st], i * TG_BK, a.N + n0);
-                } else {
-                    tma_load_2d(s.b[st], &map_w, &s.full[st], i * TG_BK, n0);
+                    if (EPI == EPI_SWIGLU)
+                        tma_load_2d(s.b[st] + (BN / 2) * TG_BK, &map_w, &s.full[st], i * TG_BK, a.N + n0);
                 }
             }
             if (failed) atomicExch(a.status, 1);
@@ -162,79 +193,109 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ---- MMA issuer ----
         if (lane == 0) {
             constexpr unsigned idesc = instr_desc_bf16(BN);
-            for (int i = 0; i < nk; ++i) {
-                const int st = i % TG_STAGES;
-                if (!mbar_wait(&s.full[st], (i / TG_STAGES) & 1)) { failed = 2; break; }
+            int it = 0, j = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x, ++j) {
+                const int buf = j & 1;
+                if (j >= 2 && !mbar_wait(&s.acc_empty[buf], ((j >> 1) - 1) & 1)) { failed = 2; break; }
                 tc_fence_after();
-                const unsigned long long ad = smem_desc_sw128(s.a[st]), bd = smem_desc_sw128(s.b[st]);
+                const unsigned acc = tmem + buf * BN;
+                for (int i = 0; i < nk; ++i, ++it) {
+                    const int st = it % TG_STAGES;
+                    if (!mbar_wait(&s.full[st], (it / TG_STAGES) & 1)) { failed = 2; break; }
+                    tc_fence_after();
+                    const unsigned long long ad = smem_desc_sw128(s.a[st]), bd = smem_desc_sw128(s.b[st]);
 #pragma unroll
-                for (int k = 0; k < TG_BK / 16; ++k)      // 32 bytes further along K per instruction
-                    umma_bf16(tmem, ad + 2 * k, bd + 2 * k, idesc, (i | k) ? 1u : 0u);
-                umma_commit(&s.empty[st]);                 // the stage is free once these MMAs have read it
+                    for (int k = 0; k < TG_BK / 16; ++k)      // 32 bytes further along K per instruction
+                        umma_bf16(acc, ad + 2 * k, bd + 2 * k, idesc, (i | k) ? 1u : 0u);
+                    umma_commit(&s.empty[st]);                 // the stage is free once these MMAs have read it
+                }
+                if (!failed) umma_commit(&s.acc_full[buf]);
             }
-            if (!failed) umma_commit(&s.acc_full);
-            else atomicExch(a.status, 2);
+            if (failed) atomicExch(a.status, 2);
         }
     } else {
-        // ---- epilogue: warps 2..5, each owns the 32 lanes (rows) warp % 4 ----
+        // ---- epilogue: warps 2..5, each owns the 32 lanes (rows) warp % 4 of the accumulator ----
         const int quarter = warp & 3;
-        const int row = m0 + quarter * 32 + lane;
-        bool ready = mbar_wait(&s.acc_full, 0);
-        if (!ready) { failed = 3; if (lane == 0) atomicExch(a.status, 3); }
-        tc_fence_after();
-        if (ready) {
-            constexpr int OUT_COLS = EPI == EPI_SWIGLU ? BN / 2 : BN;
+        unsigned char *stage = s.stage_out[quarter];
+        int j = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
+            const int m0 = (tile / tiles_n) * TG_BM, n0 = (tile % tiles_n) * OUT_COLS;
+            const int buf = j & 1;
+            if (!mbar_wait(&s.acc_full[buf], (j >> 1) & 1)) { failed = 3; if (lane == 0) atomicExch(a.status, 3); break; }
+            tc_fence_after();
+            const unsigned acc = tmem + buf * BN + ((unsigned)(quarter * 32) << 16);
+            const int row0 = m0 + quarter * 32, row = row0 + lane;
+            // columns per pass: a staging row is 128 bytes = 32 floats or 64 bfloat16
+            constexpr int PASS = (EPI == EPI_F32 || EPI == EPI_RESIDUAL) ? 32 : 64;
 #pragma unroll 1
-            for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
-                unsigned v[32], u[32];
-                tmem_ld32(tmem + ((unsigned)(quarter * 32) << 16) + c0, v);
-                if (EPI == EPI_SWIGLU) tmem_ld32(tmem + ((unsigned)(quarter * 32) << 16) + BN / 2 + c0, u);
-                if (row >= a.M) continue;
+            for (int c0 = 0; c0 < OUT_COLS; c0 += PASS) {
                 const int col = n0 + c0;
-                if (EPI == EPI_F32 || EPI == EPI_RESIDUAL) {
-                    float *dst = reinterpret_cast<float *>(a.out) + (size_t)row * a.ldo + col;
-                    const bool vec = col + 32 <= a.N && (a.ldo & 3) == 0;
-                    if (vec) {
+                if (col >= a.N) break;                                     // warp-uniform
+                if (!a.direct) {
+                    if (lane == 0) bulk_wait_read();                       // the staging tile's last store has read it
+                    __syncwarp();
+                }
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                            if (EPI == EPI_RESIDUAL) {
-                                const float4 x = *reinterpret_cast<const float4 *>(dst + j);
-                                o = make_float4(x.x + a.scale * o.x, x.y + a.scale * o.y, x.z + a.scale * o.z, x.w + a.scale * o.w);
-                            }
-                            *reinterpret_cast<float4 *>(dst + j) = o;
-                        }
-                    } else {
-                        for (int j = 0; j < 32 && col + j < a.N; ++j) {
-                            const float acc = __uint_as_float(v[j]);
-                            dst[j] = EPI == EPI_RESIDUAL ? dst[j] + a.scale * acc : acc;
-                        }
-                    }
-                } else {
-                    __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(a.out) + (size_t)row * a.ldo + col;
+                for (int half = 0; half < PASS / 32; ++half) {
+                    unsigned v[32];
+                    tmem_ld32(acc + c0 + half * 32, v);
                     float f[32];
+                    if (EPI == EPI_SWIGLU) {
+                        unsigned u[32];
+                        tmem_ld32(acc + BN / 2 + c0 + half * 32, u);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float acc = __uint_as_float(v[j]);
-                        f[j] = EPI == EPI_SWIGLU ? acc / (1.f + expf(-acc)) * __uint_as_float(u[j]) : acc;
-                    }
-                    const bool vec = col + 32 <= a.N && (a.ldo & 7) == 0;
-                    if (vec) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            uint4 o;
-                            __nv_bfloat162 p0 = __floats2bfloat162_rn(f[j], f[j + 1]), p1 = __floats2bfloat162_rn(f[j + 2], f[j + 3]);
-                            __nv_bfloat162 p2 = __floats2bfloat162_rn(f[j + 4], f[j + 5]), p3 = __floats2bfloat162_rn(f[j + 6], f[j + 7]);
-                            o.x = *reinterpret_cast<unsigned *>(&p0); o.y = *reinterpret_cast<unsigned *>(&p1);
-                            o.z = *reinterpret_cast<unsigned *>(&p2); o.w = *reinterpret_cast<unsigned *>(&p3);
-                            *reinterpret_cast<uint4 *>(dst + j) = o;
+                        for (int i = 0; i < 32; ++i) {
+                            const float g = __uint_as_float(v[i]);
+                            f[i] = g / (1.f + expf(-g)) * __uint_as_float(u[i]);
                         }
                     } else {
-                        for (int j = 0; j < 32 && col + j < a.N; ++j) dst[j] = __float2bfloat16_rn(f[j]);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]) * (EPI == EPI_RESIDUAL ? a.scale : 1.f);
+                    }
+                    if (a.direct) {
+                        // rows of the output are not 16-byte aligned: plain guarded stores
+                        if (row < a.M) {
+                            for (int i = 0; i < 32; ++i) {
+                                const int c = col + half * 32 + i;
+                                if (c >= a.N) break;
+                                if (EPI == EPI_F32) reinterpret_cast<float *>(a.out)[(size_t)row * a.ldo + c] = f[i];
+                                else if (EPI == EPI_RESIDUAL) reinterpret_cast<float *>(a.out)[(size_t)row * a.ldo + c] += f[i];
+                                else reinterpret_cast<__nv_bfloat16 *>(a.out)[(size_t)row * a.ldo + c] = __float2bfloat16_rn(f[i]);
+                            }
+                        }
+                    } else if (PASS == 32) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            stage_write(stage, lane, i, make_uint4(__float_as_uint(f[4 * i]), __float_as_uint(f[4 * i + 1]),
+                                                                   __float_as_uint(f[4 * i + 2]), __float_as_uint(f[4 * i + 3])));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(f[8 * i], f[8 * i + 1]), p1 = __floats2bfloat162_rn(f[8 * i + 2], f[8 * i + 3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(f[8 * i + 4], f[8 * i + 5]), p3 = __floats2bfloat162_rn(f[8 * i + 6], f[8 * i + 7]);
+                            stage_write(stage, lane, half * 4 + i,
+                                        make_uint4(*reinterpret_cast<unsigned *>(&p0), *reinterpret_cast<unsigned *>(&p1),
+                                                   *reinterpret_cast<unsigned *>(&p2), *reinterpret_cast<unsigned *>(&p3)));
+                        }
+                    }
+                }
+                if (!a.direct) {
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && row0 < a.M) {
+                        // TMA clips what lies beyond the matrix; the box starts inside it, never at a negative coordinate
+                        if (EPI == EPI_RESIDUAL) tma_reduce_add_2d(&map_out, stage, col, row0);
+                        else tma_store_2d(&map_out, stage, col, row0);
+                        bulk_commit();
                     }
                 }
             }
+            // this warp has read all it needs of the accumulator: hand the buffer back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
         }
+        if (lane == 0) bulk_wait_all();
     }
     // A role that gave up leaves copies or MMAs in flight: give them a bounded time to land before
     // the block's shared and tensor memory are released.
@@ -244,7 +305,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 1) tmem_dealloc(tmem, BN);
+    if (warp == 1) tmem_dealloc(tmem, 2 * BN);
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -265,27 +326,28 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// Tensor maps are kept by (pointer, rows, cols, box rows): weights and step buffers come back with
-// the same addresses step after step.  (The reference keeps its operator descriptors in an LRU
-// cache keyed by shapes and strides: src/models/cache_manager.hpp:32-138.)
-static int tensor_map_2d(const void *ptr, int rows, int cols, int box_rows, CUtensorMap *out) {
-    using Key = std::tuple<const void *, int, int, int>;
+// Tensor maps are kept by (pointer, shape, box, type): weights and step buffers come back with the
+// same addresses step after step.  (The reference keeps its operator descriptors in an LRU cache
+// keyed by shapes and strides: src/models/cache_manager.hpp:32-138.)
+static int tensor_map_2d(const void *ptr, int rows, int cols, int ld, int box_rows, int box_cols, int elem_bytes,
+                         CUtensorMap *out) {
+    using Key = std::tuple<const void *, int, int, int, int, int, int>;
     static std::map<Key, CUtensorMap> cache;
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
-    const Key key(ptr, rows, cols, box_rows);
+    const Key key(ptr, rows, cols, ld, box_rows, box_cols, elem_bytes);
     auto it = cache.find(key);
     if (it != cache.end()) { *out = it->second; return JK_OK; }
     EncodeTiledFn fn = encode_fn();
     if (!fn) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: the driver has no cuTensorMapEncodeTiled");
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(__nv_bfloat16)};
-    const cuuint32_t box[2] = {(cuuint32_t)TG_BK, (cuuint32_t)box_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t elem[2] = {1, 1};
     CUtensorMap m;
-    const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = fn(&m, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                          const_cast<void *>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: cuTensorMapEncodeTiled failed with %d", (int)r);
     if (cache.size() > 4096) cache.clear();
     cache[key] = m;
@@ -294,13 +356,14 @@ static int tensor_map_2d(const void *ptr, int rows, int cols, int box_rows, CUte
 }
 
 template <int BN, int EPI>
-static int launch_tg(const CUtensorMap &ma, const CUtensorMap &mw, const TgArgs &a, cudaStream_t stream) {
+static int launch_tg(const CUtensorMap &ma, const CUtensorMap &mw, const CUtensorMap &mo, const TgArgs &a, int sms,
+                     cudaStream_t stream) {
     const size_t smem = sizeof(TgSmem<BN>) + 1024;
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: %s", cudaGetErrorString(e));
     const int out_cols = EPI == EPI_SWIGLU ? BN / 2 : BN;
-    dim3 grid((a.N + out_cols - 1) / out_cols, (a.M + TG_BM - 1) / TG_BM);
-    gemm_tcgen05_kernel<BN, EPI><<<grid, TG_THREADS, smem, stream>>>(ma, mw, a);
+    const int tiles = ((a.N + out_cols - 1) / out_cols) * ((a.M + TG_BM - 1) / TG_BM);
+    gemm_tcgen05_kernel<BN, EPI><<<tiles < sms ? tiles : sms, TG_THREADS, smem, stream>>>(ma, mw, mo, a);
     JK_CHECK_LAUNCH("gemm_tcgen05");
     return JK_OK;
 }
@@ -309,29 +372,35 @@ static int launch_tg(const CUtensorMap &ma, const CUtensorMap &mw, const TgArgs 
 JK_EXPORT int jk_gemm_tcgen05_supports(int M, int N, int K) { return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0; }
 
 JK_EXPORT int jk_gemm_tcgen05(const void *act, const void *w, void *out, int M, int N, int K, int ldo, int epilogue,
-                              float scale, int *status, cudaStream_t stream) {
+                              float scale, int *status, int sms, cudaStream_t stream) {
     JK_REQUIRE(jk_gemm_tcgen05_supports(M, N, K), "gemm_tcgen05: M %d N %d K %d (K must be a multiple of 8)", M, N, K);
     JK_REQUIRE(epilogue >= EPI_F32 && epilogue <= EPI_SWIGLU, "gemm_tcgen05: epilogue %d", epilogue);
     JK_REQUIRE(ldo >= N && status != nullptr, "gemm_tcgen05: output stride %d < N %d, or no status word", ldo, N);
     JK_REQUIRE((reinterpret_cast<uintptr_t>(act) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
                "gemm_tcgen05: operands must be 16-byte aligned");
+    if (sms <= 0) sms = 148;
     const int w_rows = epilogue == EPI_SWIGLU ? 2 * N : N;
-    CUtensorMap ma, mw;
-    if (int rc = tensor_map_2d(act, M, K, TG_BM, &ma)) return rc;
-    TgArgs a{out, M, N, K, ldo, scale, status};
+    const int out_bytes = (epilogue == EPI_F32 || epilogue == EPI_RESIDUAL) ? 4 : 2;
+    CUtensorMap ma, mw, mo;
+    if (int rc = tensor_map_2d(act, M, K, K, TG_BM, TG_BK, 2, &ma)) return rc;
+    TgArgs a{out, M, N, K, ldo, scale, status, 0};
+    // the output goes out by TMA when its rows are 16-byte aligned, else straight from registers
+    a.direct = ((size_t)ldo * out_bytes) % 16 != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0;
+    if (a.direct) mo = ma;
+    else if (int rc = tensor_map_2d(out, M, N, ldo, 32, 128 / out_bytes, out_bytes, &mo)) return rc;
     if (epilogue == EPI_SWIGLU) {
-        if (int rc = tensor_map_2d(w, w_rows, K, 128, &mw)) return rc;
-        return launch_tg<256, EPI_SWIGLU>(ma, mw, a, stream);
+        if (int rc = tensor_map_2d(w, w_rows, K, K, 128, TG_BK, 2, &mw)) return rc;
+        return launch_tg<256, EPI_SWIGLU>(ma, mw, mo, a, sms, stream);
     }
-    // a narrower tile when the matrix has few columns or wide tiles would leave most SMs idle
+    // a narrower tile when wide tiles would leave most SMs without one
     const int tiles_m = (M + TG_BM - 1) / TG_BM;
-    const bool narrow = N <= 128 || tiles_m * ((N + 255) / 256) < 120;
-    if (int rc = tensor_map_2d(w, w_rows, K, narrow ? 128 : 256, &mw)) return rc;
-#define TG_DISPATCH(BN_)                                                            \
-    switch (epilogue) {                                                             \
-        case EPI_F32: return launch_tg<BN_, EPI_F32>(ma, mw, a, stream);             \
-        case EPI_BF16: return launch_tg<BN_, EPI_BF16>(ma, mw, a, stream);           \
-        default: return launch_tg<BN_, EPI_RESIDUAL>(ma, mw, a, stream);             \
+    const bool narrow = N <= 128 || tiles_m * ((N + 255) / 256) < sms * 3 / 4;
+    if (int rc = tensor_map_2d(w, w_rows, K, K, narrow ? 128 : 256, TG_BK, 2, &mw)) return rc;
+#define TG_DISPATCH(BN_)                                                                 \
+    switch (epilogue) {                                                                  \
+        case EPI_F32: return launch_tg<BN_, EPI_F32>(ma, mw, mo, a, sms, stream);         \
+        case EPI_BF16: return launch_tg<BN_, EPI_BF16>(ma, mw, mo, a, sms, stream);       \
+        default: return launch_tg<BN_, EPI_RESIDUAL>(ma, mw, mo, a, sms, stream);         \
     }
     if (narrow) { TG_DISPATCH(128) }
     TG_DISPATCH(256)

@@ -239,7 +239,7 @@ def gemm_tcgen05(act: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue
     lib = _build.load("gemm_tcgen05")
     _check("gemm_tcgen05", lib.jk_gemm_tcgen05(_ptr(act), _ptr(w), _ptr(out), _c_int(m), _c_int(n), _c_int(k),
                                                _c_int(out.stride(0)), _c_int(epilogue), _c_float(scale),
-                                               _ptr(gemm_status(act.device)), _stream()))
+                                               _ptr(gemm_status(act.device)), _c_int(_sm_count(act.device)), _stream()))
     return out
 
 
