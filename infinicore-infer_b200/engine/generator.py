@@ -50,6 +50,7 @@ class Generator:
                   for s in samplers]
         # the uniform of a new token depends on the request's seed and the token's absolute position
         new = self.sampler.sample(logits, params, [len(s.request.prompt) + len(s.request.generated) for s in samplers])
+        self.engine.check()
         it = iter(new)
         sampled = [next(it) if s.samples else None for s in plan]
         self.scheduler.complete(plan, sampled)

@@ -113,6 +113,11 @@ class Engine:
     def end(self, req_id) -> None:
         self.cache.release(req_id)
 
+    def check(self) -> None:
+        """Raise if a kernel of an earlier step gave up a bounded wait (reads one word; synchronises)."""
+        from .. import kernels
+        kernels.check_gemm_status(self.device)
+
     def position(self, req_id) -> int:
         return self.cache.length(req_id) if self.cache.is_live(req_id) else 0
 

@@ -1,6 +1,6 @@
 """Parts of a model: norm, position encoding, mixer, feed-forward, block; and the model built of them."""
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, SHORT_ROWS, TILE_ROWS, ResidualStream,
-                   Runtime, StepContext, part_class, register)
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, SHORT_ROWS, TILE_ROWS, PendingProduct,
+                   ResidualStream, Runtime, StepContext, part_class, register)
 from .norm import RMSNorm
 from .rope import RotaryTables
 from .attention import Attention
@@ -8,6 +8,6 @@ from .feed_forward import SwiGLU
 from .block import PreNormBlock
 from .model import Model, cache_needs, model_manifest
 
-__all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "ResidualStream", "Runtime",
+__all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "ResidualStream", "PendingProduct", "Runtime",
            "StepContext", "SHORT_ROWS", "TILE_ROWS", "part_class", "register", "RMSNorm", "RotaryTables", "Attention", "SwiGLU",
            "PreNormBlock", "Model", "cache_needs", "model_manifest"]

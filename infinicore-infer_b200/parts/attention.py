@@ -64,7 +64,7 @@ class Attention:
                         T, s.num_heads, s.num_kv_heads, s.head_dim, write_cache=writes_cache)
         o = rt.empty(T, s.num_heads * s.head_dim)
         self._attend(q, o, view, table, ctx)
-        return rt.linear(o, self.w_o, out_dtype=torch.float32)
+        return rt.product(o, self.w_o)       # the block adds it to the residual stream
 
     def _attend(self, q, o, view, table, ctx) -> None:
         """float32: one warp per (row, head), the same arithmetic whatever the batch.  bfloat16: rows of

@@ -7,8 +7,8 @@ it is in, not the other layers.  Four registries hold the four families:
     norm            forward(residual, ctx, out_scale=1.0, rows=None) -> tensor [rows, size]
     position        tables for a mixer; an object the mixer knows how to use
     mixer           cache_need(spec) -> PagedKV | StateSlot | None   (static)
-                    forward(h, ctx, view, writes_cache) -> tensor [T, hidden]
-    feed_forward    forward(h, ctx) -> tensor [T, hidden]
+                    forward(h, ctx, view, writes_cache) -> tensor [T, hidden] or PendingProduct
+    feed_forward    forward(h, ctx) -> tensor [T, hidden] or PendingProduct
     block           forward(residual, ctx, view, writes_cache) -> None
 
 Every part class also has ``tensor_decls(spec) -> {local name: TensorDecl}``, a static
@@ -79,10 +79,15 @@ class Runtime:
             return kernels.gemm_f32(h, weight, out, bias)
         out_dtype = out_dtype or torch.bfloat16
         m, k = h.shape
-        if (out_dtype == torch.float32 and bias is None and m <= 16 and not self.library_products_only
-                and kernels.linear_small_supports(m, weight.shape[0], k)):
-            out = self.empty(m, weight.shape[0], dtype=torch.float32)
-            return kernels.linear_small(h, weight, out)
+        n = weight.shape[0]
+        if not self.library_products_only:
+            if out_dtype == torch.float32 and m <= 16 and kernels.linear_small_supports(m, n, k):
+                out = kernels.linear_small(h, weight, self.empty(m, n, dtype=torch.float32))
+                return out if bias is None else out.add_(bias)
+            if self.takes_tcgen05(m, n, k):
+                out = kernels.gemm_tcgen05(h, weight, self.empty(m, n, dtype=out_dtype),
+                                           kernels.TG_F32 if out_dtype == torch.float32 else kernels.TG_BF16)
+                return out if bias is None else out.add_(bias.to(out.dtype))
         if out_dtype == torch.bfloat16:
             out = torch.mm(h, weight.t())
         else:
@@ -98,11 +103,50 @@ class Runtime:
         m, k = h.shape
         di = w_gate_up.shape[0] // 2
         act = self.empty(m, di)
-        if (self.dtype == torch.bfloat16 and m <= 16 and not self.library_products_only
-                and kernels.linear_small_supports(m, di, k)):
-            return kernels.linear_small(h, w_gate_up, act, kernels.EPI_SWIGLU)
+        if self.dtype == torch.bfloat16 and not self.library_products_only:
+            if m <= 16 and kernels.linear_small_supports(m, di, k):
+                return kernels.linear_small(h, w_gate_up, act, kernels.EPI_SWIGLU)
+            if self.takes_tcgen05(m, di, k):
+                return kernels.gemm_tcgen05(h, w_gate_up, act, kernels.TG_SWIGLU)
         gu = self.linear(h, w_gate_up, out_dtype=torch.float32)
         return kernels.swiglu(gu, act)
+
+    def product(self, act: torch.Tensor, weight: torch.Tensor) -> "PendingProduct":
+        """act @ weight^T that has not run yet: whoever takes it decides where the result goes (a
+        tensor of its own, or straight into the residual stream)."""
+        return PendingProduct(self, act, weight)
+
+    def takes_tcgen05(self, m: int, n: int, k: int) -> bool:
+        """The tcgen05 kernel works on tiles of 128 rows: it takes a product that has enough tiles to
+        fill most of the GPU; below that (a few dozen rows) the library's small-row kernels are used."""
+        from .. import kernels
+        if self.dtype != torch.bfloat16 or self.library_products_only or m <= 16:
+            return False
+        tiles = -(-m // 128) * -(-n // 128)
+        return tiles >= 96 and kernels.gemm_tcgen05_supports(m, n, k)
+
+    def fuses_residual(self, m: int, n: int, k: int) -> bool:
+        return self.takes_tcgen05(m, n, k)
+
+
+class PendingProduct:
+    """A matrix product put off until its consumer is known (see ``ResidualStream.add``)."""
+
+    def __init__(self, runtime: Runtime, act: torch.Tensor, weight: torch.Tensor):
+        self.runtime, self.act, self.weight = runtime, act, weight
+
+    def tensor(self, out_dtype: Optional[torch.dtype] = torch.float32) -> torch.Tensor:
+        return self.runtime.linear(self.act, self.weight, out_dtype=out_dtype)
+
+    def add_into(self, x: torch.Tensor, scale: float) -> bool:
+        """x += scale * product in the product's own epilogue, if the runtime has such a kernel."""
+        from .. import kernels
+        m, k = self.act.shape
+        n = self.weight.shape[0]
+        if not self.runtime.fuses_residual(m, n, k):
+            return False
+        kernels.gemm_tcgen05(self.act, self.weight, x, kernels.TG_RESIDUAL, scale)
+        return True
 
 
 SHORT_ROWS = 8      # a request with at most this many rows in a step counts as "few rows"
@@ -153,9 +197,15 @@ class ResidualStream:
         self.delta: Optional[torch.Tensor] = None
         self.scale: float = 1.0
 
-    def add(self, delta: torch.Tensor, scale: float = 1.0) -> None:
+    def add(self, delta, scale: float = 1.0) -> None:
+        """x += scale * delta, now or at the next norm.  ``delta`` is a tensor or a ``PendingProduct``;
+        a pending product is added by its own epilogue where the runtime can do that."""
         if self.delta is not None:
             self.value()
+        if isinstance(delta, PendingProduct):
+            if delta.add_into(self.x, scale):
+                return
+            delta = delta.tensor(torch.float32)
         self.delta, self.scale = delta, scale
 
     def take_pending(self):

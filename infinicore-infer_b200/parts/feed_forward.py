@@ -34,4 +34,4 @@ class SwiGLU:
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
         rt = self.runtime
         act = rt.gate_up_swiglu(h, self.w_gate_up)
-        return rt.linear(act, self.w_down, out_dtype=torch.float32)
+        return rt.product(act, self.w_down)      # the block adds it to the residual stream

@@ -49,6 +49,7 @@ def replay(engine, records, out_dir=None, on_done=None):
                 os.replace(tmp, os.path.join(out_dir, f"{step}.f32"))
         else:
             torch.cuda.synchronize()
+        engine.check()
         for rid in rec.get("end", ()):
             if engine.cache.is_live(rid):
                 engine.end(rid)
