@@ -40,6 +40,8 @@ constexpr int ROW_MAX_DH = 512;
 template <typename T, int NS>     // NS: slices of 32 elements that cover one head
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 attention_row_kernel(AttnArgs a) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float q_smem[];          // [ROW_WARPS][dh]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.y;
@@ -128,7 +130,7 @@ JK_EXPORT int jk_attention_rows(const void *q, const void *k_pages, const void *
     JK_REQUIRE(T <= 65535, "attention: %d rows exceed one launch (65535)", T);
     dim3 grid((nh + ROW_WARPS - 1) / ROW_WARPS, T);
     const size_t smem = (size_t)ROW_WARPS * dh * sizeof(float);
-#define LAUNCH_ROWS(T, NS) attention_row_kernel<T, NS><<<grid, ROW_WARPS * 32, smem, stream>>>(a)
+#define LAUNCH_ROWS(T, NS) jk_launch(attention_row_kernel<T, NS>, grid, dim3(ROW_WARPS * 32), smem, stream, a)
 #define LAUNCH_ROWS_T(T)                                \
     do {                                                \
         if (dh <= 32) LAUNCH_ROWS(T, 1);                \
@@ -206,6 +208,8 @@ __device__ __forceinline__ void bf16x8_to_float(const uint4 &raw, float (&f)[8])
 template <int LPR, int HG, bool POW2>   // lanes per key row, query heads per block, page size a power of two
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_kernel(DecodeArgs a) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int GROUPS = DEC_WARPS * 32 / LPR;
     const int split = blockIdx.x;
     const int g = a.nh / a.nkvh;
@@ -384,6 +388,8 @@ attention_decode_kernel(DecodeArgs a) {
 
 // One block per (query head, row): merge the splits' partial results.
 __global__ void attention_combine_kernel(DecodeArgs a) {
+    pdl_trigger();
+    pdl_wait();
     const int h = blockIdx.x, ri = blockIdx.y;
     const int t = a.rows ? a.rows[ri] : ri;
     const size_t base = ((size_t)ri * a.nh + h) * a.splits;
@@ -418,10 +424,10 @@ static int launch_decode(const DecodeArgs &a, cudaStream_t stream) {
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_decode: %s", cudaGetErrorString(e));
     }
-    attention_decode_kernel<LPR, HG, POW2><<<grid, DEC_WARPS * 32, smem, stream>>>(a);
+    jk_launch(attention_decode_kernel<LPR, HG, POW2>, grid, dim3(DEC_WARPS * 32), smem, stream, a);
     JK_CHECK_LAUNCH("attention_decode");
     if (a.splits > 1) {
-        attention_combine_kernel<<<dim3(a.nh, a.nrows), 64, 0, stream>>>(a);
+        jk_launch(attention_combine_kernel, dim3(a.nh, a.nrows), dim3(64), 0, stream, a);
         JK_CHECK_LAUNCH("attention_combine");
     }
     return JK_OK;
@@ -521,6 +527,8 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 template <int DH, int BN>
 __global__ void __launch_bounds__(128)
 attention_prefill_kernel(PrefillArgs a) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int STRIDE = DH + 8;            // elements per shared row
     constexpr int CH = DH / 8;                // 16-byte chunks per row
     extern __shared__ __align__(16) unsigned char pf_smem[];
@@ -603,36 +611,39 @@ attention_prefill_kernel(PrefillArgs a) {
                 mma_bf16(s[2 * n2 + 1], qf[kk], b[2], b[3]);
             }
         }
-        // scale, mask, running maximum
+        // mask and running maximum on the raw scores (the softmax scale is positive, so it commutes
+        // with the maximum and is applied inside the exponent by one fused multiply-add)
         const bool all_visible = (kv0 + BN - 1 <= p0) && (a.window == 0 || kv0 >= p_last - a.window + 1);
         float mx_a = -INFINITY, mx_b = -INFINITY;
+        if (!all_visible) {
 #pragma unroll
-        for (int i = 0; i < BN / 8; ++i) {
+            for (int i = 0; i < BN / 8; ++i) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float v = s[i][c] * a.scale_log2;
-                if (!all_visible) {
+                for (int c = 0; c < 4; ++c) {
                     const int j = kv0 + i * 8 + 2 * (lane & 3) + (c & 1);
                     const bool ok = c < 2 ? (j <= pos_a && j >= lo_a) : (j <= pos_b && j >= lo_b);
-                    if (!ok) v = -INFINITY;
+                    if (!ok) s[i][c] = -INFINITY;
                 }
-                s[i][c] = v;
-                if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
             }
+        }
+#pragma unroll
+        for (int i = 0; i < BN / 8; ++i) {
+            mx_a = fmaxf(mx_a, fmaxf(s[i][0], s[i][1]));
+            mx_b = fmaxf(mx_b, fmaxf(s[i][2], s[i][3]));
         }
         mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
         mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-        const float use_a = mn_a == -INFINITY ? 0.f : mn_a, use_b = mn_b == -INFINITY ? 0.f : mn_b;
-        const float corr_a = exp2f(m_a - use_a), corr_b = exp2f(m_b - use_b);
+        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);          // raw maxima
+        const float use_a = mn_a == -INFINITY ? 0.f : mn_a * a.scale_log2, use_b = mn_b == -INFINITY ? 0.f : mn_b * a.scale_log2;
+        const float corr_a = fast_exp2(m_a * a.scale_log2 - use_a), corr_b = fast_exp2(m_b * a.scale_log2 - use_b);
         m_a = mn_a; m_b = mn_b;
         float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
         for (int i = 0; i < BN / 8; ++i) {
-            s[i][0] = exp2f(s[i][0] - use_a); s[i][1] = exp2f(s[i][1] - use_a);
-            s[i][2] = exp2f(s[i][2] - use_b); s[i][3] = exp2f(s[i][3] - use_b);
+            s[i][0] = fast_exp2(fmaf(s[i][0], a.scale_log2, -use_a)); s[i][1] = fast_exp2(fmaf(s[i][1], a.scale_log2, -use_a));
+            s[i][2] = fast_exp2(fmaf(s[i][2], a.scale_log2, -use_b)); s[i][3] = fast_exp2(fmaf(s[i][3], a.scale_log2, -use_b));
             sum_a += s[i][0] + s[i][1]; sum_b += s[i][2] + s[i][3];
         }
         l_a = l_a * corr_a + sum_a; l_b = l_b * corr_b + sum_b;
@@ -680,7 +691,7 @@ static int launch_prefill(const PrefillArgs &a, cudaStream_t stream) {
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_prefill: %s", cudaGetErrorString(e));
     }
-    attention_prefill_kernel<DH, BN><<<dim3(a.ntiles, a.nh), 128, smem, stream>>>(a);
+    jk_launch(attention_prefill_kernel<DH, BN>, dim3(a.ntiles, a.nh), dim3(128), smem, stream, a);
     JK_CHECK_LAUNCH("attention_prefill");
     return JK_OK;
 }

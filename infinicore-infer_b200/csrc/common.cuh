@@ -47,6 +47,42 @@ char *jk_error_buffer();   // one per shared object, defined by JK_DEFINE_ERROR_
             JK_FAIL(JK_CUDA_ERROR, "%s: %s", name, cudaGetErrorString(e_));         \
     } while (0)
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// Every kernel of this package is launched with the attribute that lets it start while the kernel
+// before it in the stream is still running.  A kernel calls pdl_trigger() first (the kernel after
+// it may then be scheduled as soon as all blocks of this one have started) and pdl_wait() before it
+// reads anything an earlier kernel wrote and before its own first global write; what it does in
+// between (setting up shared memory, prefetching weights) overlaps the earlier kernel's tail.
+// Both are no-ops in a launch without the attribute.  JK_NO_PDL=1 in the environment turns it off.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+#ifndef __CUDA_ARCH__
+#include <cstdlib>
+#include <utility>
+static inline bool jk_pdl_enabled() {
+    static const bool on = [] { const char *e = std::getenv("JK_NO_PDL"); return !(e && e[0] == '1'); }();
+    return on;
+}
+#endif
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t jk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args &&...args) {
+#ifndef __CUDA_ARCH__
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = jk_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+#else
+    return cudaSuccess;
+#endif
+}
+
 // ---- element access: storage type T (float or __nv_bfloat16), arithmetic in float ----
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

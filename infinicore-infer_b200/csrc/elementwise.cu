@@ -15,6 +15,8 @@ JK_DEFINE_ERROR_BUFFER(jk_elementwise)
 template <typename TW>
 __global__ void embed_kernel(const int *__restrict__ tokens, const TW *__restrict__ table,
                              float *__restrict__ out, int d, float scale) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     const TW *src = table + (size_t)tokens[row] * d;
     float *dst = out + (size_t)row * d;
@@ -27,9 +29,9 @@ JK_EXPORT int jk_embed(const int *tokens, int ntok, const void *table, int table
     JK_REQUIRE(ntok > 0 && d > 0, "embed: ntok %d, d %d", ntok, d);
     const int threads = d >= 1024 ? 256 : 128;
     if (table_dtype == JK_F32)
-        embed_kernel<float><<<ntok, threads, 0, stream>>>(tokens, (const float *)table, out, d, scale);
+        jk_launch(embed_kernel<float>, dim3(ntok), dim3(threads), 0, stream, tokens, (const float *)table, out, d, scale);
     else if (table_dtype == JK_BF16)
-        embed_kernel<__nv_bfloat16><<<ntok, threads, 0, stream>>>(tokens, (const __nv_bfloat16 *)table, out, d, scale);
+        jk_launch(embed_kernel<__nv_bfloat16>, dim3(ntok), dim3(threads), 0, stream, tokens, (const __nv_bfloat16 *)table, out, d, scale);
     else
         JK_FAIL(JK_UNSUPPORTED, "embed: table dtype %d", table_dtype);
     JK_CHECK_LAUNCH("embed");
@@ -50,6 +52,8 @@ __global__ void add_rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__
                                    float delta_scale, const float *__restrict__ w, float eps,
                                    float out_scale, TO *__restrict__ out,
                                    const int *__restrict__ rows, int d) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float row_buf[];
     __shared__ float scratch[33];
     const int i = blockIdx.x;
@@ -83,7 +87,7 @@ static int launch_add_rmsnorm(float *x, const void *delta, float delta_scale, co
         if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "add_rmsnorm: %s", cudaGetErrorString(e));
     }
     const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-    add_rmsnorm_kernel<TD, TO><<<nout, threads, smem, stream>>>(
+    jk_launch(add_rmsnorm_kernel<TD, TO>, dim3(nout), dim3(threads), smem, stream, 
         x, (const TD *)delta, delta_scale, w, eps, out_scale, (TO *)out, rows, d);
     JK_CHECK_LAUNCH("add_rmsnorm");
     return JK_OK;
@@ -109,6 +113,8 @@ JK_EXPORT int jk_add_rmsnorm(float *x, const void *delta, int delta_dtype, float
 template <typename TD>
 __global__ void residual_add_kernel(float *__restrict__ x, const TD *__restrict__ delta,
                                     float delta_scale, size_t n) {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < n; i += stride) x[i] += delta_scale * to_f32(delta[i]);
@@ -121,9 +127,9 @@ JK_EXPORT int jk_residual_add(float *x, const void *delta, int delta_dtype, floa
     long long blocks = (n + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (delta_dtype == JK_F32)
-        residual_add_kernel<float><<<(int)blocks, threads, 0, stream>>>(x, (const float *)delta, delta_scale, (size_t)n);
+        jk_launch(residual_add_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, x, (const float *)delta, delta_scale, (size_t)n);
     else if (delta_dtype == JK_BF16)
-        residual_add_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(x, (const __nv_bfloat16 *)delta, delta_scale, (size_t)n);
+        jk_launch(residual_add_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream, x, (const __nv_bfloat16 *)delta, delta_scale, (size_t)n);
     else
         JK_FAIL(JK_UNSUPPORTED, "residual_add: dtype %d", delta_dtype);
     JK_CHECK_LAUNCH("residual_add");
@@ -136,6 +142,8 @@ JK_EXPORT int jk_residual_add(float *x, const void *delta, int delta_dtype, floa
 // ---------------------------------------------------------------------------------------
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI *__restrict__ gu, TO *__restrict__ out, int di, size_t total) {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
@@ -156,11 +164,11 @@ JK_EXPORT int jk_swiglu(const void *gu, int in_dtype, void *out, int out_dtype, 
     size_t blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;
     if (in_dtype == JK_F32 && out_dtype == JK_F32)
-        swiglu_kernel<float, float><<<(int)blocks, threads, 0, stream>>>((const float *)gu, (float *)out, di, total);
+        jk_launch(swiglu_kernel<float, float>, dim3((int)blocks), dim3(threads), 0, stream, (const float *)gu, (float *)out, di, total);
     else if (in_dtype == JK_F32 && out_dtype == JK_BF16)
-        swiglu_kernel<float, __nv_bfloat16><<<(int)blocks, threads, 0, stream>>>((const float *)gu, (__nv_bfloat16 *)out, di, total);
+        jk_launch(swiglu_kernel<float, __nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream, (const float *)gu, (__nv_bfloat16 *)out, di, total);
     else if (in_dtype == JK_BF16 && out_dtype == JK_BF16)
-        swiglu_kernel<__nv_bfloat16, __nv_bfloat16><<<(int)blocks, threads, 0, stream>>>((const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, di, total);
+        jk_launch(swiglu_kernel<__nv_bfloat16, __nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream, (const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, di, total);
     else
         JK_FAIL(JK_UNSUPPORTED, "swiglu: dtypes %d -> %d", in_dtype, out_dtype);
     JK_CHECK_LAUNCH("swiglu");
@@ -194,6 +202,8 @@ struct RopeKvArgs {
 
 template <typename TI, typename TO>
 __global__ void rope_kv_kernel(RopeKvArgs a) {
+    pdl_trigger();
+    pdl_wait();
     // blockIdx.x: token row; blockIdx.y: a chunk of `heads_per_block` heads out of the row's
     // nh query heads, nkvh key heads and nkvh value heads (in that order)
     const int t = blockIdx.x;
@@ -257,11 +267,11 @@ JK_EXPORT int jk_rope_kv(const void *qkv, int in_dtype, int ld_qkv, const float 
     const int work = a.heads_per_block * dh / 2;
     const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
     if (in_dtype == JK_F32 && out_dtype == JK_F32)
-        rope_kv_kernel<float, float><<<grid, threads, 0, stream>>>(a);
+        jk_launch(rope_kv_kernel<float, float>, grid, dim3(threads), 0, stream, a);
     else if (in_dtype == JK_F32 && out_dtype == JK_BF16)
-        rope_kv_kernel<float, __nv_bfloat16><<<grid, threads, 0, stream>>>(a);
+        jk_launch(rope_kv_kernel<float, __nv_bfloat16>, grid, dim3(threads), 0, stream, a);
     else if (in_dtype == JK_BF16 && out_dtype == JK_BF16)
-        rope_kv_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, 0, stream>>>(a);
+        jk_launch(rope_kv_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(threads), 0, stream, a);
     else
         JK_FAIL(JK_UNSUPPORTED, "rope_kv: dtypes %d -> %d", in_dtype, out_dtype);
     JK_CHECK_LAUNCH("rope_kv");
@@ -281,6 +291,8 @@ __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float *__restrict__ A, const float *__restrict__ W,
                 const float *__restrict__ bias, float *__restrict__ C, int M, int N, int K,
                 int lda, int ldw, int ldc) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float As[GF_BK][GF_BM + 1];
     __shared__ float Ws[GF_BK][GF_BN + 1];
     const int m0 = blockIdx.y * GF_BM, n0 = blockIdx.x * GF_BN;
@@ -323,7 +335,7 @@ JK_EXPORT int jk_gemm_f32(const float *A, int lda, const float *W, int ldw, cons
     JK_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_f32: M %d N %d K %d", M, N, K);
     dim3 grid((N + GF_BN - 1) / GF_BN, (M + GF_BM - 1) / GF_BM);
     JK_REQUIRE(grid.y <= 65535, "gemm_f32: M %d is too large for one launch", M);
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K, lda, ldw, ldc);
+    jk_launch(gemm_f32_kernel, grid, dim3(256), 0, stream, A, W, bias, C, M, N, K, lda, ldw, ldc);
     JK_CHECK_LAUNCH("gemm_f32");
     return JK_OK;
 }

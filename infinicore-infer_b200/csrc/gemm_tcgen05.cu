@@ -149,6 +149,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(TG_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, TgArgs a) {
+    pdl_trigger();
     extern __shared__ unsigned char tg_raw[];
     TgSmem<BN> &s = *reinterpret_cast<TgSmem<BN> *>((reinterpret_cast<uintptr_t>(tg_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -170,6 +171,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after();
     const unsigned tmem = s.tmem_base;
     int failed = 0;
+    pdl_wait();       // barriers and tensor memory are set up; now the operands of earlier kernels may be read
 
     if (warp == 0) {
         // ---- TMA producer ----
@@ -363,7 +365,7 @@ static int launch_tg(const CUtensorMap &ma, const CUtensorMap &mw, const CUtenso
     if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: %s", cudaGetErrorString(e));
     const int out_cols = EPI == EPI_SWIGLU ? BN / 2 : BN;
     const int tiles = ((a.N + out_cols - 1) / out_cols) * ((a.M + TG_BM - 1) / TG_BM);
-    gemm_tcgen05_kernel<BN, EPI><<<tiles < sms ? tiles : sms, TG_THREADS, smem, stream>>>(ma, mw, mo, a);
+    jk_launch(gemm_tcgen05_kernel<BN, EPI>, dim3(tiles < sms ? tiles : sms), dim3(TG_THREADS), smem, stream, ma, mw, mo, a);
     JK_CHECK_LAUNCH("gemm_tcgen05");
     return JK_OK;
 }

@@ -56,6 +56,7 @@ __device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1
 template <int MT, int EPI, int RING>      // MT: tiles of 8 activation rows (1 or 2); RING: ring bytes per thread
 __global__ void __launch_bounds__(SL_MAX_WARPS * 32)
 small_linear_kernel(SmallLinearArgs a) {
+    pdl_trigger();
     constexpr int NW = EPI == EPI_SWIGLU ? 2 : 1;          // weight tiles a warp streams together
     constexpr int DEPTH = RING / (NW * 2 * 16);
     extern __shared__ __align__(16) unsigned char sl_smem[];
@@ -93,7 +94,8 @@ small_linear_kernel(SmallLinearArgs a) {
         cp_async_commit();
     };
 #pragma unroll
-    for (int q = 0; q < DEPTH - 1; ++q) issue(q);
+    for (int q = 0; q < DEPTH - 1; ++q) issue(q);     // weights do not depend on the kernel before this one
+    pdl_wait();
 
     // activations into shared memory, [k / 8][row][8]; rows beyond M are zero
     const int units = a.K / 8;
@@ -190,7 +192,7 @@ static int launch_small(const SmallLinearArgs &a, int ctas, int warps, size_t sm
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "linear_small: %s", cudaGetErrorString(e));
     }
-    small_linear_kernel<MT, EPI, RING><<<ctas, warps * 32, smem, stream>>>(a);
+    jk_launch(small_linear_kernel<MT, EPI, RING>, dim3(ctas), dim3(warps * 32), smem, stream, a);
     JK_CHECK_LAUNCH("linear_small");
     return JK_OK;
 }

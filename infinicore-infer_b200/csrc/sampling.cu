@@ -61,6 +61,8 @@ __device__ int block_argmax(const float *row, int V, ArgMax *scratch) {
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float *__restrict__ logits, long long ld, int V, int *__restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ ArgMax scratch[33];
     const int idx = block_argmax(logits + (size_t)blockIdx.x * ld, V, scratch);
     if (threadIdx.x == 0) out[blockIdx.x] = idx;
@@ -72,6 +74,8 @@ constexpr int ARGMAX_CHUNK = 8192;
 
 __global__ void __launch_bounds__(256)
 argmax_chunks_kernel(const float *__restrict__ logits, long long ld, int V, ArgMax *__restrict__ part) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ ArgMax scratch[33];
     const int r = blockIdx.y, c = blockIdx.x;
     const int lo = c * ARGMAX_CHUNK, n = min(ARGMAX_CHUNK, V - lo);
@@ -80,6 +84,8 @@ argmax_chunks_kernel(const float *__restrict__ logits, long long ld, int V, ArgM
 }
 
 __global__ void argmax_merge_kernel(const ArgMax *__restrict__ part, int nchunks, int *__restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     ArgMax best{-INFINITY, 0x7fffffff};
     for (int i = threadIdx.x; i < nchunks; i += 32) best = better(best, part[(size_t)r * nchunks + i]);
@@ -105,13 +111,13 @@ JK_EXPORT int jk_argmax(const float *logits, long long ld, int nrows, int V, int
     if (scratch != nullptr && jk_argmax_scratch_bytes(nrows, V) > 0) {
         const int chunks = (V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
         JK_REQUIRE(nrows <= 65535, "argmax: %d rows exceed one launch", nrows);
-        argmax_chunks_kernel<<<dim3(chunks, nrows), 256, 0, stream>>>(logits, ld, V, (ArgMax *)scratch);
+        jk_launch(argmax_chunks_kernel, dim3(chunks, nrows), dim3(256), 0, stream, logits, ld, V, (ArgMax *)scratch);
         JK_CHECK_LAUNCH("argmax_chunks");
-        argmax_merge_kernel<<<nrows, 32, 0, stream>>>((const ArgMax *)scratch, chunks, out);
+        jk_launch(argmax_merge_kernel, dim3(nrows), dim3(32), 0, stream, (const ArgMax *)scratch, chunks, out);
         JK_CHECK_LAUNCH("argmax_merge");
         return JK_OK;
     }
-    argmax_kernel<<<nrows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, out);
+    jk_launch(argmax_kernel, dim3(nrows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, out);
     JK_CHECK_LAUNCH("argmax");
     return JK_OK;
 }
@@ -125,6 +131,8 @@ sample_kernel(const float *__restrict__ logits, long long ld, int V,
               const float *__restrict__ temperature, const int *__restrict__ topk,
               const float *__restrict__ topp, const float *__restrict__ uniform,
               int *__restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ ArgMax am_scratch[33];
     __shared__ float f_scratch[33];
     __shared__ unsigned hist_cnt[256];
@@ -261,7 +269,7 @@ JK_EXPORT int jk_sample(const float *logits, long long ld, int nrows, int V, con
                         cudaStream_t stream) {
     if (nrows == 0) return JK_OK;
     JK_REQUIRE(nrows > 0 && V > 0 && ld >= V, "sample: rows %d, vocabulary %d, stride %lld", nrows, V, ld);
-    sample_kernel<<<nrows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, topk, topp, uniform, out);
+    jk_launch(sample_kernel, dim3(nrows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature, topk, topp, uniform, out);
     JK_CHECK_LAUNCH("sample");
     return JK_OK;
 }

@@ -66,6 +66,7 @@ class Runtime:
         self.device = torch.device(device)
         self.plain_attention = False      # True: bfloat16 attention through the row kernel too
         self.library_products_only = False   # True: every bfloat16 product goes to the library
+        self.tcgen05_min_tiles = 96          # fewest 128x128 output tiles for which the tcgen05 kernel is used
 
     def empty(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
@@ -123,7 +124,7 @@ class Runtime:
         if self.dtype != torch.bfloat16 or self.library_products_only or m <= 16:
             return False
         tiles = -(-m // 128) * -(-n // 128)
-        return tiles >= 96 and kernels.gemm_tcgen05_supports(m, n, k)
+        return tiles >= self.tcgen05_min_tiles and kernels.gemm_tcgen05_supports(m, n, k)
 
     def fuses_residual(self, m: int, n: int, k: int) -> bool:
         return self.takes_tcgen05(m, n, k)

@@ -87,6 +87,23 @@ def test_whole_tail_and_portions_agree_with_the_plain_implementation(tiny_models
         assert not eng.cache.lengths and all(g.pool.in_use == 0 for g in eng.cache.groups)
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_every_product_kernel_gives_the_same_model(tiny_models, name):
+    """The bfloat16 products have three homes: the tcgen05 kernel (many rows; here forced on for any
+    step of more than 16 rows), the weight-streaming kernel (few rows) and the library.  The model's
+    logits must not care."""
+    toks, want = expected(tiny_models, name, 150, 120)
+    steps = portions("r", toks, sizes=(70, 3, 33, 14))       # 70 and 33 rows: tcgen05; 3 and 14: weight streaming
+    for mode in ("tcgen05", "library"):
+        eng = make_engine(tiny_models[name][0], "bfloat16", 256)
+        if mode == "tcgen05":
+            eng.runtime.tcgen05_min_tiles = 1
+        else:
+            eng.runtime.library_products_only = True
+        got = run(eng, steps)
+        check(got, "r", want, TOL["bfloat16"], f"{name} products by {mode}")
+
+
 @pytest.mark.parametrize("dtype", list(DTYPES))
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_mixed_requests_in_a_pool_so_small_that_pages_are_used_again(tiny_models, name, dtype):
