@@ -97,13 +97,23 @@ small_linear_kernel(SmallLinearArgs a) {
     for (int q = 0; q < DEPTH - 1; ++q) issue(q);     // weights do not depend on the kernel before this one
     pdl_wait();
 
-    // activations into shared memory, [k / 8][row][8]; rows beyond M are zero
-    const int units = a.K / 8;
-    for (int i = threadIdx.x; i < units * MT * 8; i += nthreads) {
-        const int kb = i / (MT * 8), row = i - kb * (MT * 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < a.M) v = *reinterpret_cast<const uint4 *>(a.act + (size_t)row * a.K + kb * 8);
-        act_s[i] = v;
+    // activations into shared memory, [k / 8][row][8]; rows beyond M are zero.  Plain loads, eight in
+    // flight per thread: they come from L2 and must not queue behind the weights' cp.async traffic.
+    const int total_units = (a.K / 8) * MT * 8;
+    for (int i0 = threadIdx.x; i0 < total_units; i0 += nthreads * 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * nthreads;
+            const int kb = i / (MT * 8), row = i - kb * (MT * 8);
+            v[u] = make_uint4(0, 0, 0, 0);
+            if (i < total_units && row < a.M) v[u] = *reinterpret_cast<const uint4 *>(a.act + (size_t)row * a.K + kb * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * nthreads;
+            if (i < total_units) act_s[i] = v[u];
+        }
     }
     __syncthreads();
 

@@ -274,12 +274,23 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
 
 
 def attention_decode_splits(nrows: int, nkvh: int, group: int, max_positions: int, sms: int = 148) -> int:
-    """How many ways the decode kernel cuts each row's key range: enough blocks to fill the GPU many
-    times over, no split shorter than 128 keys at the longest context.  It depends on the batch's size
-    only (not on the lengths), so a captured step keeps its grid."""
+    """How many ways the decode kernel cuts each row's key range.  It depends on the batch's size only
+    (not on the lengths), so a captured step keeps its grid.  Three blocks fit an SM; the choice weighs
+    full waves of blocks (a last wave that is nearly empty costs as much as a full one) against the
+    fixed cost of a block (about 128 keys' worth of time for set-up and the merge of its groups), at
+    half the longest context."""
     blocks = max(1, nrows * nkvh * ((group + 3) // 4 if group > 4 else 1))
-    want = -(-16 * sms // blocks)          # several waves of blocks, so that the last wave's idle SMs matter little
-    return max(1, min(want, 32, -(-max_positions // 128)))
+    slots = sms * 3
+    keys = max(1, max_positions // 2)
+    best, best_cost = 1, None
+    for s in range(1, 33):
+        if s > 1 and keys / s < 64:
+            break
+        waves = -(-blocks * s // slots)
+        cost = waves * (128 + keys / s)
+        if best_cost is None or cost < best_cost * 0.97:      # prefer fewer splits unless clearly better
+            best, best_cost = s, cost
+    return best
 
 
 def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,

@@ -420,3 +420,4 @@ def test_gemm_tcgen05_refuses_rows_that_tma_cannot_address(K):
     with pytest.raises(K.KernelError, match="multiple of 8"):
         K.gemm_tcgen05(torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV), torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV),
                        torch.zeros(4, 4, device=DEV))
+
