@@ -59,10 +59,23 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\
 
 #ifndef __CUDA_ARCH__
 #include <cstdlib>
+#include <mutex>
+#include <set>
 #include <utility>
 static inline bool jk_pdl_enabled() {
     static const bool on = [] { const char *e = std::getenv("JK_NO_PDL"); return !(e && e[0] == '1'); }();
     return on;
+}
+// Every kernel asks for the same split of the SM's on-chip memory (all of it shared memory): a step is
+// a chain of short kernels, and an SM that has to change the split between two of them drains first.
+static inline void jk_prefer_shared(const void *kernel) {
+    static const bool on = [] { const char *e = std::getenv("JK_NO_CARVEOUT"); return !(e && e[0] == '1'); }();
+    if (!on) return;
+    static std::mutex mu;
+    static std::set<const void *> seen;
+    std::lock_guard<std::mutex> lock(mu);
+    if (seen.insert(kernel).second)
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 #endif
 
@@ -70,6 +83,7 @@ template <typename... KArgs, typename... Args>
 static inline cudaError_t jk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                     Args &&...args) {
 #ifndef __CUDA_ARCH__
+    jk_prefer_shared(reinterpret_cast<const void *>(kernel));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
     cudaLaunchAttribute attr[1];

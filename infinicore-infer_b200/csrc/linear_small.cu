@@ -31,7 +31,7 @@ struct SmallLinearArgs {
     int M, N, K, ldo, ksplit, n_units;
 };
 
-constexpr int SL_MAX_WARPS = 4;
+constexpr int SL_MAX_WARPS = 8;
 constexpr int SL_RING = 256;        // ring bytes per thread: 16 loads of 16 bytes in flight
 constexpr int SL_RING_SMALL = 128;  // when the activations take most of the shared memory
 
@@ -192,7 +192,7 @@ static size_t small_linear_smem(int K, int MT, int warps, int ring) {
 }
 // The deep ring unless the activations leave too little room for it.
 static int small_linear_ring(int K, int MT, int warps) {
-    return small_linear_smem(K, MT, warps, SL_RING) <= 100 * 1024 ? SL_RING : SL_RING_SMALL;
+    return small_linear_smem(K, MT, warps, SL_RING) <= 170 * 1024 ? SL_RING : SL_RING_SMALL;
 }
 
 template <int MT, int EPI, int RING>
@@ -211,7 +211,7 @@ static int launch_small(const SmallLinearArgs &a, int ctas, int warps, size_t sm
 JK_EXPORT int jk_linear_small_supports(int M, int N, int K) {
     if (M < 1 || M > 16 || N < 1 || K < 32 || K % 32) return 0;
     const int MT = M <= 8 ? 1 : 2;
-    return small_linear_smem(K, MT, 4, small_linear_ring(K, MT, 4)) <= 200 * 1024;
+    return small_linear_smem(K, MT, 8, small_linear_ring(K, MT, 8)) <= 200 * 1024;
 }
 
 JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, int N, int K, int ldo,
@@ -225,7 +225,9 @@ JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, 
     if (sms <= 0) sms = 148;
     // Blocks of 4 warps, several per SM; a block works on one tile of 16 features at a time with its
     // warps on slices of K (short chains, and the work is cut finely enough to balance over the SMs).
-    const int warps = 4;
+    // 8 warps on one tile when the matrix is small in N (few tiles to go round) or long in K (the
+    // chain of loads per warp would be long); else 4
+    const int warps = (tiles <= 2 * sms || K >= 4096) ? 8 : 4;
     int ksplit = warps;
     while (ksplit > 1 && (K / 32) / ksplit < 2) ksplit /= 2;
     const int tiles_per_unit = warps / ksplit;
