@@ -47,32 +47,67 @@ JK_EXPORT int jk_embed(const int *tokens, int ntok, const void *table, int table
 // (reference: rmsnorm at jiuge.cpp:198, :246, :262; the residual add is the beta=1 of the
 // preceding product, inference_context.cpp:207-210.)
 // ---------------------------------------------------------------------------------------
-template <typename TD, typename TO>
+__device__ __forceinline__ float4 load4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16 *p) {
+    const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16 *p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const unsigned *>(&lo); raw.y = *reinterpret_cast<const unsigned *>(&hi);
+    *reinterpret_cast<uint2 *>(p) = raw;
+}
+
+// VEC: the width is a multiple of 4 and rows are 16-byte aligned, so four elements move at a time.
+template <typename TD, typename TO, bool VEC>
 __global__ void add_rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ delta,
                                    float delta_scale, const float *__restrict__ w, float eps,
                                    float out_scale, TO *__restrict__ out,
                                    const int *__restrict__ rows, int d) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float row_buf[];
+    extern __shared__ __align__(16) float row_buf[];
     __shared__ float scratch[33];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
     float *xr = x + (size_t)r * d;
     const TD *dr = delta ? delta + (size_t)r * d : nullptr;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
-        float v = xr[c];
-        if (dr) v += delta_scale * to_f32(dr[c]);
-        row_buf[c] = v;
-        if (dr && !rows) xr[c] = v;
-        ss += v * v;
+    if (VEC) {
+        for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+            float4 v = load4(xr + c);
+            if (dr) {
+                const float4 dv = load4(dr + c);
+                v = make_float4(v.x + delta_scale * dv.x, v.y + delta_scale * dv.y, v.z + delta_scale * dv.z, v.w + delta_scale * dv.w);
+                if (!rows) store4(xr + c, v);
+            }
+            store4(row_buf + c, v);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int c = threadIdx.x; c < d; c += blockDim.x) {
+            float v = xr[c];
+            if (dr) v += delta_scale * to_f32(dr[c]);
+            row_buf[c] = v;
+            if (dr && !rows) xr[c] = v;
+            ss += v * v;
+        }
     }
     ss = block_sum(ss, scratch);
-    const float inv = rsqrtf(ss / (float)d + eps);
+    const float inv = rsqrtf(ss / (float)d + eps) * out_scale;
     TO *o = out + (size_t)i * d;
-    for (int c = threadIdx.x; c < d; c += blockDim.x)
-        o[c] = from_f32<TO>(out_scale * (row_buf[c] * inv) * w[c]);
+    if (VEC) {
+        for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+            const float4 v = load4(row_buf + c), g = load4(w + c);
+            store4(o + c, make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w));
+        }
+    } else {
+        for (int c = threadIdx.x; c < d; c += blockDim.x) o[c] = from_f32<TO>((row_buf[c] * inv) * w[c]);
+    }
 }
 
 template <typename TD, typename TO>
@@ -81,14 +116,22 @@ static int launch_add_rmsnorm(float *x, const void *delta, float delta_scale, co
                               int d, cudaStream_t stream) {
     const size_t smem = (size_t)d * sizeof(float);
     JK_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: width %d needs %zu bytes of shared memory", d, smem);
+    const bool vec = d % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
+                     ((uintptr_t)w % 16 == 0);
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = vec ? cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                            : cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "add_rmsnorm: %s", cudaGetErrorString(e));
     }
-    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-    jk_launch(add_rmsnorm_kernel<TD, TO>, dim3(nout), dim3(threads), smem, stream, 
-        x, (const TD *)delta, delta_scale, w, eps, out_scale, (TO *)out, rows, d);
+    if (vec) {
+        const int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);
+        jk_launch(add_rmsnorm_kernel<TD, TO, true>, dim3(nout), dim3(threads), smem, stream,
+                  x, (const TD *)delta, delta_scale, w, eps, out_scale, (TO *)out, rows, d);
+    } else {
+        const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+        jk_launch(add_rmsnorm_kernel<TD, TO, false>, dim3(nout), dim3(threads), smem, stream,
+                  x, (const TD *)delta, delta_scale, w, eps, out_scale, (TO *)out, rows, d);
+    }
     JK_CHECK_LAUNCH("add_rmsnorm");
     return JK_OK;
 }
@@ -197,7 +240,7 @@ struct RopeKvArgs {
     void *q_out;
     void *k_pages;
     void *v_pages;
-    int ld_qkv, nh, nkvh, dh, page_size, max_blocks, interleaved, write_cache, heads_per_block;
+    int ld_qkv, nh, nkvh, dh, page_size, max_blocks, interleaved, write_cache, heads_per_block, vec;
 };
 
 template <typename TI, typename TO>
@@ -221,6 +264,33 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
     const int total_heads = a.write_cache ? a.nh + 2 * a.nkvh : a.nh;
     const int h_begin = blockIdx.y * a.heads_per_block;
     const int h_end = min(total_heads, h_begin + a.heads_per_block);
+    if (a.vec) {
+        // four pairs at a time: elements j..j+3 of the first half with j+half..j+half+3 of the second
+        const int q4 = half / 4;
+        for (int i = threadIdx.x; i < (h_end - h_begin) * q4; i += blockDim.x) {
+            const int h = h_begin + i / q4, j = (i % q4) * 4;
+            const bool rotated = h < a.nh + a.nkvh;
+            float4 x0 = load4(src + h * a.dh + j), x1 = load4(src + h * a.dh + half + j);
+            if (a.bias) {
+                const float4 b0 = load4(a.bias + h * a.dh + j), b1 = load4(a.bias + h * a.dh + half + j);
+                x0 = make_float4(x0.x + b0.x, x0.y + b0.y, x0.z + b0.z, x0.w + b0.w);
+                x1 = make_float4(x1.x + b1.x, x1.y + b1.y, x1.z + b1.z, x1.w + b1.w);
+            }
+            float4 y0 = x0, y1 = x1;
+            if (cs && rotated) {
+                const float4 c = load4(cs + j), sn4 = load4(sn + j);
+                y0 = make_float4(x0.x * c.x - x1.x * sn4.x, x0.y * c.y - x1.y * sn4.y, x0.z * c.z - x1.z * sn4.z, x0.w * c.w - x1.w * sn4.w);
+                y1 = make_float4(x0.x * sn4.x + x1.x * c.x, x0.y * sn4.y + x1.y * c.y, x0.z * sn4.z + x1.z * c.z, x0.w * sn4.w + x1.w * c.w);
+            }
+            TO *dst;
+            if (h < a.nh) dst = (TO *)a.q_out + ((size_t)t * a.nh + h) * a.dh;
+            else if (h < a.nh + a.nkvh) dst = (TO *)a.k_pages + slot + (size_t)(h - a.nh) * head_stride;
+            else dst = (TO *)a.v_pages + slot + (size_t)(h - a.nh - a.nkvh) * head_stride;
+            store4(dst + j, y0);
+            store4(dst + half + j, y1);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < (h_end - h_begin) * half; i += blockDim.x) {
         const int h = h_begin + i / half, j = i % half;
         const bool rotated = h < a.nh + a.nkvh;             // value heads are copied as they are
@@ -256,7 +326,11 @@ JK_EXPORT int jk_rope_kv(const void *qkv, int in_dtype, int ld_qkv, const float 
                "rope_kv: cache write asked for without pages");
     JK_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "rope_kv: one of cos/sin is null");
     RopeKvArgs a{qkv, bias, positions, row_req, block_table, cos_table, sin_table, q_out, k_pages,
-                 v_pages, ld_qkv, nh, nkvh, dh, page_size, max_blocks, interleaved, write_cache, 0};
+                 v_pages, ld_qkv, nh, nkvh, dh, page_size, max_blocks, interleaved, write_cache, 0, 0};
+    // four elements at a time when the layout allows it (pairs j, j + dh/2; everything 16-byte aligned)
+    a.vec = !interleaved && dh % 8 == 0 && ld_qkv % 4 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
+            ((uintptr_t)k_pages % 16 == 0) && ((uintptr_t)v_pages % 16 == 0) && ((uintptr_t)bias % 16 == 0) &&
+            ((uintptr_t)cos_table % 16 == 0) && ((uintptr_t)sin_table % 16 == 0);
     // few rows: cut each row's heads over several blocks so that the GPU is not left to ntok blocks
     const int total_heads = write_cache ? nh + 2 * nkvh : nh;
     int chunks = 1;
@@ -264,7 +338,7 @@ JK_EXPORT int jk_rope_kv(const void *qkv, int in_dtype, int ld_qkv, const float 
     a.heads_per_block = (total_heads + chunks - 1) / chunks;
     const dim3 grid(ntok, (total_heads + a.heads_per_block - 1) / a.heads_per_block);
     JK_REQUIRE(grid.y <= 65535, "rope_kv: too many head chunks");
-    const int work = a.heads_per_block * dh / 2;
+    const int work = a.heads_per_block * dh / 2 / (a.vec ? 4 : 1);
     const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
     if (in_dtype == JK_F32 && out_dtype == JK_F32)
         jk_launch(rope_kv_kernel<float, float>, grid, dim3(threads), 0, stream, a);
