@@ -525,7 +525,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 
 template <int DH, int BN>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, DH <= 64 ? 4 : (DH <= 128 ? 2 : 1))
 attention_prefill_kernel(PrefillArgs a) {
     pdl_trigger();
     pdl_wait();
