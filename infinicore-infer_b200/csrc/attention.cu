@@ -497,7 +497,7 @@ struct PrefillArgs {
     const int *req_start;    // [nreq + 1]
     const int *req_pos;      // [nreq]
     const int *block_table;  // [nreq, max_blocks]
-    int ntiles, nh, nkvh, page_size, max_blocks, window;
+    int ntiles, nh, nkvh, page_size, max_blocks, window, tile_rows;
     float scale_log2;
 };
 
@@ -536,11 +536,15 @@ attention_prefill_kernel(PrefillArgs a) {
     __nv_bfloat16 *Ks = Qs + PF_BM * STRIDE;              // [2][BN][STRIDE]
     __nv_bfloat16 *Vs = Ks + 2 * BN * STRIDE;             // [2][BN][STRIDE]
 
-    const int tile = a.ntiles - 1 - blockIdx.x;           // later tiles see more keys: start them first
+    // the step's tiles are tile_rows rows long; a block takes 64 of them
+    const int parts = a.tile_rows / PF_BM;
+    const int idx = a.ntiles * parts - 1 - blockIdx.x;    // later tiles see more keys: start them first
+    const int tile = idx / parts;
     const int h = blockIdx.y;
     const int hk = h / (a.nh / a.nkvh);
     const int r = a.tiles[2 * tile];
-    const int row0 = a.tiles[2 * tile + 1];
+    const int row0 = a.tiles[2 * tile + 1] + (idx % parts) * PF_BM;
+    if (row0 >= a.req_start[r + 1]) return;               // this part of the tile lies beyond the request
     const int nrows = min(PF_BM, a.req_start[r + 1] - row0);
     const int p0 = a.req_pos[r] + (row0 - a.req_start[r]);   // position of the tile's first row
     const int p_last = p0 + nrows - 1;
@@ -691,7 +695,7 @@ static int launch_prefill(const PrefillArgs &a, cudaStream_t stream) {
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_prefill: %s", cudaGetErrorString(e));
     }
-    jk_launch(attention_prefill_kernel<DH, BN>, dim3(a.ntiles, a.nh), dim3(128), smem, stream, a);
+    jk_launch(attention_prefill_kernel<DH, BN>, dim3(a.ntiles * (a.tile_rows / PF_BM), a.nh), dim3(128), smem, stream, a);
     JK_CHECK_LAUNCH("attention_prefill");
     return JK_OK;
 }
@@ -702,7 +706,7 @@ JK_EXPORT int jk_attention_prefill_supports(int dh) {
 }
 
 JK_EXPORT int jk_attention_prefill(const void *q, const void *k_pages, const void *v_pages, void *out,
-                                   const int *tiles, int ntiles, const int *req_start, const int *req_pos,
+                                   const int *tiles, int ntiles, int tile_rows, const int *req_start, const int *req_pos,
                                    const int *block_table, int max_blocks, int page_size, int nh, int nkvh,
                                    int dh, float scale, int window, cudaStream_t stream) {
     if (ntiles == 0) return JK_OK;
@@ -712,7 +716,8 @@ JK_EXPORT int jk_attention_prefill(const void *q, const void *k_pages, const voi
                page_size, max_blocks, window);
     PrefillArgs a{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_pages, (const __nv_bfloat16 *)v_pages,
                   (__nv_bfloat16 *)out, tiles, req_start, req_pos, block_table,
-                  ntiles, nh, nkvh, page_size, max_blocks, window, scale * 1.4426950408889634f};
+                  ntiles, nh, nkvh, page_size, max_blocks, window, tile_rows, scale * 1.4426950408889634f};
+    JK_REQUIRE(tile_rows >= PF_BM && tile_rows % PF_BM == 0, "attention_prefill: tiles of %d rows (a multiple of %d is needed)", tile_rows, PF_BM);
     switch (dh) {
         case 16: return launch_prefill<16, 64>(a, stream);
         case 32: return launch_prefill<32, 64>(a, stream);

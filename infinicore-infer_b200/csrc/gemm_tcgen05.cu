@@ -149,7 +149,6 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(TG_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, TgArgs a) {
-    pdl_trigger();
     extern __shared__ unsigned char tg_raw[];
     TgSmem<BN> &s = *reinterpret_cast<TgSmem<BN> *>((reinterpret_cast<uintptr_t>(tg_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -171,6 +170,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after();
     const unsigned tmem = s.tmem_base;
     int failed = 0;
+    // The next kernel may be scheduled only once every block holds its tensor memory: a later kernel that
+    // took tensor memory on an SM and then waited for this grid, while a block of this grid still waited
+    // for tensor memory there, would never end.
+    pdl_trigger();
     pdl_wait();       // barriers and tensor memory are set up; now the operands of earlier kernels may be read
 
     if (warp == 0) {

@@ -330,11 +330,14 @@ def attention_prefill_supports(dh: int) -> bool:
     return bool(_build.load("attention").jk_attention_prefill_supports(_c_int(dh)))
 
 
+TILE_ROWS = 128      # rows of a query tile in the tile lists that the prefill attention kernels take
+
+
 def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                       tiles: torch.Tensor, ntiles: int, req_start: torch.Tensor, req_pos: torch.Tensor,
                       block_table: torch.Tensor, nh: int, scale: float, window: int = 0) -> torch.Tensor:
-    """bfloat16 tensor-core attention of requests that bring many rows: ``tiles[i] = (batch entry, first
-    row)`` names 64-row tiles of query rows."""
+    """bfloat16 tensor-core (mma.sync) attention of requests that bring many rows: ``tiles[i] = (batch
+    entry, first row)`` names TILE_ROWS-row tiles of query rows."""
     for name, t in (("q", q), ("k_pages", k_pages), ("v_pages", v_pages), ("out", out)):
         _need(t, name, torch.bfloat16)
     for name, t in (("tiles", tiles), ("req_start", req_start), ("req_pos", req_pos), ("block_table", block_table)):
@@ -344,9 +347,33 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         raise KernelError("attention_prefill: the tile list is shorter than ntiles")
     lib = _build.load("attention")
     _check("attention", lib.jk_attention_prefill(
-        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), _c_int(ntiles), _ptr(req_start), _ptr(req_pos),
-        _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size), _c_int(nh), _c_int(nkvh), _c_int(dh),
-        _c_float(scale), _c_int(window or 0), _stream()))
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), _c_int(ntiles), _c_int(TILE_ROWS), _ptr(req_start),
+        _ptr(req_pos), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size), _c_int(nh), _c_int(nkvh),
+        _c_int(dh), _c_float(scale), _c_int(window or 0), _stream()))
+    return out
+
+
+def attention_tcgen05_supports(dh: int, page_size: int) -> bool:
+    return bool(_build.load("attention_tcgen05").jk_attention_tcgen05_supports(_c_int(dh), _c_int(page_size)))
+
+
+def attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                      tiles: torch.Tensor, ntiles: int, ntok: int, req_start: torch.Tensor, req_pos: torch.Tensor,
+                      block_table: torch.Tensor, nh: int, scale: float, window: int = 0) -> torch.Tensor:
+    """The same attention of TILE_ROWS-row query tiles on the tcgen05 tensor cores (TMA operands, both
+    products with accumulators in tensor memory); head sizes 64 and 128, pages that divide 128."""
+    for name, t in (("q", q), ("k_pages", k_pages), ("v_pages", v_pages), ("out", out)):
+        _need(t, name, torch.bfloat16)
+    for name, t in (("tiles", tiles), ("req_start", req_start), ("req_pos", req_pos), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    num_pages, nkvh, page_size, dh = k_pages.shape
+    if tiles.numel() < 2 * ntiles or q.numel() < ntok * nh * dh:
+        raise KernelError("attention_tcgen05: the tile list or q is too short")
+    lib = _build.load("attention_tcgen05")
+    _check("attention_tcgen05", lib.jk_attention_tcgen05(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), _c_int(ntiles), _c_int(ntok), _ptr(req_start),
+        _ptr(req_pos), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(num_pages), _c_int(page_size), _c_int(nh),
+        _c_int(nkvh), _c_int(dh), _c_float(scale), _c_int(window or 0), _ptr(gemm_status(q.device)), _stream()))
     return out
 
 

@@ -27,6 +27,7 @@ MODULES: Dict[str, List[str]] = {
     "sampling": ["sampling.cu"],
     "linear_small": ["linear_small.cu"],
     "gemm_tcgen05": ["gemm_tcgen05.cu"],
+    "attention_tcgen05": ["attention_tcgen05.cu"],
 }
 HEADERS = ["common.cuh", "attention_static_scratch.h"]
 

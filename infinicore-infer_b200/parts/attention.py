@@ -68,21 +68,27 @@ class Attention:
 
     def _attend(self, q, o, view, table, ctx) -> None:
         """float32: one warp per (row, head), the same arithmetic whatever the batch.  bfloat16: rows of
-        requests with few rows go to the split-key decode kernel, 64-row tiles of the others to the
-        tensor-core kernel; head sizes that kernel is not built for take the row kernel."""
+        requests with few rows go to the split-key decode kernel, tiles of the others to a tensor-core
+        kernel (tcgen05 where it is built for the head and page size, else mma.sync); head sizes neither
+        is built for take the row kernel."""
         from .. import kernels
         s, T = self.spec, ctx.ntok
         fast = (self.runtime.dtype == torch.bfloat16 and not self.runtime.plain_attention
                 and (ctx.n_short or ctx.n_tiles) and s.head_dim % 8 == 0 and s.head_dim <= 256)
-        if fast and ctx.n_tiles and not kernels.attention_prefill_supports(s.head_dim):
+        if fast and ctx.n_tiles and not (kernels.attention_prefill_supports(s.head_dim)
+                                         or kernels.attention_tcgen05_supports(s.head_dim, view.page_size)):
             fast = False
         if not fast:
             kernels.attention_rows(q, view.k_pages, view.v_pages, o, ctx.positions, ctx.row_req, table, T,
                                    s.num_heads, s.softmax_scale, s.window or 0)
             return
         if ctx.n_tiles:
-            kernels.attention_prefill(q, view.k_pages, view.v_pages, o, ctx.tiles, ctx.n_tiles, ctx.req_start,
-                                      ctx.req_pos, table, s.num_heads, s.softmax_scale, s.window or 0)
+            if not self.runtime.legacy_tensor_cores and kernels.attention_tcgen05_supports(s.head_dim, view.page_size):
+                kernels.attention_tcgen05(q, view.k_pages, view.v_pages, o, ctx.tiles, ctx.n_tiles, T, ctx.req_start,
+                                          ctx.req_pos, table, s.num_heads, s.softmax_scale, s.window or 0)
+            else:
+                kernels.attention_prefill(q, view.k_pages, view.v_pages, o, ctx.tiles, ctx.n_tiles, ctx.req_start,
+                                          ctx.req_pos, table, s.num_heads, s.softmax_scale, s.window or 0)
         if ctx.n_short:
             splits = kernels.attention_decode_splits(ctx.n_short, s.num_kv_heads, s.num_heads // s.num_kv_heads,
                                                      s.window or (s.position.max_positions if s.position else 1 << 20))

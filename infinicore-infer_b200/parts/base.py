@@ -66,6 +66,7 @@ class Runtime:
         self.device = torch.device(device)
         self.plain_attention = False      # True: bfloat16 attention through the row kernel too
         self.library_products_only = False   # True: every bfloat16 product goes to the library
+        self.legacy_tensor_cores = False     # True: prefill attention on mma.sync even where tcgen05 is built
         self.tcgen05_min_tiles = 96          # fewest 128x128 output tiles for which the tcgen05 kernel is used
 
     def empty(self, *shape, dtype=None) -> torch.Tensor:
@@ -151,7 +152,7 @@ class PendingProduct:
 
 
 SHORT_ROWS = 8      # a request with at most this many rows in a step counts as "few rows"
-TILE_ROWS = 64      # rows per tile of the others
+TILE_ROWS = 128     # rows per tile of the others; the same constant as kernels.TILE_ROWS (a test holds them equal)
 
 
 @dataclass
@@ -174,7 +175,7 @@ class StepContext:
     want_rows: torch.Tensor         # int32 [n_want] rows whose logits are wanted
     n_want: int
     # Work lists for mixers that treat few-row and many-row requests differently: the rows of
-    # requests that bring at most SHORT_ROWS rows, and 64-row tiles (batch entry, first row) of the rest.
+    # requests that bring at most SHORT_ROWS rows, and TILE_ROWS-row tiles (batch entry, first row) of the rest.
     short_rows: Optional[torch.Tensor] = None     # int32 [n_short]; None means rows 0..n_short-1
     n_short: int = 0
     tiles: Optional[torch.Tensor] = None          # int32 [n_tiles, 2]

@@ -198,16 +198,21 @@ def _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, plant=N
         rows = torch.randperm(T, generator=g).to(torch.int32).to(DEV)
         K.attention_decode(qd, kd, vd, out, rows, T, positions.to(DEV), row_req.to(DEV), bt, nh, scale,
                            window or 0, splits)
-    else:
+    else:                                                  # "prefill" (mma.sync) or "tcgen05"
         starts = [0]
         for r in range(R):
             assert list(queries[r]) == list(range(queries[r][0], queries[r][0] + len(queries[r]))) if len(queries[r]) else True
             starts.append(starts[-1] + len(queries[r]))
-        tiles = [(r, t0) for r in range(R) for t0 in range(starts[r], starts[r + 1], 64)]
+        tiles = [(r, t0) for r in range(R) for t0 in range(starts[r], starts[r + 1], K.TILE_ROWS)]
         req_pos = [queries[r][0] if len(queries[r]) else 0 for r in range(R)]
         i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
-        K.attention_prefill(qd, kd, vd, out, i32(tiles).flatten(), len(tiles), i32(starts), i32(req_pos), bt, nh,
-                            scale, window or 0)
+        if impl == "tcgen05":
+            K.attention_tcgen05(qd, kd, vd, out, i32(tiles).flatten(), len(tiles), T, i32(starts), i32(req_pos), bt, nh,
+                                scale, window or 0)
+            K.check_gemm_status(DEV)
+        else:
+            K.attention_prefill(qd, kd, vd, out, i32(tiles).flatten(), len(tiles), i32(starts), i32(req_pos), bt, nh,
+                                scale, window or 0)
     want = torch.cat([plain_attention(qf[r].double(), k[r].double(), v[r].double(), scale, window)[queries[r]]
                       for r in range(R) if len(queries[r])])
     return out.view(T, nh, dh), want, v
@@ -247,8 +252,21 @@ def test_attention_prefill_kernel_on_tensor_cores(K, nh, nkvh, dh, page, window)
     _close(got, want, torch.bfloat16, scale=2.0)
 
 
+@pytest.mark.parametrize("nh,nkvh,dh,page,window", [(4, 4, 64, 16, None), (3, 1, 64, 8, None), (8, 2, 128, 16, None),
+                                                     (6, 2, 64, 32, 100), (2, 1, 128, 64, 33), (4, 2, 64, 128, None),
+                                                     (36, 36, 64, 16, None)])
+def test_attention_prefill_kernel_on_tcgen05(K, nh, nkvh, dh, page, window):
+    from infinicore_infer_b200.parts import TILE_ROWS
+    assert K.attention_tcgen05_supports(dh, page) and not K.attention_tcgen05_supports(48, 16)
+    assert TILE_ROWS == K.TILE_ROWS
+    lens = [150, 460, 128, 40]
+    queries = [list(range(0, 150)), list(range(203, 460)), list(range(0, 128)), list(range(31, 40))]
+    got, want, _ = _attention_case(K, torch.bfloat16, nh, nkvh, dh, page, window, lens, queries, seed=dh + page, impl="tcgen05")
+    _close(got, want, torch.bfloat16, scale=2.0)
+
+
 @pytest.mark.parametrize("impl,dtype", [("rows", torch.float32), ("rows", torch.bfloat16), ("decode", torch.bfloat16),
-                                         ("prefill", torch.bfloat16)])
+                                         ("prefill", torch.bfloat16), ("tcgen05", torch.bfloat16)])
 @pytest.mark.parametrize("window", [None, 50])
 def test_attention_finds_one_far_key_among_hundreds(K, impl, dtype, window):
     nh, nkvh, dh, page = 4, 2, 64, 16
@@ -257,7 +275,7 @@ def test_attention_finds_one_far_key_among_hundreds(K, impl, dtype, window):
     # at 320 the key at 319, across a page's edge
     far = 3 if window is None else 699 - window + 1
     plant = [(0, 699, far, 1), (0, 320, 319, 2)]
-    if impl == "prefill":
+    if impl in ("prefill", "tcgen05"):
         queries, i699, i320 = [list(range(300, 700))], 399, 20
     else:
         queries, i699, i320 = [[320, 512, 699]], 2, 0
