@@ -536,11 +536,12 @@ attention_prefill_kernel(PrefillArgs a) {
     __nv_bfloat16 *Ks = Qs + PF_BM * STRIDE;              // [2][BN][STRIDE]
     __nv_bfloat16 *Vs = Ks + 2 * BN * STRIDE;             // [2][BN][STRIDE]
 
-    // the step's tiles are tile_rows rows long; a block takes 64 of them
+    // the step's tiles are tile_rows rows long; a block takes 64 of them.  Blocks start in the order of
+    // the tile list (the caller lists the tiles with the most keys first), all heads of a tile together.
     const int parts = a.tile_rows / PF_BM;
-    const int idx = a.ntiles * parts - 1 - blockIdx.x;    // later tiles see more keys: start them first
+    const int idx = blockIdx.y;
     const int tile = idx / parts;
-    const int h = blockIdx.y;
+    const int h = blockIdx.x;
     const int hk = h / (a.nh / a.nkvh);
     const int r = a.tiles[2 * tile];
     const int row0 = a.tiles[2 * tile + 1] + (idx % parts) * PF_BM;
@@ -695,7 +696,7 @@ static int launch_prefill(const PrefillArgs &a, cudaStream_t stream) {
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_prefill: %s", cudaGetErrorString(e));
     }
-    jk_launch(attention_prefill_kernel<DH, BN>, dim3(a.ntiles * (a.tile_rows / PF_BM), a.nh), dim3(128), smem, stream, a);
+    jk_launch(attention_prefill_kernel<DH, BN>, dim3(a.nh, a.ntiles * (a.tile_rows / PF_BM)), dim3(128), smem, stream, a);
     JK_CHECK_LAUNCH("attention_prefill");
     return JK_OK;
 }
@@ -711,7 +712,7 @@ JK_EXPORT int jk_attention_prefill(const void *q, const void *k_pages, const voi
                                    int dh, float scale, int window, cudaStream_t stream) {
     if (ntiles == 0) return JK_OK;
     JK_REQUIRE(ntiles > 0 && nh > 0 && nkvh > 0 && nh % nkvh == 0, "attention_prefill: tiles %d heads %d/%d", ntiles, nh, nkvh);
-    JK_REQUIRE(nh <= 65535, "attention_prefill: %d heads exceed one launch", nh);
+    JK_REQUIRE(ntiles * (tile_rows / PF_BM) <= 65535, "attention_prefill: %d tiles exceed one launch", ntiles);
     JK_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "attention_prefill: page size %d, blocks %d, window %d",
                page_size, max_blocks, window);
     PrefillArgs a{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_pages, (const __nv_bfloat16 *)v_pages,

@@ -213,14 +213,17 @@ class Engine:
             row += 1
             req_start.append(row)
         short_rows: List[int] = []
-        tiles: List[int] = []
+        tile_list: List[tuple] = []
         for i in range(nB):
             r0, r1 = req_start[i], req_start[i + 1]
             if r1 - r0 <= SHORT_ROWS:
                 short_rows.extend(range(r0, r1))
             else:
                 for t0 in range(r0, r1, TILE_ROWS):
-                    tiles.extend((i, t0))
+                    tile_list.append((starts[i] + (t0 - r0), i, t0))
+        # the attention kernels start tiles in the order of the list: those that see the most keys first
+        tile_list.sort(key=lambda t: -t[0])
+        tiles: List[int] = [v for t in tile_list for v in t[1:]]
         host[lay.short_rows: lay.short_rows + len(short_rows)] = short_rows
         host[lay.tiles: lay.tiles + len(tiles)] = tiles
         n_want = len(want_rows)
