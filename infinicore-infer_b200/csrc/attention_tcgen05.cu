@@ -90,15 +90,9 @@ __device__ __forceinline__ void tmem_dealloc(unsigned addr, unsigned columns) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(unsigned tmem_c, unsigned long long adesc, unsigned long long bdesc,
-                                          unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
-                 ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
-}
-// The same with each descriptor as two 32-bit words: the high word is one constant per operand kind and
-// the low word moves by a small constant from product to product, so the thread that issues spends one
-// addition per operand instead of rebuilding 64-bit descriptors.
+// D (tensor memory) (+)= A B, operands by shared-memory descriptors.  Each descriptor comes as two 32-bit
+// words: the high word is one constant per operand kind and the low word moves by a small constant from
+// product to product, so the thread that issues spends one addition per operand.
 __device__ __forceinline__ void umma_bf16_words(unsigned tmem_c, unsigned a_lo, unsigned a_hi, unsigned b_lo, unsigned b_hi,
                                                 unsigned idesc, unsigned accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
@@ -195,19 +189,12 @@ __device__ __forceinline__ void exp2_poly2(unsigned long long x2, float &e0, flo
     e1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
 }
 
-// K-major operand tile [rows][64 bf16], 128-byte swizzle: groups of 8 rows are 1024 bytes apart.
-__device__ __forceinline__ unsigned long long desc_kmajor(const void *tile) {
-    const unsigned long long addr = smem_u32(tile);
-    return ((addr & 0x3FFFFull) >> 4) | (1ull << 16) | ((1024ull >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// MN-major operand (the value tile as B of P V): memory rows are K (keys), 128 bytes = 64 elements of
-// MN each; groups of 8 keys are 1024 bytes apart (stride byte offset); further groups of 64 MN
-// elements are `mn_group_bytes` apart (leading byte offset).
-__device__ __forceinline__ unsigned long long desc_mnmajor(const void *tile, unsigned mn_group_bytes) {
-    const unsigned long long addr = smem_u32(tile);
-    return ((addr & 0x3FFFFull) >> 4) | ((unsigned long long)(mn_group_bytes >> 4) << 16) | ((1024ull >> 4) << 32) |
-           (1ull << 46) | (2ull << 61);
-}
+// Shared-memory descriptors of the 128-byte-swizzled tiles (built in the issuing thread):
+//   K-major operand [rows][64 bf16]: groups of 8 rows are 1024 bytes apart (stride offset), leading offset 1;
+//   MN-major operand (the value tile as B of P V): memory rows are keys (the K dimension), 128 bytes =
+//   64 elements of the head each; groups of 8 keys are 1024 bytes apart (stride offset), further
+//   groups of 64 head elements one whole tile apart (leading offset);
+//   version 1, layout type 2 (128-byte swizzle).
 // D float32, A and B bfloat16, M = 128; b_mn: B is MN-major.
 __host__ __device__ constexpr unsigned instr_desc(int n, bool b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((unsigned)(n >> 3) << 17) | ((unsigned)(AT_BM >> 4) << 24);
