@@ -45,6 +45,9 @@ class CacheGroup:
         self.pool = PagePool(num_pages, reserved=1, name=self.name)
         self.tables: Dict[object, List[int]] = {}      # request -> page of each block (NO_PAGE if none)
         self.first_block: Dict[object, int] = {}       # request -> first block still held
+        # requests whose table may have a block without a page between first_block and its end; for all
+        # others the blocks a step lacks are simply those beyond the table's end (no scan)
+        self._holes: set = set()
 
     # -- how many new pages a request needs to hold positions [first_needed, new_len) -------
     def _first_needed_block(self, start: int) -> int:
@@ -57,6 +60,8 @@ class CacheGroup:
         table = self.tables.get(req, [])
         last = (new_len + self.page_size - 1) // self.page_size
         first = max(self._first_needed_block(start), self.first_block.get(req, 0))
+        if req not in self._holes and first <= len(table):
+            return max(0, last - len(table))
         return sum(1 for b in range(first, last) if b >= len(table) or table[b] == NO_PAGE)
 
     def reserve(self, req, start: int, new_len: int) -> List[int]:
@@ -65,8 +70,13 @@ class CacheGroup:
         self.first_block.setdefault(req, 0)
         last = (new_len + self.page_size - 1) // self.page_size
         first = max(self._first_needed_block(start), self.first_block[req])
-        want = [b for b in range(first, last) if b >= len(table) or table[b] == NO_PAGE]
+        if req not in self._holes and first <= len(table):
+            want = list(range(len(table), last))
+        else:
+            want = [b for b in range(first, last) if b >= len(table) or table[b] == NO_PAGE]
         pages = self.pool.alloc(len(want))           # raises OutOfPages before anything changes
+        if first > len(table):
+            self._holes.add(req)                     # blocks between the table's end and `first` stay empty
         while len(table) < last:
             table.append(NO_PAGE)
         for b, p in zip(want, pages):
@@ -80,6 +90,10 @@ class CacheGroup:
         for b, p in enumerate(table):
             if p in back:
                 table[b] = NO_PAGE
+        while table and table[-1] == NO_PAGE and len(table) > self.first_block.get(req, 0):
+            table.pop()                              # what was reserved last lies at the end
+        if any(p == NO_PAGE for p in table[self.first_block.get(req, 0):]):
+            self._holes.add(req)
         self.pool.free(pages)
 
     def trim(self, req, new_len: int) -> int:
@@ -113,6 +127,7 @@ class CacheGroup:
     def release(self, req) -> int:
         table = self.tables.pop(req, None)
         self.first_block.pop(req, None)
+        self._holes.discard(req)
         if table is None:
             return 0
         pages = [p for p in table if p != NO_PAGE]

@@ -181,6 +181,12 @@ def test_random_orders_of_requests_keep_every_page_accounted_for(seed):
             new_len = min(96, live[r] + n)
             if new_len == live[r]:
                 continue
+            for g in m.groups:
+                # the count without a scan equals the count by looking at every block
+                t = g.table(r)
+                first = max(g._first_needed_block(live[r]), g.first_block.get(r, 0))
+                by_scan = sum(1 for b in range(first, (new_len + page - 1) // page) if b >= len(t) or t[b] == NO_PAGE)
+                assert g.pages_needed(r, live[r], new_len) == by_scan
             ok = m.can_reserve({r: new_len})
             try:
                 m.reserve(r, new_len)
