@@ -14,6 +14,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
+import numpy as np
+
 from .pages import OutOfPages, PagePool
 
 NO_PAGE = 0     # block-table entry of a block that holds nothing (the null page)
@@ -37,7 +39,8 @@ class StateSlot:
 class CacheGroup:
     """Host bookkeeping of one group: pool, block tables, trimming."""
 
-    def __init__(self, need: PagedKV, cache_ids: List[int], num_pages: int, page_size: int, name: str = ""):
+    def __init__(self, need: PagedKV, cache_ids: List[int], num_pages: int, page_size: int, name: str = "",
+                 max_blocks: Optional[int] = None):
         self.need = need
         self.cache_ids = list(cache_ids)
         self.page_size = page_size
@@ -48,6 +51,10 @@ class CacheGroup:
         # requests whose table may have a block without a page between first_block and its end; for all
         # others the blocks a step lacks are simply those beyond the table's end (no scan)
         self._holes: set = set()
+        # with `max_blocks`: every table also as an int32 row, kept in step with the list, so that a step
+        # copies a request's row into its upload buffer in one piece
+        self.max_blocks = max_blocks
+        self.rows: Dict[object, np.ndarray] = {}
 
     # -- how many new pages a request needs to hold positions [first_needed, new_len) -------
     def _first_needed_block(self, start: int) -> int:
@@ -81,6 +88,11 @@ class CacheGroup:
             table.append(NO_PAGE)
         for b, p in zip(want, pages):
             table[b] = p
+        if self.max_blocks is not None and want:
+            row = self.rows.get(req)
+            if row is None:
+                row = self.rows[req] = np.zeros(self.max_blocks, dtype=np.int32)
+            row[want] = pages
         return pages
 
     def give_back(self, req, pages: List[int]) -> None:
@@ -90,6 +102,8 @@ class CacheGroup:
         for b, p in enumerate(table):
             if p in back:
                 table[b] = NO_PAGE
+                if req in self.rows:
+                    self.rows[req][b] = NO_PAGE
         while table and table[-1] == NO_PAGE and len(table) > self.first_block.get(req, 0):
             table.pop()                              # what was reserved last lies at the end
         if any(p == NO_PAGE for p in table[self.first_block.get(req, 0):]):
@@ -107,6 +121,8 @@ class CacheGroup:
             if table[b] != NO_PAGE:
                 freed.append(table[b])
                 table[b] = NO_PAGE
+                if req in self.rows:
+                    self.rows[req][b] = NO_PAGE
         self.first_block[req] = max(self.first_block[req], min(keep_from, len(table)))
         self.pool.free(freed)
         return len(freed)
@@ -121,6 +137,8 @@ class CacheGroup:
             raise ValueError(f"cache group {self.name}: positions before {new_len} have left the window already")
         freed = [p for p in table[keep:] if p != NO_PAGE]
         del table[keep:]
+        if req in self.rows:
+            self.rows[req][keep:] = NO_PAGE
         self.pool.free(freed)
         return len(freed)
 
@@ -128,6 +146,7 @@ class CacheGroup:
         table = self.tables.pop(req, None)
         self.first_block.pop(req, None)
         self._holes.discard(req)
+        self.rows.pop(req, None)
         if table is None:
             return 0
         pages = [p for p in table if p != NO_PAGE]
@@ -136,3 +155,7 @@ class CacheGroup:
 
     def table(self, req) -> List[int]:
         return self.tables.get(req, [])
+
+    def row(self, req) -> Optional[np.ndarray]:
+        """The table as an int32 row of ``max_blocks`` entries (None if the request holds nothing yet)."""
+        return self.rows.get(req)

@@ -60,7 +60,7 @@ class CacheManager:
                 by_need.setdefault(need, []).append(c)
         for gi, (need, ids) in enumerate(by_need.items()):
             n = (pages_per_group or {}).get(gi, num_pages)
-            group = CacheGroup(need, ids, n + 1, page_size)
+            group = CacheGroup(need, ids, n + 1, page_size, max_blocks=self.max_blocks)
             self.groups.append(group)
             if device is not None:
                 shape = (len(ids), n + 1, need.num_kv_heads, page_size, need.head_dim)
@@ -147,10 +147,12 @@ class CacheManager:
     def block_table_rows(self, group_index: int, reqs: Sequence[object], out: np.ndarray) -> None:
         """Fill ``out[i, :]`` (int32, ``[len(reqs), max_blocks]``) with request i's pages."""
         g = self.groups[group_index]
-        out[:len(reqs)].fill(NO_PAGE)
         for i, r in enumerate(reqs):
-            t = g.table(r)
-            out[i, :len(t)] = t
+            row = g.row(r)
+            if row is None:
+                out[i].fill(NO_PAGE)
+            else:
+                out[i] = row
 
     def slot_ids(self, reqs: Sequence[object]) -> List[int]:
         return [self.slots.slot_of(r) for r in reqs]
@@ -179,3 +181,10 @@ class CacheManager:
                 raise AssertionError(f"{g.name}: pool says {sorted(held)} are out, tables hold {sorted(seen)}")
             if g.pool.in_use + g.pool.available != g.pool.capacity:
                 raise AssertionError(f"{g.name}: a page is lost")
+            for req, table in g.tables.items():
+                row = g.row(req)
+                mirror = [] if row is None else row.tolist()
+                if mirror[:len(table)] != table and any(p != NO_PAGE for p in table):
+                    raise AssertionError(f"{g.name}: the row of {req!r} differs from its table")
+                if any(p != NO_PAGE for p in mirror[len(table):]):
+                    raise AssertionError(f"{g.name}: the row of {req!r} holds pages beyond its table")

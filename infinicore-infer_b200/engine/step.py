@@ -89,6 +89,7 @@ class Engine:
         self._meta_host = [torch.zeros(cap, dtype=torch.int32, pin_memory=True) for _ in range(3)]
         self._meta_events: List[Optional[torch.cuda.Event]] = [None] * 3
         self._meta_turn = 0
+        self._decode_templates: Dict[int, tuple] = {}
         self._graphs: Dict[int, object] = {}
         self.steps_run = 0
         self.tokens_run = 0
@@ -238,10 +239,7 @@ class Engine:
         mb = self.cache.max_blocks
         for gi, off in enumerate(lay.tables):
             self.cache.block_table_rows(gi, reqs, host[off: off + nB * mb].reshape(nB, mb))
-        self._meta_dev[:lay.total].copy_(self._meta_host[turn][:lay.total], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self._meta_events[turn] = ev
+        self._copy_meta(turn, lay.total)
         ctx = self._context(lay, len(want_rows))
         ctx.host_req_start = req_start
         ctx.host_req_pos = list(starts) + [0] * (nB - B)
@@ -251,6 +249,43 @@ class Engine:
         ctx.short_rows = None if ctx.n_short == nT else self._meta_dev[lay.short_rows: lay.short_rows + ctx.n_short]
         ctx.tiles = self._meta_dev[lay.tiles: lay.tiles + len(tiles)]
         return ctx
+
+    def _copy_meta(self, turn: int, words: int) -> None:
+        self._meta_dev[:words].copy_(self._meta_host[turn][:words], non_blocking=True)
+        if self._meta_events[turn] is None:
+            self._meta_events[turn] = torch.cuda.Event()
+        self._meta_events[turn].record()
+
+    def _upload_decode_replay(self, entries, starts, bucket: int) -> None:
+        """The upload of a captured decode step that is only replayed: the same buffer contents as
+        ``_upload(..., pad_to=bucket)`` gives, without the device views that only a capture needs.
+        What does not change from step to step comes from a template made once per bucket."""
+        B = len(entries)
+        made = self._decode_templates.get(bucket)
+        if made is None:
+            lay = _Layout(bucket, bucket, len(self.cache.groups), self.cache.max_blocks)
+            t = np.zeros(lay.total, dtype=np.int32)
+            t[lay.row_req: lay.row_req + bucket] = np.arange(bucket)
+            t[lay.req_start: lay.req_start + bucket + 1] = np.arange(bucket + 1)
+            t[lay.short_rows: lay.short_rows + bucket] = np.arange(bucket)
+            t[lay.want_rows: lay.want_rows + bucket] = np.arange(bucket)
+            made = self._decode_templates[bucket] = (lay, t)
+        lay, template = made
+        turn = self._meta_turn
+        self._meta_turn = (turn + 1) % len(self._meta_host)
+        if self._meta_events[turn] is not None:
+            self._meta_events[turn].synchronize()
+        host = self._meta_host[turn].numpy()
+        host[:lay.total] = template
+        host[lay.tokens: lay.tokens + B] = [e.tokens[0] for e in entries]
+        host[lay.positions: lay.positions + B] = starts
+        host[lay.req_pos: lay.req_pos + B] = starts
+        reqs = [e.req_id for e in entries]
+        host[lay.slot_ids: lay.slot_ids + B] = self.cache.slot_ids(reqs)
+        mb = self.cache.max_blocks
+        for gi, off in enumerate(lay.tables):
+            self.cache.block_table_rows(gi, reqs, host[off: off + bucket * mb].reshape(bucket, mb))
+        self._copy_meta(turn, lay.total)
 
     def _context(self, lay: _Layout, n_want: int) -> StepContext:
         m, mb = self._meta_dev, self.cache.max_blocks
@@ -285,9 +320,11 @@ class Engine:
             dummy.decode_only = True
             self.model.forward(dummy, self.cache.views)
             torch.cuda.synchronize()
-        ctx = self._upload(entries, starts, B, B, pad_to=bucket)
-        ctx.decode_only = True
-        if rec is None:
+        if rec is not None:
+            self._upload_decode_replay(entries, starts, bucket)
+        else:
+            ctx = self._upload(entries, starts, B, B, pad_to=bucket)
+            ctx.decode_only = True
             from .. import kernels
             graph = torch.cuda.CUDAGraph()
             before = kernels.launch_count
@@ -298,11 +335,11 @@ class Engine:
         graph, out, launches = rec
         graph.replay()
         self.kernel_launches += launches
+        if all(len(e.want) == 1 for e in entries):
+            return out[:B]
         rows = []
         for i, e in enumerate(entries):
             rows.extend([i] * len(e.want))
-        if len(rows) == B and all(r == i for i, r in enumerate(rows)):
-            return out[:B]
         if not rows:
             return out[:0]
         return out[torch.tensor(rows, device=self.device)]
