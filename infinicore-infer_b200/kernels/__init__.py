@@ -354,7 +354,10 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
 
 
 def attention_tcgen05_supports(dh: int, page_size: int) -> bool:
-    return bool(_build.load("attention_tcgen05").jk_attention_tcgen05_supports(_c_int(dh), _c_int(page_size)))
+    """Head sizes 64 and 128 with pages that divide a tile of 128 keys and fill whole groups of 8 rows (the
+    same rule as the library's ``jk_attention_tcgen05_supports``; answered here so that a model the
+    kernel is not built for never compiles its module)."""
+    return dh in (64, 128) and page_size in (8, 16, 32, 64, 128)
 
 
 def attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
