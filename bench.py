@@ -33,6 +33,20 @@ SHAPE_2B = dict(model_type="minicpm", num_hidden_layers=40, hidden_size=2304, nu
                 num_key_value_heads=36, intermediate_size=5760, vocab_size=122753,
                 max_position_embeddings=4096, rms_norm_eps=1e-5, rope_theta=10000.0, scale_emb=12,
                 scale_depth=1.4, dim_model_base=256, tie_word_embeddings=True)
+# configs[3] and configs[4]: the shapes of the two serving-style workloads (--workload)
+SHAPE_1B = dict(model_type="minicpm", num_hidden_layers=52, hidden_size=1536, num_attention_heads=24,
+                num_key_value_heads=8, intermediate_size=3840, vocab_size=73440,
+                max_position_embeddings=4096, rms_norm_eps=1e-5, rope_theta=10000.0, scale_emb=12,
+                scale_depth=1.4, dim_model_base=256, tie_word_embeddings=True)
+SHAPE_8B = dict(model_type="fm9g", num_hidden_layers=32, hidden_size=4096, num_attention_heads=32,
+                num_key_value_heads=2, intermediate_size=16384, vocab_size=73448,
+                max_position_embeddings=4096, rms_norm_eps=1e-5, rope_theta=10000.0, scale_emb=12,
+                scale_depth=1.4, dim_model_base=256, tie_word_embeddings=False)
+WORKLOADS = {
+    # name: (shape, requests, prompt lengths, new tokens, portion size, token budget of a step)
+    "1b-mixed": (SHAPE_1B, 32, (16, 1024), 128, 256, 512),
+    "8b-serving": (SHAPE_8B, 64, (512, 2048), 256, 512, 2048),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -104,6 +118,64 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def run_workload(name, layers=None):
+    """A serving-style workload through the scheduler: all requests are submitted at once, prompts are
+    cut into portions under the step's token budget beside the others' decoded tokens, every request
+    generates its full count (no stop token).  Prints one JSON line of its own kind."""
+    import random
+    import torch
+    from infinicore_infer_b200.config import MiniCPMConfig
+    from infinicore_infer_b200.engine import Engine, Generator
+    from infinicore_infer_b200.parts import model_manifest
+    from infinicore_infer_b200.weights import DeviceRandomWeights
+
+    shape, n_req, (lo, hi), new_tokens, chunk, budget = WORKLOADS[name]
+    shape = dict(shape)
+    full_layers = shape["num_hidden_layers"]
+    if layers:
+        shape["num_hidden_layers"] = layers
+    cfg = MiniCPMConfig.from_dict(shape)
+    spec = cfg.model_spec()
+    dev, page = "cuda:0", 16
+    rng = random.Random(0)
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(rng.randint(lo, hi))] for _ in range(n_req)]
+    cache_tokens = sum(len(p) + new_tokens + page for p in prompts)
+    weights = DeviceRandomWeights(model_manifest(spec), seed=0, compute_dtype=torch.bfloat16, device=dev, std=0.02,
+                                  untied=not shape["tie_word_embeddings"])
+    engine = Engine(spec, weights, dtype=torch.bfloat16, device=dev, cache_tokens=cache_tokens, page_size=page,
+                    max_requests=n_req, max_step_tokens=budget)
+    results = []
+    with ClockSampler() as clocks:
+        for rep in range(2):                   # the first pass warms up (graph captures, lazy handles)
+            g = Generator(engine, max_batch=n_req, max_tokens_per_step=budget, chunk_size=chunk)
+            reqs = [g.submit(p, max_new_tokens=new_tokens, eos_token_ids=()) for p in prompts]
+            torch.cuda.synchronize()
+            l0 = engine.kernel_launches
+            t0 = time.perf_counter()
+            g.run()
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            generated = sum(len(r.generated) for r in reqs)
+            results.append((dt, generated, dict(g.scheduler.counters), engine.kernel_launches - l0))
+    dt, generated, counters, launches = results[-1]
+    prompt_tokens = sum(len(p) for p in prompts)
+    print(json.dumps({
+        "workload": name, "metric": "generated tok/s through the scheduler (host tokens in and out every step)",
+        "value": round(generated / dt, 1), "unit": "tokens/s", "seconds": round(dt, 3),
+        "generated_tokens": generated, "prompt_tokens": prompt_tokens,
+        "all_tokens_per_s": round((generated + prompt_tokens) / dt, 1),
+        "scheduler": counters, "gpu_launches": int(launches), "dtype": "bf16",
+        "data": "synthetic: random-init weights N(0,0.02), uniform random token ids",
+        "config": {"model": name, "layers": cfg.num_hidden_layers, "layers_of_shape": full_layers,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "requests": n_req, "prompt_len_min": lo, "prompt_len_max": hi, "new_tokens": new_tokens,
+                   "portion": chunk, "tokens_per_step": budget, "page_size": page},
+        "clocks": clocks.summary(),
+    }))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -117,6 +189,8 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
                     help="run a few steps between cudaProfilerStart/Stop (for ncu --profile-from-start off) and exit")
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="instead of the decode benchmark: a serving-style workload through the scheduler")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -129,6 +203,8 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload:
+        return run_workload(args.workload, args.layers)
 
     import torch
     from infinicore_infer_b200.config import MiniCPMConfig
