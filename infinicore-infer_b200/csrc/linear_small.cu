@@ -10,8 +10,10 @@
 // out in shared memory as [k / 8][row][8] so that its B registers are one conflict-free 16-byte
 // load as well.  No shuffle, no ldmatrix, no transposition of weights.
 //
-// A block's 4 warps are split into (tiles of 16 features) x (slices of K); the slices' partial
-// sums meet in shared memory and the first slice's warp runs the epilogue:
+// Two kernels share this layout.  `small_linear_tile_kernel` (below) takes every K whose 16-row tile
+// fits in shared memory: one block per tile, the whole tile in flight at once.  `small_linear_kernel`
+// takes longer K with a ring: a block's warps are split into (tiles of 16 features) x (slices of K).
+// In both the slices' partial sums meet in shared memory and the first slice's warp runs the epilogue:
 //   EPI_F32     out[m, n] = acc                       (float32; the residual add and the next
 //                                                      norm are the consumer's)
 //   EPI_SWIGLU  out[m, n] = silu(gate) * up           (bfloat16; the warp computes features n
@@ -187,6 +189,156 @@ small_linear_kernel(SmallLinearArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// The kernel for every K whose tile of 16 weight rows fits in shared memory (K <= 6400).  One block =
+// one tile of 16 features, its warps on slices of K, and NOTHING is staged or looped over: every
+// thread issues the cp.async copies of its whole share of the tile at once (before it waits for the
+// kernel before it: weights depend on nothing), so that the whole matrix is in flight over the GPU
+// from the first microsecond; a pure read of the matrix in this pattern takes 6.9 us for 32 MB where
+// a ring of 256 bytes per thread with the same access pattern takes 11.7.  The copies are committed
+// in four groups and the products start when the first has landed.  The activations are not staged
+// either: a thread reads its 16 bytes per block of 32 k straight from global memory (they sit in L2,
+// a few tens of KB that every block reads), a few blocks ahead.  Shared memory holds the tile only
+// (private to each thread: it reads back what it copied, so no barrier stands between copy and use);
+// the K slices' partial sums meet in the same memory once the products are done.
+//   EPI_SWIGLU here pairs 8 gate rows with their 8 up rows in one 16-row tile: a thread's accumulators
+//   c0, c1 are then the gate and c2, c3 the up of the same feature and activation rows.
+// ---------------------------------------------------------------------------------------------------
+constexpr int ST_GROUPS = 4;        // commit groups of a thread's copies
+constexpr int ST_AHEAD = 4;         // blocks of k the activation loads run ahead
+
+constexpr int ST_MAX_WARPS = 16;
+
+template <int MT, int EPI>
+__global__ void __launch_bounds__(ST_MAX_WARPS * 32)
+small_linear_tile_kernel(SmallLinearArgs a) {
+    pdl_trigger();
+    extern __shared__ __align__(16) unsigned char st_smem[];
+    uint4 *mine = reinterpret_cast<uint4 *>(st_smem) + threadIdx.x;       // [2 * per_slice][threads]
+    const int nthreads = blockDim.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;           // warp = K slice
+    const int g = lane >> 2, t = lane & 3;
+    const int kblocks = a.K / 32;
+    const int per_slice = (kblocks + a.ksplit - 1) / a.ksplit;
+    const int kb_begin = min(kblocks, warp * per_slice), kb_end = min(kblocks, kb_begin + per_slice);
+    const int nkb = kb_end - kb_begin;
+    const int per_group = (per_slice + ST_GROUPS - 1) / ST_GROUPS;
+    // weight rows of this thread: EPI_F32: features n0 + g and n0 + g + 8; EPI_SWIGLU: gate and up of n0 + g.
+    // Rows are clamped inside the matrix; what a clamped row yields is not stored.
+    const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? 8 : 16);
+    const size_t r0 = min(n0 + g, a.N - 1);
+    const size_t r1 = EPI == EPI_SWIGLU ? (size_t)a.N + min(n0 + g, a.N - 1) : (size_t)min(n0 + g + 8, a.N - 1);
+    const __nv_bfloat16 *p0 = a.w + r0 * a.K + (size_t)kb_begin * 32 + t * 8;
+    const __nv_bfloat16 *p1 = a.w + r1 * a.K + (size_t)kb_begin * 32 + t * 8;
+    for (int d = 0; d < per_slice; ++d) {
+        if (d < nkb) {
+            cp_async16(mine + (size_t)(2 * d) * nthreads, p0 + d * 32);
+            cp_async16(mine + (size_t)(2 * d + 1) * nthreads, p1 + d * 32);
+        }
+        if ((d + 1) % per_group == 0 || d + 1 == per_slice) cp_async_commit();
+    }
+    // every thread commits the same number of groups: pad to ST_GROUPS
+    for (int j = (per_slice + per_group - 1) / per_group; j < ST_GROUPS; ++j) cp_async_commit();
+    pdl_wait();          // the weights do not depend on the kernel before this one; the activations do
+
+    const __nv_bfloat16 *ap[MT];
+    bool arow[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        arow[m] = m * 8 + g < a.M;
+        ap[m] = a.act + (size_t)(arow[m] ? m * 8 + g : 0) * a.K + (size_t)kb_begin * 32 + t * 8;
+    }
+    float acc[MT][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+    uint4 bq[ST_AHEAD][MT];
+#pragma unroll
+    for (int d = 0; d < ST_AHEAD; ++d)
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+            bq[d][m] = (arow[m] && d < nkb) ? *reinterpret_cast<const uint4 *>(ap[m] + d * 32) : make_uint4(0, 0, 0, 0);
+
+    for (int q0 = 0; q0 < nkb; q0 += ST_AHEAD) {
+#pragma unroll
+        for (int d = 0; d < ST_AHEAD; ++d) {
+            const int q = q0 + d;
+            if (q < nkb) {
+                if (q % per_group == 0) {                       // the group of copies this block of k belongs to
+                    const int grp = q / per_group;
+                    if (grp == 0) cp_async_wait<ST_GROUPS - 1>();
+                    else if (grp == 1) cp_async_wait<ST_GROUPS - 2>();
+                    else if (grp == 2) cp_async_wait<ST_GROUPS - 3>();
+                    else cp_async_wait<0>();
+                }
+                const uint4 w0 = mine[(size_t)(2 * q) * nthreads], w1 = mine[(size_t)(2 * q + 1) * nthreads];
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    const uint4 b = bq[d][m];
+                    mma16816(acc[m], w0.x, w1.x, w0.y, w1.y, b.x, b.y);
+                    mma16816(acc[m], w0.z, w1.z, w0.w, w1.w, b.z, b.w);
+                    if (arow[m] && q + ST_AHEAD < nkb) bq[d][m] = *reinterpret_cast<const uint4 *>(ap[m] + (q + ST_AHEAD) * 32);
+                }
+            }
+        }
+    }
+    // partial sums of the K slices meet in shared memory (the tile's place: every product is done)
+    if (a.ksplit > 1) {
+        __syncthreads();
+        float *red_s = reinterpret_cast<float *>(st_smem);               // [warps][MT][4][32]
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) red_s[((warp * MT + m) * 4 + c) * 32 + lane] = acc[m][c];
+        __syncthreads();
+        if (warp == 0) {
+            for (int s = 1; s < a.ksplit; ++s)
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[m][c] += red_s[((s * MT + m) * 4 + c) * 32 + lane];
+        }
+    }
+    if (warp == 0) {
+        // accumulator element c of tile m: weight row g (+8 for c >= 2), activation row m*8 + 2t + (c & 1)
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int c = 0; c < (EPI == EPI_SWIGLU ? 2 : 4); ++c) {
+                const int row = m * 8 + 2 * t + (c & 1);
+                if (EPI == EPI_F32) {
+                    const int n = n0 + g + (c >> 1) * 8;
+                    if (n < a.N && row < a.M) reinterpret_cast<float *>(a.out)[(size_t)row * a.ldo + n] = acc[m][c];
+                } else {
+                    const int n = n0 + g;
+                    const float gate = acc[m][c], up = acc[m][c + 2];
+                    if (n < a.N && row < a.M)
+                        reinterpret_cast<__nv_bfloat16 *>(a.out)[(size_t)row * a.ldo + n] =
+                            __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+                }
+            }
+    }
+}
+
+// Shared memory of the tile kernel: the tile, padded to whole slices (and room for the partial sums).
+static size_t small_tile_smem(int K, int MT, int ksplit) {
+    const int per_slice = (K / 32 + ksplit - 1) / ksplit;
+    const size_t tile = (size_t)2 * per_slice * ksplit * 32 * 16;
+    const size_t red = (size_t)ksplit * MT * 4 * 32 * sizeof(float);
+    return tile > red ? tile : red;
+}
+
+template <int MT, int EPI>
+static int launch_tile(const SmallLinearArgs &a, size_t smem, cudaStream_t stream) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(small_linear_tile_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "linear_small: %s", cudaGetErrorString(e));
+    }
+    const int tiles = EPI == EPI_SWIGLU ? (a.N + 7) / 8 : (a.N + 15) / 16;
+    jk_launch(small_linear_tile_kernel<MT, EPI>, dim3(tiles), dim3(a.ksplit * 32), smem, stream, a);
+    JK_CHECK_LAUNCH("linear_small");
+    return JK_OK;
+}
+
 static size_t small_linear_smem(int K, int MT, int warps, int ring) {
     return (size_t)(K / 8) * MT * 8 * 16 + (size_t)ring * warps * 32 + (size_t)warps * 2 * MT * 4 * 32 * sizeof(float);
 }
@@ -221,6 +373,23 @@ JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, 
     JK_REQUIRE(epilogue == EPI_F32 || epilogue == EPI_SWIGLU, "linear_small: epilogue %d", epilogue);
     JK_REQUIRE(ldo >= N, "linear_small: output stride %d < N %d", ldo, N);
     const int MT = M <= 8 ? 1 : 2;
+    {
+        // the tile kernel: all warps of a block on one tile, as many slices of K as leave each at least two
+        // blocks of k; 16 warps when the tiles are too few to give every SM two blocks (the copies are
+        // issued by more threads and each slice is shorter), else 8
+        if (sms <= 0) sms = 148;
+        const int n_tiles = epilogue == EPI_SWIGLU ? (N + 7) / 8 : (N + 15) / 16;
+        int ksplit = n_tiles < 2 * sms ? ST_MAX_WARPS : SL_MAX_WARPS;
+        while (ksplit > 1 && (K / 32) / ksplit < 2) ksplit /= 2;
+        const size_t smem = small_tile_smem(K, MT, ksplit);
+        if (smem <= 200 * 1024) {
+            SmallLinearArgs a{(const __nv_bfloat16 *)act, (const __nv_bfloat16 *)w, out, M, N, K, ldo, ksplit, 0};
+            if (MT == 1 && epilogue == EPI_F32) return launch_tile<1, EPI_F32>(a, smem, stream);
+            if (MT == 2 && epilogue == EPI_F32) return launch_tile<2, EPI_F32>(a, smem, stream);
+            if (MT == 1) return launch_tile<1, EPI_SWIGLU>(a, smem, stream);
+            return launch_tile<2, EPI_SWIGLU>(a, smem, stream);
+        }
+    }
     const int tiles = (N + 15) / 16;
     if (sms <= 0) sms = 148;
     // Blocks of 4 warps, several per SM; a block works on one tile of 16 features at a time with its
