@@ -19,6 +19,11 @@
 //                EPI_RESIDUAL  out[m, n] += scale * acc              float32, in place (the residual stream)
 //                EPI_SWIGLU    out[m, n]  = silu(acc[n]) * acc[N+n]  bfloat16; W is [2N, K], gate rows then
 //                                                                    up rows, and a tile holds BN/2 of each.
+//                EPI_QKV       the columns are heads [q | k | v]: query and key heads are rotated (rotate-half,
+//                              angles from float32 cos/sin tables at the row's position) and rounded to
+//                              bfloat16; queries go to q_out, keys and values straight into their cache
+//                              pages through the block table (what a separate rotary kernel did with a
+//                              float32 copy of the product in between: src/models/jiuge/jiuge.cpp:200-218).
 // Rows, columns and the K range that a tile has beyond the matrices are zero-filled by TMA and
 // never stored.  Warp roles: warp 0 TMA, warp 1 MMA (and owner of the tensor-memory allocation),
 // warps 2..5 epilogue.  Every wait on an mbarrier is bounded; a wait that runs out records a code in
@@ -35,10 +40,23 @@
 
 JK_DEFINE_ERROR_BUFFER(jk_gemm_tcgen05)
 
-enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3 };
+enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_QKV = 4 };
 
 constexpr int TG_BM = 128, TG_BK = 64, TG_STAGES = 4, TG_THREADS = 192;
 constexpr unsigned TG_SPIN_LIMIT = 1u << 20;      // polls of one wait before it gives up
+
+// EPI_QKV: where the fused [q | k | v] projection's columns go (bfloat16 all).
+struct QkvDest {
+    __nv_bfloat16 *q_out;          // [M, nh * dh]
+    __nv_bfloat16 *k_pages;        // [pages, nkvh, page_size, dh]
+    __nv_bfloat16 *v_pages;
+    const float *cos_table;        // [positions, dh / 2], or null: no rotation
+    const float *sin_table;
+    const int *positions;          // [M]
+    const int *row_req;            // [M]
+    const int *block_table;        // [requests, max_blocks]
+    int nh, nkvh, dh, page_size, max_blocks;
+};
 
 struct TgArgs {
     void *out;
@@ -46,6 +64,7 @@ struct TgArgs {
     float scale;
     int *status;       // device word: 0, or the code of the wait that ran out
     int direct;        // 1: the output's rows are not 16-byte aligned, store from registers instead of by TMA
+    QkvDest qkv;       // EPI_QKV only
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -230,6 +249,76 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tc_fence_after();
             const unsigned acc = tmem + buf * BN + ((unsigned)(quarter * 32) << 16);
             const int row0 = m0 + quarter * 32, row = row0 + lane;
+            if (EPI == EPI_QKV) {
+                // thread = row: its position picks the angles and the cache slot; a head's two halves
+                // are read from tensor memory 32 pairs at a time, rotated and stored 64 bytes at a time
+                const QkvDest &d = a.qkv;
+                const int half = d.dh / 2;
+                int pos = 0;
+                size_t slot = 0;
+                if (row < a.M) {
+                    pos = d.positions[row];
+                    const int page = d.block_table[(size_t)d.row_req[row] * d.max_blocks + pos / d.page_size];
+                    slot = ((size_t)page * d.nkvh * d.page_size + (pos % d.page_size)) * d.dh;
+                }
+                const float *cs = d.cos_table ? d.cos_table + (size_t)pos * half : nullptr;
+                const float *sn = d.sin_table ? d.sin_table + (size_t)pos * half : nullptr;
+                // this row's angles for 32 pairs; with heads of 64 they are the same for every head of the tile
+                float cr[32], sr[32];
+                auto load_angles = [&](int part) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cs + part + i));
+                        const float4 s4 = __ldg(reinterpret_cast<const float4 *>(sn + part + i));
+                        cr[i] = c4.x; cr[i + 1] = c4.y; cr[i + 2] = c4.z; cr[i + 3] = c4.w;
+                        sr[i] = s4.x; sr[i + 1] = s4.y; sr[i + 2] = s4.z; sr[i + 3] = s4.w;
+                    }
+                };
+                if (cs != nullptr && half == 32) load_angles(0);
+#pragma unroll 1
+                for (int c0 = 0; c0 < OUT_COLS; c0 += d.dh) {
+                    if (n0 + c0 >= a.N) break;                             // warp-uniform
+                    const int h = (n0 + c0) / d.dh;
+                    __nv_bfloat16 *dst;
+                    if (h < d.nh) dst = d.q_out + ((size_t)row * d.nh + h) * d.dh;
+                    else if (h < d.nh + d.nkvh) dst = d.k_pages + slot + (size_t)(h - d.nh) * d.page_size * d.dh;
+                    else dst = d.v_pages + slot + (size_t)(h - d.nh - d.nkvh) * d.page_size * d.dh;
+                    const bool rotated = cs != nullptr && h < d.nh + d.nkvh;
+#pragma unroll 1
+                    for (int part = 0; part < half; part += 32) {
+                        unsigned x0[32], x1[32];
+                        tmem_ld32(acc + c0 + part, x0);
+                        tmem_ld32(acc + c0 + half + part, x1);
+                        if (rotated && half != 32) load_angles(part);
+                        if (row < a.M) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                unsigned w0[4], w1[4];
+#pragma unroll
+                                for (int e = 0; e < 8; e += 2) {
+                                    float y0[2], y1[2];
+#pragma unroll
+                                    for (int z = 0; z < 2; ++z) {
+                                        const float u = __uint_as_float(x0[i + e + z]), v = __uint_as_float(x1[i + e + z]);
+                                        y0[z] = rotated ? u * cr[i + e + z] - v * sr[i + e + z] : u;
+                                        y1[z] = rotated ? u * sr[i + e + z] + v * cr[i + e + z] : v;
+                                    }
+                                    const __nv_bfloat162 b0 = __floats2bfloat162_rn(y0[0], y0[1]);
+                                    const __nv_bfloat162 b1 = __floats2bfloat162_rn(y1[0], y1[1]);
+                                    w0[e / 2] = *reinterpret_cast<const unsigned *>(&b0);
+                                    w1[e / 2] = *reinterpret_cast<const unsigned *>(&b1);
+                                }
+                                *reinterpret_cast<uint4 *>(dst + part + i) = make_uint4(w0[0], w0[1], w0[2], w0[3]);
+                                *reinterpret_cast<uint4 *>(dst + half + part + i) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
+                continue;
+            }
             // columns per pass: a staging row is 128 bytes = 32 floats or 64 bfloat16
             constexpr int PASS = (EPI == EPI_F32 || EPI == EPI_RESIDUAL) ? 32 : 64;
 #pragma unroll 1
@@ -373,6 +462,33 @@ static int launch_tg(const CUtensorMap &ma, const CUtensorMap &mw, const CUtenso
     return JK_OK;
 }
 
+// The fused [q | k | v] projection with rotation and cache write in its epilogue.  Head sizes 64 and 128
+// (a 256-column tile holds whole heads, a head's halves are multiples of 32 columns).
+JK_EXPORT int jk_gemm_tcgen05_qkv_supports(int dh) { return dh == 64 || dh == 128; }
+
+JK_EXPORT int jk_gemm_tcgen05_qkv(const void *act, const void *w, int M, int K, void *q_out, void *k_pages, void *v_pages,
+                                  const float *cos_table, const float *sin_table, const int *positions,
+                                  const int *row_req, const int *block_table, int max_blocks, int page_size, int nh,
+                                  int nkvh, int dh, int *status, int sms, cudaStream_t stream) {
+    const int N = (nh + 2 * nkvh) * dh;
+    JK_REQUIRE(jk_gemm_tcgen05_qkv_supports(dh), "gemm_tcgen05_qkv: head size %d (64 and 128 are built)", dh);
+    JK_REQUIRE(M >= 1 && K >= 8 && K % 8 == 0 && nh >= 1 && nkvh >= 1, "gemm_tcgen05_qkv: M %d K %d heads %d/%d", M, K, nh, nkvh);
+    JK_REQUIRE(status != nullptr && q_out && k_pages && v_pages && positions && row_req && block_table && max_blocks > 0 && page_size > 0,
+               "gemm_tcgen05_qkv: a destination or index array is missing");
+    JK_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "gemm_tcgen05_qkv: cos and sin tables come together");
+    JK_REQUIRE((reinterpret_cast<uintptr_t>(act) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
+               (reinterpret_cast<uintptr_t>(q_out) & 15) == 0 && (reinterpret_cast<uintptr_t>(k_pages) & 15) == 0 &&
+               (reinterpret_cast<uintptr_t>(v_pages) & 15) == 0, "gemm_tcgen05_qkv: operands must be 16-byte aligned");
+    if (sms <= 0) sms = 148;
+    CUtensorMap ma, mw;
+    if (int rc = tensor_map_2d(act, M, K, K, TG_BM, TG_BK, 2, &ma)) return rc;
+    if (int rc = tensor_map_2d(w, N, K, K, 256, TG_BK, 2, &mw)) return rc;
+    TgArgs a{nullptr, M, N, K, N, 1.f, status, 0,
+             QkvDest{(__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_pages, (__nv_bfloat16 *)v_pages, cos_table, sin_table,
+                     positions, row_req, block_table, nh, nkvh, dh, page_size, max_blocks}};
+    return launch_tg<256, EPI_QKV>(ma, mw, ma, a, sms, stream);
+}
+
 // K must keep rows 16-byte aligned for TMA; everything else is free.
 JK_EXPORT int jk_gemm_tcgen05_supports(int M, int N, int K) { return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0; }
 
@@ -388,7 +504,7 @@ JK_EXPORT int jk_gemm_tcgen05(const void *act, const void *w, void *out, int M, 
     const int out_bytes = (epilogue == EPI_F32 || epilogue == EPI_RESIDUAL) ? 4 : 2;
     CUtensorMap ma, mw, mo;
     if (int rc = tensor_map_2d(act, M, K, K, TG_BM, TG_BK, 2, &ma)) return rc;
-    TgArgs a{out, M, N, K, ldo, scale, status, 0};
+    TgArgs a{out, M, N, K, ldo, scale, status, 0, QkvDest{}};
     // the output goes out by TMA when its rows are 16-byte aligned, else straight from registers
     a.direct = ((size_t)ldo * out_bytes) % 16 != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0;
     if (a.direct) mo = ma;

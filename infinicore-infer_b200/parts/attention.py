@@ -54,14 +54,22 @@ class Attention:
         from .. import kernels
         s, rt = self.spec, self.runtime
         T = ctx.ntok
-        qkv = rt.linear(h, self.w_qkv, out_dtype=torch.float32)
         q = rt.empty(T, s.num_heads * s.head_dim)
         table = ctx.block_tables[view.group_index]
         pos = self.position
-        kernels.rope_kv(qkv, self.b_qkv, ctx.positions, ctx.row_req, table, view.page_size,
-                        pos.cos if pos else None, pos.sin if pos else None,
-                        pos.interleaved if pos else False, q, view.k_pages, view.v_pages,
-                        T, s.num_heads, s.num_kv_heads, s.head_dim, write_cache=writes_cache)
+        n, k = self.w_qkv.shape
+        if (rt.dtype == torch.bfloat16 and self.b_qkv is None and writes_cache and not (pos and pos.interleaved)
+                and not rt.library_products_only and rt.takes_tcgen05(T, n, k)
+                and kernels.gemm_tcgen05_qkv_supports(s.head_dim)):
+            # many rows: the product's epilogue rotates and writes q and the cache itself
+            kernels.gemm_tcgen05_qkv(h, self.w_qkv, q, view.k_pages, view.v_pages, pos.cos if pos else None,
+                                     pos.sin if pos else None, ctx.positions, ctx.row_req, table, s.num_heads)
+        else:
+            qkv = rt.linear(h, self.w_qkv, out_dtype=torch.float32)
+            kernels.rope_kv(qkv, self.b_qkv, ctx.positions, ctx.row_req, table, view.page_size,
+                            pos.cos if pos else None, pos.sin if pos else None,
+                            pos.interleaved if pos else False, q, view.k_pages, view.v_pages,
+                            T, s.num_heads, s.num_kv_heads, s.head_dim, write_cache=writes_cache)
         o = rt.empty(T, s.num_heads * s.head_dim)
         self._attend(q, o, view, table, ctx)
         return rt.product(o, self.w_o)       # the block adds it to the residual stream

@@ -112,6 +112,52 @@ def _scatter_pages(k, v, tables, page, num_pages, dtype):
     return kp, vp
 
 
+@pytest.mark.parametrize("nh,nkvh,dh,page,with_rope", [(4, 2, 64, 16, True), (3, 1, 128, 8, True), (5, 5, 64, 32, False),
+                                                        (9, 3, 64, 16, True)])
+def test_qkv_product_rotates_and_writes_the_cache_in_its_epilogue(K, nh, nkvh, dh, page, with_rope):
+    """The tcgen05 product of the fused [q | k | v] matrix, rotation and cache write included, against
+    a plain product, a plain rotation and a plain scatter."""
+    assert K.gemm_tcgen05_qkv_supports(dh) and not K.gemm_tcgen05_qkv_supports(48)
+    g = torch.Generator().manual_seed(dh + nh)
+    lens = [(37, 150), (0, 131), (200, 3)]              # (start position, rows): tiles of 128 rows straddle requests
+    T = sum(n for _, n in lens)
+    kdim = 200
+    width = (nh + 2 * nkvh) * dh
+    act = (torch.randn(T, kdim, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(width, kdim, generator=g) * 0.1).to(torch.bfloat16)
+    max_pos, theta = 384, 5000.0
+    j = torch.arange(dh // 2, dtype=torch.float64)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] / theta ** (j / (dh // 2))
+    cos, sin = ang.cos().float(), ang.sin().float()
+    max_blocks = max_pos // page
+    table = (torch.randperm(3 * max_blocks, generator=g) + 1).view(3, max_blocks).to(torch.int32)
+    positions = torch.cat([torch.arange(s, s + n) for s, n in lens]).to(torch.int32)
+    row_req = torch.cat([torch.full((n,), i) for i, (_, n) in enumerate(lens)]).to(torch.int32)
+    num_pages = 3 * max_blocks + 1
+    kp = torch.zeros(num_pages, nkvh, page, dh, dtype=torch.bfloat16, device=DEV)
+    vp = torch.zeros_like(kp)
+    q_out = torch.full((T, nh * dh), 9.0, dtype=torch.bfloat16, device=DEV)
+    K.gemm_tcgen05_qkv(act.to(DEV), w.to(DEV), q_out, kp, vp, cos.to(DEV) if with_rope else None,
+                       sin.to(DEV) if with_rope else None, positions.to(DEV), row_req.to(DEV), table.to(DEV), nh)
+    K.check_gemm_status(DEV)
+    x = act.double() @ w.double().T
+    q = x[:, :nh * dh].view(T, nh, dh)
+    k = x[:, nh * dh:(nh + nkvh) * dh].view(T, nkvh, dh)
+    v = x[:, (nh + nkvh) * dh:].view(T, nkvh, dh)
+    rot = (lambda t: plain_rope(t, positions, theta)) if with_rope else (lambda t: t)
+    _close(q_out.view(T, nh, dh), rot(q), torch.bfloat16, scale=2.0)
+    want_k = torch.zeros(num_pages, nkvh, page, dh, dtype=torch.float64)
+    want_v = torch.zeros_like(want_k)
+    rk = rot(k)
+    for t in range(T):
+        p = int(table[row_req[t], positions[t] // page])
+        want_k[p, :, positions[t] % page] = rk[t]
+        want_v[p, :, positions[t] % page] = v[t]
+    _close(kp, want_k, torch.bfloat16, scale=2.0)
+    _close(vp, want_v, torch.bfloat16, scale=2.0)
+    assert float(kp[0].abs().max()) == 0.0              # the null page was not written
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkvh,dh,page,interleaved", [(6, 2, 48, 8, False), (4, 4, 16, 16, True),
                                                           (3, 1, 128, 4, False), (8, 2, 256, 32, False)])
