@@ -24,13 +24,27 @@
 
 JK_DEFINE_ERROR_BUFFER(jk_linear_small)
 
-enum { EPI_F32 = 0, EPI_SWIGLU = 1 };
+enum { EPI_F32 = 0, EPI_SWIGLU = 1, EPI_QKV = 2 };
+
+// EPI_QKV: where the fused [q | k | v] projection's columns go (bfloat16 all).
+struct SmallQkvDest {
+    __nv_bfloat16 *q_out;          // [M, nh * dh]
+    __nv_bfloat16 *k_pages;        // [pages, nkvh, page_size, dh]
+    __nv_bfloat16 *v_pages;
+    const float *cos_table;        // [positions, dh / 2], or null: no rotation
+    const float *sin_table;
+    const int *positions;          // [M]
+    const int *row_req;            // [M]
+    const int *block_table;        // [requests, max_blocks]
+    int nh, nkvh, dh, page_size, max_blocks;
+};
 
 struct SmallLinearArgs {
     const __nv_bfloat16 *act;   // [M, K]
     const __nv_bfloat16 *w;     // [N, K]  (EPI_SWIGLU: [2N, K], gate rows then up rows)
     void *out;                  // EPI_F32: float [M, ldo]; EPI_SWIGLU: bfloat16 [M, ldo]
     int M, N, K, ldo, ksplit, n_units;
+    SmallQkvDest qkv;           // EPI_QKV only
 };
 
 constexpr int SL_MAX_WARPS = 8;
@@ -203,6 +217,12 @@ small_linear_kernel(SmallLinearArgs a) {
 // the K slices' partial sums meet in the same memory once the products are done.
 //   EPI_SWIGLU here pairs 8 gate rows with their 8 up rows in one 16-row tile: a thread's accumulators
 //   c0, c1 are then the gate and c2, c3 the up of the same feature and activation rows.
+//   EPI_QKV (the fused [q | k | v] projection) pairs, in the same way, 8 features of a head's first half
+//   with their partners in the second half, so that a thread holds both members of a rotary pair; it
+//   rotates query and key heads (rotate-half, float32 cos/sin at the row's position), rounds to
+//   bfloat16 and writes queries to q_out and keys and values into their cache pages through the block
+//   table (what a separate kernel did with a float32 copy of the product in between:
+//   src/models/jiuge/jiuge.cpp:200-218).
 // ---------------------------------------------------------------------------------------------------
 constexpr int ST_GROUPS = 4;        // commit groups of a thread's copies
 constexpr int ST_AHEAD = 4;         // blocks of k the activation loads run ahead
@@ -226,8 +246,15 @@ small_linear_tile_kernel(SmallLinearArgs a) {
     // weight rows of this thread: EPI_F32: features n0 + g and n0 + g + 8; EPI_SWIGLU: gate and up of n0 + g.
     // Rows are clamped inside the matrix; what a clamped row yields is not stored.
     const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? 8 : 16);
-    const size_t r0 = min(n0 + g, a.N - 1);
-    const size_t r1 = EPI == EPI_SWIGLU ? (size_t)a.N + min(n0 + g, a.N - 1) : (size_t)min(n0 + g + 8, a.N - 1);
+    // EPI_QKV: block -> (head, 8 pairs of it); rows j0 + g of the head's first half and of its second half
+    const int qkv_tiles = EPI == EPI_QKV ? a.qkv.dh / 16 : 1;
+    const int qkv_head = blockIdx.x / qkv_tiles, qkv_j0 = (blockIdx.x % qkv_tiles) * 8;
+    size_t r0 = min(n0 + g, a.N - 1);
+    size_t r1 = EPI == EPI_SWIGLU ? (size_t)a.N + min(n0 + g, a.N - 1) : (size_t)min(n0 + g + 8, a.N - 1);
+    if (EPI == EPI_QKV) {
+        r0 = (size_t)qkv_head * a.qkv.dh + qkv_j0 + g;
+        r1 = r0 + a.qkv.dh / 2;
+    }
     const __nv_bfloat16 *p0 = a.w + r0 * a.K + (size_t)kb_begin * 32 + t * 8;
     const __nv_bfloat16 *p1 = a.w + r1 * a.K + (size_t)kb_begin * 32 + t * 8;
     for (int d = 0; d < per_slice; ++d) {
@@ -298,7 +325,36 @@ small_linear_tile_kernel(SmallLinearArgs a) {
                     for (int c = 0; c < 4; ++c) acc[m][c] += red_s[((s * MT + m) * 4 + c) * 32 + lane];
         }
     }
-    if (warp == 0) {
+    if (warp == 0 && EPI == EPI_QKV) {
+        const SmallQkvDest &d = a.qkv;
+        const int half = d.dh / 2, j = qkv_j0 + g, h = qkv_head;
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int row = m * 8 + 2 * t + c;
+                if (row >= a.M) continue;
+                const int pos = d.positions[row];
+                float y0 = acc[m][c], y1 = acc[m][c + 2];                 // elements j and j + half of head h
+                if (d.cos_table != nullptr && h < d.nh + d.nkvh) {
+                    const float cs = d.cos_table[(size_t)pos * half + j], sn = d.sin_table[(size_t)pos * half + j];
+                    const float x0 = y0, x1 = y1;
+                    y0 = x0 * cs - x1 * sn;
+                    y1 = x0 * sn + x1 * cs;
+                }
+                __nv_bfloat16 *dst;
+                if (h < d.nh) {
+                    dst = d.q_out + ((size_t)row * d.nh + h) * d.dh;
+                } else {
+                    const int page = d.block_table[(size_t)d.row_req[row] * d.max_blocks + pos / d.page_size];
+                    const size_t slot = ((size_t)page * d.nkvh * d.page_size + (pos % d.page_size)) * d.dh;
+                    dst = (h < d.nh + d.nkvh ? d.k_pages + (size_t)(h - d.nh) * d.page_size * d.dh
+                                             : d.v_pages + (size_t)(h - d.nh - d.nkvh) * d.page_size * d.dh) + slot;
+                }
+                dst[j] = __float2bfloat16_rn(y0);
+                dst[j + half] = __float2bfloat16_rn(y1);
+            }
+    } else if (warp == 0) {
         // accumulator element c of tile m: weight row g (+8 for c >= 2), activation row m*8 + 2t + (c & 1)
 #pragma unroll
         for (int m = 0; m < MT; ++m)
@@ -333,7 +389,7 @@ static int launch_tile(const SmallLinearArgs &a, size_t smem, cudaStream_t strea
         cudaError_t e = cudaFuncSetAttribute(small_linear_tile_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "linear_small: %s", cudaGetErrorString(e));
     }
-    const int tiles = EPI == EPI_SWIGLU ? (a.N + 7) / 8 : (a.N + 15) / 16;
+    const int tiles = EPI == EPI_SWIGLU ? (a.N + 7) / 8 : (a.N + 15) / 16;     // EPI_QKV: 16 features a tile as well
     jk_launch(small_linear_tile_kernel<MT, EPI>, dim3(tiles), dim3(a.ksplit * 32), smem, stream, a);
     JK_CHECK_LAUNCH("linear_small");
     return JK_OK;
@@ -366,6 +422,36 @@ JK_EXPORT int jk_linear_small_supports(int M, int N, int K) {
     return small_linear_smem(K, MT, 8, small_linear_ring(K, MT, 8)) <= 200 * 1024;
 }
 
+// The fused [q | k | v] projection of at most 16 rows with rotation and cache write in its epilogue.
+// Any head size that is a multiple of 16; K up to what a 16-row tile may take of shared memory.
+JK_EXPORT int jk_linear_small_qkv_supports(int M, int K, int dh) {
+    if (M < 1 || M > 16 || K < 32 || K % 32 || dh < 16 || dh % 16) return 0;
+    int ksplit = ST_MAX_WARPS;
+    while (ksplit > 1 && (K / 32) / ksplit < 2) ksplit /= 2;
+    return small_tile_smem(K, M <= 8 ? 1 : 2, ksplit) <= 200 * 1024;
+}
+
+JK_EXPORT int jk_linear_small_qkv(const void *act, const void *w, int M, int K, void *q_out, void *k_pages, void *v_pages,
+                                  const float *cos_table, const float *sin_table, const int *positions,
+                                  const int *row_req, const int *block_table, int max_blocks, int page_size, int nh,
+                                  int nkvh, int dh, int sms, cudaStream_t stream) {
+    JK_REQUIRE(jk_linear_small_qkv_supports(M, K, dh), "linear_small_qkv: M %d K %d head size %d is outside what the kernel takes", M, K, dh);
+    JK_REQUIRE(nh >= 1 && nkvh >= 1 && q_out && k_pages && v_pages && positions && row_req && block_table && max_blocks > 0 && page_size > 0,
+               "linear_small_qkv: a destination or index array is missing");
+    JK_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "linear_small_qkv: cos and sin tables come together");
+    if (sms <= 0) sms = 148;
+    const int N = (nh + 2 * nkvh) * dh, MT = M <= 8 ? 1 : 2;
+    const int n_tiles = N / 16;
+    int ksplit = n_tiles < 2 * sms ? ST_MAX_WARPS : SL_MAX_WARPS;
+    while (ksplit > 1 && (K / 32) / ksplit < 2) ksplit /= 2;
+    const size_t smem = small_tile_smem(K, MT, ksplit);
+    SmallLinearArgs a{(const __nv_bfloat16 *)act, (const __nv_bfloat16 *)w, nullptr, M, N, K, N, ksplit, 0,
+                      SmallQkvDest{(__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_pages, (__nv_bfloat16 *)v_pages, cos_table,
+                                   sin_table, positions, row_req, block_table, nh, nkvh, dh, page_size, max_blocks}};
+    if (MT == 1) return launch_tile<1, EPI_QKV>(a, smem, stream);
+    return launch_tile<2, EPI_QKV>(a, smem, stream);
+}
+
 JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, int N, int K, int ldo,
                               int epilogue, int sms, cudaStream_t stream) {
     JK_REQUIRE(jk_linear_small_supports(M, N, K), "linear_small: M %d N %d K %d is outside what the kernel takes "
@@ -383,7 +469,7 @@ JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, 
         while (ksplit > 1 && (K / 32) / ksplit < 2) ksplit /= 2;
         const size_t smem = small_tile_smem(K, MT, ksplit);
         if (smem <= 200 * 1024) {
-            SmallLinearArgs a{(const __nv_bfloat16 *)act, (const __nv_bfloat16 *)w, out, M, N, K, ldo, ksplit, 0};
+            SmallLinearArgs a{(const __nv_bfloat16 *)act, (const __nv_bfloat16 *)w, out, M, N, K, ldo, ksplit, 0, SmallQkvDest{}};
             if (MT == 1 && epilogue == EPI_F32) return launch_tile<1, EPI_F32>(a, smem, stream);
             if (MT == 2 && epilogue == EPI_F32) return launch_tile<2, EPI_F32>(a, smem, stream);
             if (MT == 1) return launch_tile<1, EPI_SWIGLU>(a, smem, stream);
@@ -401,7 +487,7 @@ JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, 
     while (ksplit > 1 && (K / 32) / ksplit < 2) ksplit /= 2;
     const int tiles_per_unit = warps / ksplit;
     SmallLinearArgs a{(const __nv_bfloat16 *)act, (const __nv_bfloat16 *)w, out, M, N, K, ldo, ksplit,
-                      (tiles + tiles_per_unit - 1) / tiles_per_unit};
+                      (tiles + tiles_per_unit - 1) / tiles_per_unit, SmallQkvDest{}};
     const int ring = small_linear_ring(K, MT, warps);
     const size_t smem = small_linear_smem(K, MT, warps, ring);
     int per_sm = (int)((220 * 1024) / (smem + 1024));

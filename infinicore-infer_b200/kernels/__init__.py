@@ -198,6 +198,45 @@ def linear_small(act: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue
     return out
 
 
+def linear_small_qkv_supports(m: int, k: int, dh: int) -> bool:
+    """Whether the small-row product can take the fused [q | k | v] projection with rotation and cache
+    write in its epilogue."""
+    return bool(_build.load("linear_small").jk_linear_small_qkv_supports(_c_int(m), _c_int(k), _c_int(dh)))
+
+
+def linear_small_qkv(act: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor,
+                     v_pages: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                     positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor, nh: int) -> torch.Tensor:
+    """The fused [q | k | v] projection of at most 16 bfloat16 rows: query and key heads rotated
+    (rotate-half), queries to ``q_out``, keys and values into their pages, all from the epilogue."""
+    _check_qkv_args("linear_small_qkv", act, w, q_out, k_pages, v_pages, cos, sin, positions, row_req, block_table, nh)
+    m, k = act.shape
+    _, nkvh, page_size, dh = k_pages.shape
+    lib = _build.load("linear_small")
+    _check("linear_small", lib.jk_linear_small_qkv(
+        _ptr(act), _ptr(w), _c_int(m), _c_int(k), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(cos), _ptr(sin),
+        _ptr(positions), _ptr(row_req), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size), _c_int(nh),
+        _c_int(nkvh), _c_int(dh), _c_int(_sm_count(act.device)), _stream()))
+    return q_out
+
+
+def _check_qkv_args(what, act, w, q_out, k_pages, v_pages, cos, sin, positions, row_req, block_table, nh) -> None:
+    for name, t in (("act", act), ("w", w), ("q_out", q_out), ("k_pages", k_pages), ("v_pages", v_pages)):
+        _need(t, name, torch.bfloat16)
+    for name, t in (("positions", positions), ("row_req", row_req), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    m, k = act.shape
+    _, nkvh, page_size, dh = k_pages.shape
+    if w.shape != ((nh + 2 * nkvh) * dh, k) or q_out.numel() < m * nh * dh or v_pages.shape != k_pages.shape:
+        raise KernelError(f"{what}: act {tuple(act.shape)}, w {tuple(w.shape)}, pages {tuple(k_pages.shape)}")
+    if positions.numel() < m or row_req.numel() < m:
+        raise KernelError(f"{what}: positions or row_req hold fewer entries than rows")
+    if cos is not None:
+        _need(cos, "cos", torch.float32); _need(sin, "sin", torch.float32)
+        if cos.shape[1] != dh // 2 or sin.shape != cos.shape:
+            raise KernelError(f"{what}: cos/sin tables must be [positions, head_dim/2]")
+
+
 def gemm_tcgen05_qkv_supports(dh: int) -> bool:
     """Head sizes for which the tcgen05 product can rotate and store [q | k | v] in its epilogue."""
     return dh in (64, 128)
@@ -209,20 +248,9 @@ def gemm_tcgen05_qkv(act: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_
     """The fused [q | k | v] projection of bfloat16 rows: ``act @ w^T`` with query and key heads rotated
     (rotate-half; cos/sin ``[positions, dh/2]`` float32 or None), queries written to ``q_out`` and keys and
     values into their pages through ``block_table``, all from the product's epilogue."""
-    for name, t in (("act", act), ("w", w), ("q_out", q_out), ("k_pages", k_pages), ("v_pages", v_pages)):
-        _need(t, name, torch.bfloat16)
-    for name, t in (("positions", positions), ("row_req", row_req), ("block_table", block_table)):
-        _need(t, name, torch.int32)
+    _check_qkv_args("gemm_tcgen05_qkv", act, w, q_out, k_pages, v_pages, cos, sin, positions, row_req, block_table, nh)
     m, k = act.shape
     _, nkvh, page_size, dh = k_pages.shape
-    if w.shape != ((nh + 2 * nkvh) * dh, k) or q_out.numel() < m * nh * dh or v_pages.shape != k_pages.shape:
-        raise KernelError(f"gemm_tcgen05_qkv: act {tuple(act.shape)}, w {tuple(w.shape)}, pages {tuple(k_pages.shape)}")
-    if positions.numel() < m or row_req.numel() < m:
-        raise KernelError("gemm_tcgen05_qkv: positions or row_req hold fewer entries than rows")
-    if cos is not None:
-        _need(cos, "cos", torch.float32); _need(sin, "sin", torch.float32)
-        if cos.shape[1] != dh // 2 or sin.shape != cos.shape:
-            raise KernelError("gemm_tcgen05_qkv: cos/sin tables must be [positions, head_dim/2]")
     lib = _build.load("gemm_tcgen05")
     _check("gemm_tcgen05", lib.jk_gemm_tcgen05_qkv(
         _ptr(act), _ptr(w), _c_int(m), _c_int(k), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(cos), _ptr(sin),

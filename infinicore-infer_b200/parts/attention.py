@@ -58,11 +58,15 @@ class Attention:
         table = ctx.block_tables[view.group_index]
         pos = self.position
         n, k = self.w_qkv.shape
-        if (rt.dtype == torch.bfloat16 and self.b_qkv is None and writes_cache and not (pos and pos.interleaved)
-                and not rt.library_products_only and rt.takes_tcgen05(T, n, k)
-                and kernels.gemm_tcgen05_qkv_supports(s.head_dim)):
-            # many rows: the product's epilogue rotates and writes q and the cache itself
+        # the product's epilogue can rotate and write q and the cache itself: no float32 copy of the
+        # product, no rotary kernel (the tcgen05 kernel for many rows, the small-row kernel for few)
+        fusable = (rt.dtype == torch.bfloat16 and self.b_qkv is None and writes_cache
+                   and not (pos and pos.interleaved) and not rt.library_products_only)
+        if fusable and rt.takes_tcgen05(T, n, k) and kernels.gemm_tcgen05_qkv_supports(s.head_dim):
             kernels.gemm_tcgen05_qkv(h, self.w_qkv, q, view.k_pages, view.v_pages, pos.cos if pos else None,
+                                     pos.sin if pos else None, ctx.positions, ctx.row_req, table, s.num_heads)
+        elif fusable and T <= 16 and kernels.linear_small_qkv_supports(T, k, s.head_dim):
+            kernels.linear_small_qkv(h, self.w_qkv, q, view.k_pages, view.v_pages, pos.cos if pos else None,
                                      pos.sin if pos else None, ctx.positions, ctx.row_req, table, s.num_heads)
         else:
             qkv = rt.linear(h, self.w_qkv, out_dtype=torch.float32)

@@ -158,6 +158,49 @@ def test_qkv_product_rotates_and_writes_the_cache_in_its_epilogue(K, nh, nkvh, d
     assert float(kp[0].abs().max()) == 0.0              # the null page was not written
 
 
+@pytest.mark.parametrize("nh,nkvh,dh,page,with_rope,rows", [(4, 2, 64, 16, True, 8), (3, 1, 128, 8, True, 1), (5, 5, 48, 32, False, 16),
+                                                             (9, 3, 16, 16, True, 11), (2, 2, 80, 4, True, 5)])
+def test_small_row_qkv_product_rotates_and_writes_the_cache_in_its_epilogue(K, nh, nkvh, dh, page, with_rope, rows):
+    """The same for at most 16 rows (decoded tokens of several requests): the small-row kernel."""
+    kdim = 160
+    assert K.linear_small_qkv_supports(rows, kdim, dh) and not K.linear_small_qkv_supports(17, kdim, dh)
+    assert not K.linear_small_qkv_supports(rows, kdim, 24)
+    g = torch.Generator().manual_seed(dh + nh + rows)
+    width = (nh + 2 * nkvh) * dh
+    act = (torch.randn(rows, kdim, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(width, kdim, generator=g) * 0.1).to(torch.bfloat16)
+    max_pos, theta = 96, 5000.0
+    j = torch.arange(dh // 2, dtype=torch.float64)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] / theta ** (j / (dh // 2))
+    cos, sin = ang.cos().float(), ang.sin().float()
+    max_blocks = max_pos // page
+    table = (torch.randperm(rows * max_blocks, generator=g) + 1).view(rows, max_blocks).to(torch.int32)
+    positions = torch.randint(0, max_pos, (rows,), generator=g).to(torch.int32)      # one decoded token per request
+    row_req = torch.arange(rows, dtype=torch.int32)
+    num_pages = rows * max_blocks + 1
+    kp = torch.zeros(num_pages, nkvh, page, dh, dtype=torch.bfloat16, device=DEV)
+    vp = torch.zeros_like(kp)
+    q_out = torch.full((rows, nh * dh), 9.0, dtype=torch.bfloat16, device=DEV)
+    K.linear_small_qkv(act.to(DEV), w.to(DEV), q_out, kp, vp, cos.to(DEV) if with_rope else None,
+                       sin.to(DEV) if with_rope else None, positions.to(DEV), row_req.to(DEV), table.to(DEV), nh)
+    x = act.double() @ w.double().T
+    q = x[:, :nh * dh].view(rows, nh, dh)
+    k = x[:, nh * dh:(nh + nkvh) * dh].view(rows, nkvh, dh)
+    v = x[:, (nh + nkvh) * dh:].view(rows, nkvh, dh)
+    rot = (lambda t: plain_rope(t, positions, theta)) if with_rope else (lambda t: t)
+    _close(q_out.view(rows, nh, dh), rot(q), torch.bfloat16, scale=2.0)
+    want_k = torch.zeros(num_pages, nkvh, page, dh, dtype=torch.float64)
+    want_v = torch.zeros_like(want_k)
+    rk = rot(k)
+    for t in range(rows):
+        p = int(table[row_req[t], positions[t] // page])
+        want_k[p, :, positions[t] % page] = rk[t]
+        want_v[p, :, positions[t] % page] = v[t]
+    _close(kp, want_k, torch.bfloat16, scale=2.0)
+    _close(vp, want_v, torch.bfloat16, scale=2.0)
+    assert float(kp[0].abs().max()) == 0.0              # the null page was not written
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkvh,dh,page,interleaved", [(6, 2, 48, 8, False), (4, 4, 16, 16, True),
                                                           (3, 1, 128, 4, False), (8, 2, 256, 32, False)])
