@@ -37,7 +37,9 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # the raw handle of the current stream of the current device (a Stream object costs microseconds
+    # to build, and every launch asks)
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, contiguous=True):

@@ -68,6 +68,7 @@ class Runtime:
         self.library_products_only = False   # True: every bfloat16 product goes to the library
         self.legacy_tensor_cores = False     # True: prefill attention on mma.sync even where tcgen05 is built
         self.tcgen05_min_tiles = 96          # fewest 128x128 output tiles for which the tcgen05 kernel is used
+        self.tcgen05_min_rows = 1024         # ... and fewest rows: below, the library's split-K kernels win
 
     def empty(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
@@ -119,10 +120,12 @@ class Runtime:
         return PendingProduct(self, act, weight)
 
     def takes_tcgen05(self, m: int, n: int, k: int) -> bool:
-        """The tcgen05 kernel works on tiles of 128 rows: it takes a product that has enough tiles to
-        fill most of the GPU; below that (a few dozen rows) the library's small-row kernels are used."""
+        """The tcgen05 kernel works on 128 x 256 tiles with one block per SM: it takes a product that has
+        enough rows and tiles to keep every SM on full tiles (measured on the 2B shape: level with the
+        library, epilogue fusions included, from about a thousand rows; at a few hundred rows the
+        library's smaller tiles and split K are up to twice as fast)."""
         from .. import kernels
-        if self.dtype != torch.bfloat16 or self.library_products_only or m <= 16:
+        if self.dtype != torch.bfloat16 or self.library_products_only or m < max(17, self.tcgen05_min_rows):
             return False
         tiles = -(-m // 128) * -(-n // 128)
         return tiles >= self.tcgen05_min_tiles and kernels.gemm_tcgen05_supports(m, n, k)

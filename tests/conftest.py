@@ -41,11 +41,18 @@ TINY_C = dict(
     model_type="minicpm", num_hidden_layers=2, hidden_size=80, num_attention_heads=6, num_key_value_heads=2,
     head_dim=48, intermediate_size=136, vocab_size=301, max_position_embeddings=288, rms_norm_eps=3e-6,
     rope_theta=50000.0, scale_emb=7.0, scale_depth=2.1, dim_model_base=20, tie_word_embeddings=True)
+# A fourth with heads of 64, the size for which the tcgen05 attention kernel and the fused q/k/v epilogue
+# of the tcgen05 product are built (grouped heads 2:1).
+TINY_D = dict(
+    model_type="minicpm", num_hidden_layers=2, hidden_size=128, num_attention_heads=2, num_key_value_heads=1,
+    intermediate_size=200, vocab_size=333, max_position_embeddings=448, rms_norm_eps=1e-5,
+    rope_theta=20000.0, scale_emb=5.0, scale_depth=1.7, dim_model_base=32, tie_word_embeddings=True)
 # Matrices are N(0, std) with std near 1/sqrt(hidden): every product keeps its input's variance, so
 # attention scores spread over several units (a sharp softmax) and a wrong key, page or position
 # moves the logits far beyond any tolerance.  (With N(0, 0.02) scores are all near zero, every
 # softmax is flat, and dropping one key among hundreds would hide inside the rounding.)
-TINY = {"A": (TINY_A, 0, 0.125, 0.01), "B": (TINY_B, 1, 0.1, 0.02), "C": (TINY_C, 2, 0.11, 0.03)}
+TINY = {"A": (TINY_A, 0, 0.125, 0.01), "B": (TINY_B, 1, 0.1, 0.02), "C": (TINY_C, 2, 0.11, 0.03),
+        "D": (TINY_D, 3, 0.09, 0.02)}
 
 
 def make_folder(tmp_path_factory, name):

@@ -21,7 +21,7 @@ DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 # bfloat16: activations are rounded to 8 significant bits about five times a layer; with 2-3 layers
 # the logits carry an error of about sqrt(5 L) * 2^-9 = 0.8 % of their scale; three times that is allowed.
 TOL = {"float32": 3e-5, "bfloat16": 2.5e-2}
-LENGTHS = {"A": [5, 47, 130], "B": [1, 40, 97], "C": [33, 64, 100]}
+LENGTHS = {"A": [5, 47, 130], "B": [1, 40, 97], "C": [33, 64, 100], "D": [9, 140, 300]}
 
 
 def make_engine(folder, dtype, cache_tokens, **kw):
@@ -66,7 +66,7 @@ def engines(tiny_models):
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_tail_and_portions_agree_with_the_plain_implementation(tiny_models, engines, name, dtype):
     eng = engines(name, dtype)
     for i, n in enumerate(LENGTHS[name]):
@@ -98,14 +98,41 @@ def test_every_product_kernel_gives_the_same_model(tiny_models, name):
         eng = make_engine(tiny_models[name][0], "bfloat16", 256)
         if mode == "tcgen05":
             eng.runtime.tcgen05_min_tiles = 1
+            eng.runtime.tcgen05_min_rows = 17
         else:
             eng.runtime.library_products_only = True
         got = run(eng, steps)
         check(got, "r", want, TOL["bfloat16"], f"{name} products by {mode}")
 
 
+def test_the_tcgen05_kernels_carry_a_whole_model(tiny_models):
+    """Heads of 64: portions of more than 8 rows run the tcgen05 attention kernel; with the row limit of
+    the tcgen05 product lowered, the q/k/v product rotates and writes the cache in its epilogue, gate/up
+    applies SwiGLU in its epilogue and o/down add into the residual stream by TMA.  Whole, in portions
+    (several 128-row tiles, ragged ends) and mixed with decoded tokens, against the plain implementation."""
+    eng = make_engine(tiny_models["D"][0], "bfloat16", 1024)
+    eng.runtime.tcgen05_min_tiles = 1
+    eng.runtime.tcgen05_min_rows = 17
+    toks, want = expected(tiny_models, "D", 400, 300)
+    toks2, want2 = expected(tiny_models, "D", 401, 150)
+    for what, steps in (("whole", whole("r", toks)), ("portions", portions("r", toks, sizes=(140, 2, 129, 20, 9))),
+                        ("tail", tail_decode("r", toks))):
+        got = run(eng, steps)
+        check(got, "r", want, TOL["bfloat16"], f"D tcgen05 {what}")
+    # two requests at once: a portion of one beside decoded tokens of the other
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:200], "want": list(range(200))}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": toks[200:201], "want": [0]},
+                                     {"id": "b", "tokens": toks2[:149], "want": list(range(149))}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": toks[201:300], "want": list(range(99))},
+                                     {"id": "b", "tokens": toks2[149:150], "want": [0]}], "end": ["a", "b"]}]
+    got = run(eng, steps)
+    check(got, "a", want, TOL["bfloat16"], "D tcgen05 mixed a")
+    check(got, "b", want2, TOL["bfloat16"], "D tcgen05 mixed b")
+    eng.check()
+
+
 @pytest.mark.parametrize("dtype", list(DTYPES))
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_requests_in_a_pool_so_small_that_pages_are_used_again(tiny_models, name, dtype):
     lens = {"a": 70, "b": 33, "c": 90, "d": 48, "e": 61, "f": 20}
     reqs, wants = {}, {}
