@@ -1,0 +1,257 @@
+// The step of the standard decoder stack, run from native code: one call launches every kernel of a
+// step (embedding, the layers, the final norm, the output product) where the Python parts would make
+// a dozen calls a layer.  It runs the same kernels with the same routing as the parts do:
+//
+//   rows <= 16            the weight-streaming kernels of linear_small.cu (q/k/v with rotation and cache
+//                         write in the epilogue, gate/up with SwiGLU in the epilogue)
+//   rows >= min_rows      the tcgen05 kernels of gemm_tcgen05.cu (q/k/v epilogue, SwiGLU epilogue, residual
+//                         add by TMA)
+//   in between            cuBLAS, bfloat16 operands, float32 accumulation and output, with the rotary
+//                         kernel, the SwiGLU kernel and the fused add + norm kernel around it
+//   attention             tiles of requests with many rows -> attention_tcgen05 (or the mma.sync kernel);
+//                         rows of requests with few rows -> the split-key decode kernel
+//
+// The kernels live in their own shared objects; the caller hands their entry points over once
+// (jk_runner_bind).  Everything a step needs arrives in four plain structs; nothing is allocated here.
+// (The reference's counterpart is the per-device worker that runs inferDeviceBatch,
+// src/models/jiuge/jiuge.cpp:126-305.)
+#include "common.cuh"
+
+#include <cublas_v2.h>
+#include <mutex>
+
+JK_DEFINE_ERROR_BUFFER(jk_runner)
+
+// ---- entry points of the kernel modules (signatures as in their sources) -------------------------------
+extern "C" {
+typedef int (*EmbedFn)(const int *, int, const void *, int, int, float, float *, cudaStream_t);
+typedef int (*AddRmsnormFn)(float *, const void *, int, float, const float *, float, float, void *, int, const int *, int,
+                            int, cudaStream_t);
+typedef int (*SwigluFn)(const void *, int, void *, int, int, int, cudaStream_t);
+typedef int (*RopeKvFn)(const void *, int, int, const float *, const int *, const int *, const int *, int, int,
+                        const float *, const float *, int, void *, void *, void *, int, int, int, int, int, int,
+                        cudaStream_t);
+typedef int (*LinearSmallFn)(const void *, const void *, void *, int, int, int, int, int, int, cudaStream_t);
+typedef int (*LinearSmallQkvFn)(const void *, const void *, int, int, void *, void *, void *, const float *, const float *,
+                                const int *, const int *, const int *, int, int, int, int, int, int, cudaStream_t);
+typedef int (*GemmTcgen05Fn)(const void *, const void *, void *, int, int, int, int, int, float, int *, int, cudaStream_t);
+typedef int (*GemmTcgen05QkvFn)(const void *, const void *, int, int, void *, void *, void *, const float *, const float *,
+                                const int *, const int *, const int *, int, int, int, int, int, int *, int, cudaStream_t);
+typedef int (*AttentionDecodeFn)(const void *, const void *, const void *, void *, float *, const int *, int, const int *,
+                                 const int *, const int *, int, int, int, int, int, float, int, int, cudaStream_t);
+typedef int (*AttentionPrefillFn)(const void *, const void *, const void *, void *, const int *, int, int, const int *,
+                                  const int *, const int *, int, int, int, int, int, float, int, cudaStream_t);
+typedef int (*AttentionTcgen05Fn)(const void *, const void *, const void *, void *, const int *, int, int, const int *,
+                                  const int *, const int *, int, int, int, int, int, int, float, int, int *, cudaStream_t);
+typedef const char *(*LastErrorFn)();
+}
+
+struct RunnerFns {
+    EmbedFn embed;
+    AddRmsnormFn add_rmsnorm;
+    SwigluFn swiglu;
+    RopeKvFn rope_kv;
+    LinearSmallFn linear_small;
+    LinearSmallQkvFn linear_small_qkv;
+    GemmTcgen05Fn gemm_tcgen05;
+    GemmTcgen05QkvFn gemm_tcgen05_qkv;
+    AttentionDecodeFn attention_decode;
+    AttentionPrefillFn attention_prefill;
+    AttentionTcgen05Fn attention_tcgen05;
+    LastErrorFn err_elementwise, err_linear_small, err_gemm_tcgen05, err_attention, err_attention_tcgen05;
+};
+static RunnerFns g_fns = {};
+static bool g_bound = false;
+
+JK_EXPORT int jk_runner_bind(const RunnerFns *fns) {
+    JK_REQUIRE(fns != nullptr, "runner_bind: no table");
+    const void *const *p = reinterpret_cast<const void *const *>(fns);
+    for (size_t i = 0; i < sizeof(RunnerFns) / sizeof(void *); ++i)
+        JK_REQUIRE(p[i] != nullptr, "runner_bind: entry %d of the table is empty", (int)i);
+    g_fns = *fns;
+    g_bound = true;
+    return JK_OK;
+}
+
+// What never changes from step to step.
+struct RunnerModel {
+    int layers, hidden, heads, kv_heads, head_dim, intermediate, vocab;
+    int page_size, max_blocks, num_pages, window;
+    int sms, tcgen05_min_rows, tcgen05_min_tiles;
+    int attention_tcgen05;          // 1: tiles go to the tcgen05 attention kernel, 0: to the mma.sync kernel
+    int embed_dtype;                // JK_F32 or JK_BF16
+    float embed_scale, residual_scale, logit_scale, softmax_scale, final_eps;
+    const void *embedding;          // [vocab, hidden]
+    const void *lm_head;            // [vocab, hidden] bfloat16
+    const float *final_norm;        // [hidden]
+    const float *cos_table;         // [positions, head_dim / 2] or null
+    const float *sin_table;
+    int *status;                    // the word in which the tcgen05 kernels record a wait that ran out
+};
+
+struct RunnerLayer {
+    const void *w_qkv, *w_o, *w_gate_up, *w_down;      // bfloat16 [N, K]
+    const float *norm1, *norm2;
+    float eps1, eps2;
+    void *k_pages, *v_pages;                           // bfloat16 [pages, kv_heads, page_size, head_dim]
+};
+
+// One step's batch (device arrays of the step's metadata buffer) and where its logits go.
+struct RunnerStep {
+    int ntok, nreq, n_want, n_tiles, n_short, splits;
+    const int *tokens, *positions, *row_req, *req_start, *req_pos, *want_rows, *short_rows, *tiles, *block_table;
+    float *logits;                  // [n_want, vocab]
+};
+
+// Buffers for `max_tokens` rows, made once by the caller.
+struct RunnerScratch {
+    float *x;                       // [T, hidden] the residual stream
+    void *h;                        // bf16 [T, hidden]
+    float *qkv;                     // [T, (heads + 2 kv_heads) * head_dim]
+    void *q, *o;                    // bf16 [T, heads * head_dim]
+    float *delta;                   // [T, hidden]
+    float *gate_up;                 // [T, 2 * intermediate]
+    void *act;                      // bf16 [T, intermediate]
+    void *hw;                       // bf16 [max wanted rows, hidden]
+    float *decode_scratch;          // partial results of the split-key attention
+    void *workspace;                // for the library
+    long long workspace_bytes;
+};
+
+static int g_launches = 0;      // kernels launched by the last jk_runner_forward (the library's count as one each)
+JK_EXPORT int jk_runner_launches() { return g_launches; }
+
+#define RUN(module, call)                                                                                   \
+    do {                                                                                                    \
+        ++g_launches;                                                                                       \
+        if (int rc_ = (call)) {                                                                             \
+            snprintf(jk_error_buffer(), 512, "%s", g_fns.err_##module());                                   \
+            return rc_;                                                                                     \
+        }                                                                                                   \
+    } while (0)
+
+// ---- the library product: out[M, N] (float32) = act[M, K] * w[N, K]^T, bfloat16 operands --------------------
+// cublasGemmEx with the library's own choice of kernel (it splits K for narrow outputs by itself), float32
+// accumulation; the handle works in the caller's workspace so that nothing is allocated inside a capture.
+static cublasHandle_t g_blas = nullptr;
+static std::mutex g_blas_mutex;
+
+static int lt_product(const void *act, const void *w, float *out, int M, int N, int K, const RunnerScratch &s, cudaStream_t stream) {
+    std::lock_guard<std::mutex> lock(g_blas_mutex);
+    if (!g_blas && cublasCreate(&g_blas) != CUBLAS_STATUS_SUCCESS) JK_FAIL(JK_CUDA_ERROR, "runner: cublasCreate failed");
+    if (cublasSetStream(g_blas, stream) != CUBLAS_STATUS_SUCCESS ||
+        cublasSetWorkspace(g_blas, s.workspace, (size_t)s.workspace_bytes) != CUBLAS_STATUS_SUCCESS)
+        JK_FAIL(JK_CUDA_ERROR, "runner: the library refused the stream or the workspace");
+    // row-major out[M, N] is column-major [N, M] = W^T (op T on the column-major [K, N]) * act (column-major [K, M])
+    const float one = 1.f, zero = 0.f;
+    ++g_launches;
+    const cublasStatus_t st = cublasGemmEx(g_blas, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &one, w, CUDA_R_16BF, K, act, CUDA_R_16BF, K,
+                                           &zero, out, CUDA_R_32F, N, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT_TENSOR_OP);
+    if (st != CUBLAS_STATUS_SUCCESS) JK_FAIL(JK_CUDA_ERROR, "runner: the library's product of %d x %d x %d failed with %d", M, N, K, (int)st);
+    return JK_OK;
+}
+
+static bool takes_tcgen05(const RunnerModel &m, int rows, int n, int k) {
+    if (rows <= 16 || k % 8) return false;
+    // fewer rows are taken only if the output is so wide that its tiles make several waves all the same
+    if (rows < m.tcgen05_min_rows && (long long)((rows + 127) / 128) * ((n + 255) / 256) < 3LL * m.sms) return false;
+    const long long tiles = (long long)((rows + 127) / 128) * ((n + 127) / 128);
+    return tiles >= m.tcgen05_min_tiles;
+}
+
+// out (float32 [rows, n]) = act * w^T by whichever kernel takes `rows`
+static int product_f32(const RunnerModel &m, const RunnerScratch &s, const void *act, const void *w, float *out, int rows, int n,
+                       int k, cudaStream_t stream) {
+    if (rows <= 16 && k % 32 == 0) {
+        RUN(linear_small, g_fns.linear_small(act, w, out, rows, n, k, n, 0, m.sms, stream));
+    } else if (takes_tcgen05(m, rows, n, k)) {
+        RUN(gemm_tcgen05, g_fns.gemm_tcgen05(act, w, out, rows, n, k, n, 0, 1.f, m.status, m.sms, stream));
+    } else {
+        if (int rc = lt_product(act, w, out, rows, n, k, s, stream)) return rc;
+    }
+    return JK_OK;
+}
+
+// x += scale * (act * w^T): in the product's epilogue where that exists, else left pending for the next norm
+static int product_into_residual(const RunnerModel &m, const RunnerScratch &s, const void *act, const void *w, int rows, int n,
+                                 int k, bool *pending, cudaStream_t stream) {
+    if (takes_tcgen05(m, rows, n, k)) {
+        RUN(gemm_tcgen05, g_fns.gemm_tcgen05(act, w, s.x, rows, n, k, n, 2, m.residual_scale, m.status, m.sms, stream));
+        *pending = false;
+        return JK_OK;
+    }
+    *pending = true;
+    return product_f32(m, s, act, w, s.delta, rows, n, k, stream);
+}
+
+JK_EXPORT int jk_runner_forward(const RunnerModel *mp, const RunnerLayer *layers, const RunnerStep *sp, const RunnerScratch *cp,
+                                cudaStream_t stream) {
+    JK_REQUIRE(g_bound, "runner_forward: jk_runner_bind has not been called");
+    JK_REQUIRE(mp && layers && sp && cp, "runner_forward: a struct is missing");
+    const RunnerModel &m = *mp;
+    const RunnerStep &st = *sp;
+    const RunnerScratch &s = *cp;
+    const int T = st.ntok, d = m.hidden, nh = m.heads, nkvh = m.kv_heads, dh = m.head_dim, di = m.intermediate;
+    const int nq = (nh + 2 * nkvh) * dh;
+    g_launches = 0;
+    if (T == 0) return JK_OK;
+    RUN(elementwise, g_fns.embed(st.tokens, T, m.embedding, m.embed_dtype, d, m.embed_scale, s.x, stream));
+    bool pending = false;       // s.delta holds a product that has not been added to x yet
+    for (int l = 0; l < m.layers; ++l) {
+        const RunnerLayer &L = layers[l];
+        // ---- attention ----
+        RUN(elementwise, g_fns.add_rmsnorm(s.x, pending ? s.delta : nullptr, JK_F32, m.residual_scale, L.norm1, L.eps1, 1.f, s.h,
+                                           JK_BF16, nullptr, T, d, stream));
+        pending = false;
+        if (takes_tcgen05(m, T, nq, d) && (dh == 64 || dh == 128)) {
+            RUN(gemm_tcgen05, g_fns.gemm_tcgen05_qkv(s.h, L.w_qkv, T, d, s.q, L.k_pages, L.v_pages, m.cos_table, m.sin_table,
+                                                     st.positions, st.row_req, st.block_table, m.max_blocks, m.page_size, nh,
+                                                     nkvh, dh, m.status, m.sms, stream));
+        } else if (T <= 16 && d % 32 == 0 && dh % 16 == 0) {
+            RUN(linear_small, g_fns.linear_small_qkv(s.h, L.w_qkv, T, d, s.q, L.k_pages, L.v_pages, m.cos_table, m.sin_table,
+                                                     st.positions, st.row_req, st.block_table, m.max_blocks, m.page_size, nh,
+                                                     nkvh, dh, m.sms, stream));
+        } else {
+            if (int rc = product_f32(m, s, s.h, L.w_qkv, s.qkv, T, nq, d, stream)) return rc;
+            RUN(elementwise, g_fns.rope_kv(s.qkv, JK_F32, nq, nullptr, st.positions, st.row_req, st.block_table, m.max_blocks,
+                                           m.page_size, m.cos_table, m.sin_table, 0, s.q, L.k_pages, L.v_pages, JK_BF16, T, nh,
+                                           nkvh, dh, 1, stream));
+        }
+        if (st.n_tiles > 0) {
+            if (m.attention_tcgen05)
+                RUN(attention_tcgen05, g_fns.attention_tcgen05(s.q, L.k_pages, L.v_pages, s.o, st.tiles, st.n_tiles, T, st.req_start,
+                                                               st.req_pos, st.block_table, m.max_blocks, m.num_pages, m.page_size,
+                                                               nh, nkvh, dh, m.softmax_scale, m.window, m.status, stream));
+            else
+                RUN(attention, g_fns.attention_prefill(s.q, L.k_pages, L.v_pages, s.o, st.tiles, st.n_tiles, 128, st.req_start,
+                                                       st.req_pos, st.block_table, m.max_blocks, m.page_size, nh, nkvh, dh,
+                                                       m.softmax_scale, m.window, stream));
+        }
+        if (st.n_short > 0)
+            RUN(attention, g_fns.attention_decode(s.q, L.k_pages, L.v_pages, s.o, st.splits > 1 ? s.decode_scratch : nullptr,
+                                                  st.short_rows, st.n_short, st.positions, st.row_req, st.block_table,
+                                                  m.max_blocks, m.page_size, nh, nkvh, dh, m.softmax_scale, m.window, st.splits,
+                                                  stream));
+        if (int rc = product_into_residual(m, s, s.o, L.w_o, T, d, nh * dh, &pending, stream)) return rc;
+        // ---- feed-forward ----
+        RUN(elementwise, g_fns.add_rmsnorm(s.x, pending ? s.delta : nullptr, JK_F32, m.residual_scale, L.norm2, L.eps2, 1.f, s.h,
+                                           JK_BF16, nullptr, T, d, stream));
+        pending = false;
+        if (T <= 16 && d % 32 == 0) {
+            RUN(linear_small, g_fns.linear_small(s.h, L.w_gate_up, s.act, T, di, d, di, 1, m.sms, stream));
+        } else if (takes_tcgen05(m, T, di, d)) {
+            RUN(gemm_tcgen05, g_fns.gemm_tcgen05(s.h, L.w_gate_up, s.act, T, di, d, di, 3, 1.f, m.status, m.sms, stream));
+        } else {
+            if (int rc = lt_product(s.h, L.w_gate_up, s.gate_up, T, 2 * di, d, s, stream)) return rc;
+            RUN(elementwise, g_fns.swiglu(s.gate_up, JK_F32, s.act, JK_BF16, T, di, stream));
+        }
+        if (int rc = product_into_residual(m, s, s.act, L.w_down, T, d, di, &pending, stream)) return rc;
+    }
+    // the logit scale rides on the final norm, which looks at the wanted rows only
+    if (st.n_want > 0) {
+        RUN(elementwise, g_fns.add_rmsnorm(s.x, pending ? s.delta : nullptr, JK_F32, m.residual_scale, m.final_norm, m.final_eps,
+                                           m.logit_scale, s.hw, JK_BF16, st.want_rows, st.n_want, d, stream));
+        if (int rc = product_f32(m, s, s.hw, m.lm_head, st.logits, st.n_want, m.vocab, d, stream)) return rc;
+    }
+    return JK_OK;
+}

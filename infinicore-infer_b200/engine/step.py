@@ -12,6 +12,9 @@ once per batch-size bucket, with the batch padded by rows that read and write th
 """
 from __future__ import annotations
 
+import gc
+import os
+
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -67,7 +70,7 @@ class Engine:
 
     def __init__(self, spec, weights, dtype: torch.dtype = torch.bfloat16, device="cuda:0",
                  cache_tokens: int = 4096, page_size: int = 16, max_requests: int = 64,
-                 max_step_tokens: int = 8192, use_graphs: bool = True):
+                 max_step_tokens: int = 8192, use_graphs: bool = True, native_runner: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
         self.spec = spec
@@ -94,6 +97,11 @@ class Engine:
         self.steps_run = 0
         self.tokens_run = 0
         self.kernel_launches = 0      # this package's kernels launched by steps (replayed graphs included)
+        # the standard stack is issued from native code (csrc/runner.cu); other models through the parts
+        self.runner = None
+        if native_runner and os.environ.get("JK_NO_RUNNER") != "1":
+            from .runner import NativeRunner
+            self.runner = NativeRunner.build(self)
 
     # ---- construction -------------------------------------------------------------------------
     @classmethod
@@ -148,13 +156,21 @@ class Engine:
             from .. import kernels
             ctx = self._upload(entries, starts, len(entries), sum(len(e.tokens) for e in entries))
             before = kernels.launch_count
-            logits = self.model.forward(ctx, self.cache.views)
+            logits = self._forward(ctx)
             self.kernel_launches += kernels.launch_count - before
         for r, n in new_len.items():
             self.cache.commit(r, n)
         self.steps_run += 1
         self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits
+
+    def _forward(self, ctx: StepContext) -> torch.Tensor:
+        if self.runner is not None:
+            from .. import kernels
+            logits = self.runner.forward(ctx)
+            kernels.launch_count += self.runner.launches
+            return logits
+        return self.model.forward(ctx, self.cache.views)
 
     # ---- checks that run before anything touches the device ------------------------------------
     def _validate(self, entries: Sequence[StepEntry]) -> None:
@@ -318,7 +334,7 @@ class Engine:
             # step exactly once, at the replay below.
             dummy = self._upload([], [], 0, 0, pad_to=bucket)
             dummy.decode_only = True
-            self.model.forward(dummy, self.cache.views)
+            self._forward(dummy)
             torch.cuda.synchronize()
         if rec is not None:
             self._upload_decode_replay(entries, starts, bucket)
@@ -328,8 +344,16 @@ class Engine:
             from .. import kernels
             graph = torch.cuda.CUDAGraph()
             before = kernels.launch_count
-            with torch.cuda.graph(graph):
-                out = self.model.forward(ctx, self.cache.views)
+            # no garbage collection while capturing: an unreachable engine's graphs, destroyed by the collector
+            # in the middle of this capture, would invalidate it
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    out = self._forward(ctx)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             rec = (graph, out, kernels.launch_count - before)
             self._graphs[bucket] = rec
         graph, out, launches = rec

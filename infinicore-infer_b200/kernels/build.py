@@ -28,7 +28,10 @@ MODULES: Dict[str, List[str]] = {
     "linear_small": ["linear_small.cu"],
     "gemm_tcgen05": ["gemm_tcgen05.cu"],
     "attention_tcgen05": ["attention_tcgen05.cu"],
+    "runner": ["runner.cu"],
 }
+# libraries a module links against (the others need the CUDA runtime only)
+LINK: Dict[str, List[str]] = {"runner": ["-lcublas"]}
 HEADERS = ["common.cuh", "attention_static_scratch.h"]
 
 # -use_fast_math is deliberately absent: expf, division and sqrt stay accurate.
@@ -71,7 +74,7 @@ def build_dir() -> str:
 
 def _digest(module: str) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + LINK.get(module, [])).encode())
     for name in MODULES[module] + HEADERS:
         with open(os.path.join(CSRC, name), "rb") as f:
             h.update(name.encode())
@@ -107,7 +110,8 @@ def build(module: str, verbose: bool = True) -> str:
                 return so
             nvcc = find_nvcc()
             tmp = f"{so}.tmp{os.getpid()}"
-            cmd = [nvcc] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp] + [os.path.join(CSRC, s) for s in MODULES[module]]
+            cmd = ([nvcc] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp] + [os.path.join(CSRC, s) for s in MODULES[module]]
+                   + LINK.get(module, []))
             if verbose:
                 print(f"[infinicore_infer_b200] compiling kernel module '{module}' for sm_100a ...",
                       file=sys.stderr, flush=True)

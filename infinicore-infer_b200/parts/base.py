@@ -125,7 +125,11 @@ class Runtime:
         library, epilogue fusions included, from about a thousand rows; at a few hundred rows the
         library's smaller tiles and split K are up to twice as fast)."""
         from .. import kernels
-        if self.dtype != torch.bfloat16 or self.library_products_only or m < max(17, self.tcgen05_min_rows):
+        if self.dtype != torch.bfloat16 or self.library_products_only or m <= 16:
+            return False
+        # fewer rows are taken only if the output is so wide that its tiles make several waves all the same
+        # (the output matrix over the vocabulary)
+        if m < self.tcgen05_min_rows and -(-m // 128) * -(-n // 256) < 3 * kernels._sm_count(self.device):
             return False
         tiles = -(-m // 128) * -(-n // 128)
         return tiles >= self.tcgen05_min_tiles and kernels.gemm_tcgen05_supports(m, n, k)

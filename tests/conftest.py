@@ -45,7 +45,7 @@ TINY_C = dict(
 # of the tcgen05 product are built (grouped heads 2:1).
 TINY_D = dict(
     model_type="minicpm", num_hidden_layers=2, hidden_size=128, num_attention_heads=2, num_key_value_heads=1,
-    intermediate_size=200, vocab_size=333, max_position_embeddings=448, rms_norm_eps=1e-5,
+    intermediate_size=192, vocab_size=333, max_position_embeddings=448, rms_norm_eps=1e-5,
     rope_theta=20000.0, scale_emb=5.0, scale_depth=1.7, dim_model_base=32, tie_word_embeddings=True)
 # Matrices are N(0, std) with std near 1/sqrt(hidden): every product keeps its input's variance, so
 # attention scores spread over several units (a sharp softmax) and a wrong key, page or position

@@ -1,0 +1,47 @@
+"""The native runner (csrc/runner.cu) issues the same kernels as the parts do: the two ways of running a
+step must give the same logits, and the runner must leave alone what it is not built for."""
+import numpy as np
+import pytest
+import torch
+
+from test_replay import TOL, check, expected, make_engine, run
+from trace_helpers import mixed, portions, tail_decode, whole
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_native_runner_and_parts_give_the_same_logits(tiny_models, name):
+    folder = tiny_models[name][0]
+    native = make_engine(folder, "bfloat16", 1024)
+    parts = make_engine(folder, "bfloat16", 1024, native_runner=False)
+    assert native.runner is not None and parts.runner is None
+    toks, want = expected(tiny_models, name, 500, 200)
+    toks2, want2 = expected(tiny_models, name, 501, 90)
+    reqs = {"a": toks, "b": toks2}
+    plan = [{"a": 150}, {"a": 1, "b": 60}, {"a": 2, "b": 1}, {"a": 1, "b": 1}, {"a": 46, "b": 28}]
+    for what, steps in (("whole", whole("a", toks)), ("tail", tail_decode("a", toks)),
+                        ("portions", portions("a", toks, sizes=(40, 3, 130, 9, 2))), ("mixed", mixed(reqs, plan))):
+        got_n, got_p = run(native, steps), run(parts, steps)
+        assert got_n.keys() == got_p.keys()
+        scale = np.abs(want).max()
+        for key in got_n:
+            # the same kernels in the same order: equal to the last bit, except where a product of 17 to
+            # 1023 rows went to the library through two doors (torch.mm there, cublasGemmEx here), whose
+            # choice of kernel may differ
+            assert np.abs(got_n[key] - got_p[key]).max() <= 2e-3 * scale, (name, what, key)
+        check(got_n, "a", want, TOL["bfloat16"], f"{name} native {what}")
+    # decoded tokens only (no library product anywhere): bit for bit
+    steps = tail_decode("a", toks[:40], tail=40)
+    got_n, got_p = run(native, steps), run(parts, steps)
+    for key in got_n:
+        assert np.array_equal(got_n[key], got_p[key]), (name, "decode", key)
+    native.check()
+
+
+def test_native_runner_leaves_other_models_to_the_parts(tiny_models):
+    from infinicore_infer_b200.engine.runner import NativeRunner
+    eng = make_engine(tiny_models["C"][0], "bfloat16", 256)          # hidden 80: outside the small-row kernels
+    assert eng.runner is None and "small-row" in NativeRunner.why_not
+    eng = make_engine(tiny_models["A"][0], "float32", 256)
+    assert eng.runner is None and "bfloat16" in NativeRunner.why_not
