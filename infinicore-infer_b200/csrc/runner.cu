@@ -65,9 +65,15 @@ static bool g_bound = false;
 
 JK_EXPORT int jk_runner_bind(const RunnerFns *fns) {
     JK_REQUIRE(fns != nullptr, "runner_bind: no table");
-    const void *const *p = reinterpret_cast<const void *const *>(fns);
-    for (size_t i = 0; i < sizeof(RunnerFns) / sizeof(void *); ++i)
-        JK_REQUIRE(p[i] != nullptr, "runner_bind: entry %d of the table is empty", (int)i);
+    // the tcgen05 modules may be left out by a caller whose model or step size never reaches them (they are
+    // then not even compiled); everything else is needed by every model
+    JK_REQUIRE(fns->embed && fns->add_rmsnorm && fns->swiglu && fns->rope_kv && fns->linear_small && fns->linear_small_qkv &&
+               fns->attention_decode && fns->attention_prefill && fns->err_elementwise && fns->err_linear_small &&
+               fns->err_attention, "runner_bind: an entry that every model needs is empty");
+    JK_REQUIRE((fns->gemm_tcgen05 != nullptr) == (fns->gemm_tcgen05_qkv != nullptr) &&
+               (fns->gemm_tcgen05 != nullptr) == (fns->err_gemm_tcgen05 != nullptr) &&
+               (fns->attention_tcgen05 != nullptr) == (fns->err_attention_tcgen05 != nullptr),
+               "runner_bind: a module's entries come together");
     g_fns = *fns;
     g_bound = true;
     return JK_OK;
@@ -152,7 +158,7 @@ static int lt_product(const void *act, const void *w, float *out, int M, int N, 
 }
 
 static bool takes_tcgen05(const RunnerModel &m, int rows, int n, int k) {
-    if (rows <= 16 || k % 8) return false;
+    if (rows <= 16 || k % 8 || g_fns.gemm_tcgen05 == nullptr) return false;
     // fewer rows are taken only if the output is so wide that its tiles make several waves all the same
     if (rows < m.tcgen05_min_rows && (long long)((rows + 127) / 128) * ((n + 255) / 256) < 3LL * m.sms) return false;
     const long long tiles = (long long)((rows + 127) / 128) * ((n + 127) / 128);
@@ -218,7 +224,7 @@ JK_EXPORT int jk_runner_forward(const RunnerModel *mp, const RunnerLayer *layers
                                            nkvh, dh, 1, stream));
         }
         if (st.n_tiles > 0) {
-            if (m.attention_tcgen05)
+            if (m.attention_tcgen05 && g_fns.attention_tcgen05 != nullptr)
                 RUN(attention_tcgen05, g_fns.attention_tcgen05(s.q, L.k_pages, L.v_pages, s.o, st.tiles, st.n_tiles, T, st.req_start,
                                                                st.req_pos, st.block_table, m.max_blocks, m.num_pages, m.page_size,
                                                                nh, nkvh, dh, m.softmax_scale, m.window, m.status, stream));

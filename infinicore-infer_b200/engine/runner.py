@@ -137,27 +137,14 @@ class NativeRunner:
         dev = rt.device
         self.lib = _build.load("runner")
         self.lib.jk_runner_last_error.restype = ctypes.c_char_p
-        mods = {m: _build.load(m) for m in ("elementwise", "linear_small", "gemm_tcgen05", "attention", "attention_tcgen05")}
-        fns = _Fns(
-            embed=_addr(mods["elementwise"], "jk_embed"), add_rmsnorm=_addr(mods["elementwise"], "jk_add_rmsnorm"),
-            swiglu=_addr(mods["elementwise"], "jk_swiglu"), rope_kv=_addr(mods["elementwise"], "jk_rope_kv"),
-            linear_small=_addr(mods["linear_small"], "jk_linear_small"),
-            linear_small_qkv=_addr(mods["linear_small"], "jk_linear_small_qkv"),
-            gemm_tcgen05=_addr(mods["gemm_tcgen05"], "jk_gemm_tcgen05"),
-            gemm_tcgen05_qkv=_addr(mods["gemm_tcgen05"], "jk_gemm_tcgen05_qkv"),
-            attention_decode=_addr(mods["attention"], "jk_attention_decode"),
-            attention_prefill=_addr(mods["attention"], "jk_attention_prefill"),
-            attention_tcgen05=_addr(mods["attention_tcgen05"], "jk_attention_tcgen05"),
-            err_elementwise=_addr(mods["elementwise"], "jk_elementwise_last_error"),
-            err_linear_small=_addr(mods["linear_small"], "jk_linear_small_last_error"),
-            err_gemm_tcgen05=_addr(mods["gemm_tcgen05"], "jk_gemm_tcgen05_last_error"),
-            err_attention=_addr(mods["attention"], "jk_attention_last_error"),
-            err_attention_tcgen05=_addr(mods["attention_tcgen05"], "jk_attention_tcgen05_last_error"))
-        self._check(self.lib.jk_runner_bind(ctypes.byref(fns)))
-
         first = model.layers[0]
         a = first.mixer.spec
         d, di, dh = spec.hidden_size, first.feed_forward.spec.intermediate_size, a.head_dim
+        nq = (a.num_heads + 2 * a.num_kv_heads) * dh
+        self._products = [(nq, d), (d, a.num_heads * dh), (di, d), (d, di), (spec.vocab_size, d)]
+        self._attention_tcgen05 = kernels.attention_tcgen05_supports(dh, cache.page_size)
+        self._bound_tcgen05 = None
+        self._bind()
         self.dims = (d, di, a.num_heads, a.num_kv_heads, dh)
         pos = first.mixer.position
         k0 = cache.views[0].k_pages
@@ -166,7 +153,7 @@ class NativeRunner:
             vocab=spec.vocab_size, page_size=cache.page_size, max_blocks=cache.max_blocks, num_pages=k0.shape[0],
             window=a.window or 0, sms=kernels._sm_count(dev), tcgen05_min_rows=rt.tcgen05_min_rows,
             tcgen05_min_tiles=rt.tcgen05_min_tiles,
-            attention_tcgen05=1 if kernels.attention_tcgen05_supports(dh, cache.page_size) else 0,
+            attention_tcgen05=1 if self._attention_tcgen05 else 0,
             embed_dtype=kernels.dtype_code(model.embedding.dtype), embed_scale=spec.embed_scale,
             residual_scale=first.spec.residual_scale, logit_scale=spec.logit_scale, softmax_scale=a.softmax_scale,
             final_eps=model.final_norm.spec.eps, embedding=model.embedding.data_ptr(), lm_head=model.lm_head.data_ptr(),
@@ -184,7 +171,6 @@ class NativeRunner:
         T = engine.max_step_tokens
         f32 = lambda *shape: torch.empty(shape, dtype=torch.float32, device=dev)
         b16 = lambda *shape: torch.empty(shape, dtype=torch.bfloat16, device=dev)
-        nq = (a.num_heads + 2 * a.num_kv_heads) * dh
         self._buffers = dict(x=f32(T, d), h=b16(T, d), qkv=f32(T, nq), q=b16(T, a.num_heads * dh), o=b16(T, a.num_heads * dh),
                              delta=f32(T, d), gate_up=f32(T, 2 * di), act=b16(T, di), hw=b16(T, d),
                              workspace=torch.empty(32 << 20, dtype=torch.uint8, device=dev))
@@ -192,9 +178,36 @@ class NativeRunner:
         self._scratch = _Scratch(workspace_bytes=32 << 20, decode_scratch=self._decode_scratch.data_ptr(),
                                  **{k: v.data_ptr() for k, v in self._buffers.items()})
         self._max_positions = a.position.max_positions if a.position else 1 << 20
-        self._attn_lib = mods["attention"]
+        self._attn_lib = _build.load("attention")
         self._attn_lib.jk_attention_decode_scratch_floats.restype = ctypes.c_longlong
         self.launches = 0
+
+    def _bind(self) -> None:
+        """Hand the kernel modules' entry points to the native side.  The tcgen05 product is bound (and so
+        compiled) only if a step of this engine can reach it under the runtime's routing, the tcgen05
+        attention only for the head and page sizes it is built for."""
+        rt = self.runtime
+        need_tc = any(rt.takes_tcgen05(self.max_step_tokens, n, k) for n, k in self._products)
+        if self._bound_tcgen05 is not None and (self._bound_tcgen05 or not need_tc):
+            return
+        names = ["elementwise", "linear_small", "attention"] + (["gemm_tcgen05"] if need_tc else []) \
+            + (["attention_tcgen05"] if self._attention_tcgen05 else [])
+        mods = {m: _build.load(m) for m in names}
+        get = lambda module, name: _addr(mods[module], name) if module in mods else None
+        fns = _Fns(
+            embed=get("elementwise", "jk_embed"), add_rmsnorm=get("elementwise", "jk_add_rmsnorm"),
+            swiglu=get("elementwise", "jk_swiglu"), rope_kv=get("elementwise", "jk_rope_kv"),
+            linear_small=get("linear_small", "jk_linear_small"), linear_small_qkv=get("linear_small", "jk_linear_small_qkv"),
+            gemm_tcgen05=get("gemm_tcgen05", "jk_gemm_tcgen05"), gemm_tcgen05_qkv=get("gemm_tcgen05", "jk_gemm_tcgen05_qkv"),
+            attention_decode=get("attention", "jk_attention_decode"), attention_prefill=get("attention", "jk_attention_prefill"),
+            attention_tcgen05=get("attention_tcgen05", "jk_attention_tcgen05"),
+            err_elementwise=get("elementwise", "jk_elementwise_last_error"),
+            err_linear_small=get("linear_small", "jk_linear_small_last_error"),
+            err_gemm_tcgen05=get("gemm_tcgen05", "jk_gemm_tcgen05_last_error"),
+            err_attention=get("attention", "jk_attention_last_error"),
+            err_attention_tcgen05=get("attention_tcgen05", "jk_attention_tcgen05_last_error"))
+        self._check(self.lib.jk_runner_bind(ctypes.byref(fns)))
+        self._bound_tcgen05 = need_tc
 
     def _check(self, rc: int) -> None:
         if rc:
@@ -206,6 +219,7 @@ class NativeRunner:
         if (rt.tcgen05_min_rows, rt.tcgen05_min_tiles) != self._routing:       # a test moved the thresholds
             self._routing = (rt.tcgen05_min_rows, rt.tcgen05_min_tiles)
             self._model.tcgen05_min_rows, self._model.tcgen05_min_tiles = rt.tcgen05_min_rows, rt.tcgen05_min_tiles
+            self._bind()
         d, di, nh, nkvh, dh = self.dims
         T = ctx.ntok
         if T > self.max_step_tokens:
