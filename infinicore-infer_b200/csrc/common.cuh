@@ -22,11 +22,13 @@ enum JkStatus : int {
     JK_CUDA_ERROR = 3,
 };
 
-char *jk_error_buffer();   // one per shared object, defined by JK_DEFINE_ERROR_BUFFER
+// One per shared object, defined by JK_DEFINE_ERROR_BUFFER; hidden, so that a module loaded into a program
+// that already has another module's symbols keeps writing to its own.
+__attribute__((visibility("hidden"))) char *jk_error_buffer();
 
 #define JK_DEFINE_ERROR_BUFFER(prefix)                                              \
     static thread_local char g_error[512] = "";                                    \
-    char *jk_error_buffer() { return g_error; }                                    \
+    __attribute__((visibility("hidden"))) char *jk_error_buffer() { return g_error; }                                  \
     JK_EXPORT const char *prefix##_last_error() { return g_error; }
 
 #define JK_FAIL(code, ...)                                                          \

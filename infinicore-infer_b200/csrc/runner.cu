@@ -16,52 +16,16 @@
 // (The reference's counterpart is the per-device worker that runs inferDeviceBatch,
 // src/models/jiuge/jiuge.cpp:126-305.)
 #include "common.cuh"
+#include "runner.h"
 
 #include <cublas_v2.h>
 #include <mutex>
 
 JK_DEFINE_ERROR_BUFFER(jk_runner)
 
-// ---- entry points of the kernel modules (signatures as in their sources) -------------------------------
-extern "C" {
-typedef int (*EmbedFn)(const int *, int, const void *, int, int, float, float *, cudaStream_t);
-typedef int (*AddRmsnormFn)(float *, const void *, int, float, const float *, float, float, void *, int, const int *, int,
-                            int, cudaStream_t);
-typedef int (*SwigluFn)(const void *, int, void *, int, int, int, cudaStream_t);
-typedef int (*RopeKvFn)(const void *, int, int, const float *, const int *, const int *, const int *, int, int,
-                        const float *, const float *, int, void *, void *, void *, int, int, int, int, int, int,
-                        cudaStream_t);
-typedef int (*LinearSmallFn)(const void *, const void *, void *, int, int, int, int, int, int, cudaStream_t);
-typedef int (*LinearSmallQkvFn)(const void *, const void *, int, int, void *, void *, void *, const float *, const float *,
-                                const int *, const int *, const int *, int, int, int, int, int, int, cudaStream_t);
-typedef int (*GemmTcgen05Fn)(const void *, const void *, void *, int, int, int, int, int, float, int *, int, cudaStream_t);
-typedef int (*GemmTcgen05QkvFn)(const void *, const void *, int, int, void *, void *, void *, const float *, const float *,
-                                const int *, const int *, const int *, int, int, int, int, int, int *, int, cudaStream_t);
-typedef int (*AttentionDecodeFn)(const void *, const void *, const void *, void *, float *, const int *, int, const int *,
-                                 const int *, const int *, int, int, int, int, int, float, int, int, cudaStream_t);
-typedef int (*AttentionPrefillFn)(const void *, const void *, const void *, void *, const int *, int, int, const int *,
-                                  const int *, const int *, int, int, int, int, int, float, int, cudaStream_t);
-typedef int (*AttentionTcgen05Fn)(const void *, const void *, const void *, void *, const int *, int, int, const int *,
-                                  const int *, const int *, int, int, int, int, int, int, float, int, int *, cudaStream_t);
-typedef const char *(*LastErrorFn)();
-}
-
-struct RunnerFns {
-    EmbedFn embed;
-    AddRmsnormFn add_rmsnorm;
-    SwigluFn swiglu;
-    RopeKvFn rope_kv;
-    LinearSmallFn linear_small;
-    LinearSmallQkvFn linear_small_qkv;
-    GemmTcgen05Fn gemm_tcgen05;
-    GemmTcgen05QkvFn gemm_tcgen05_qkv;
-    AttentionDecodeFn attention_decode;
-    AttentionPrefillFn attention_prefill;
-    AttentionTcgen05Fn attention_tcgen05;
-    LastErrorFn err_elementwise, err_linear_small, err_gemm_tcgen05, err_attention, err_attention_tcgen05;
-};
 static RunnerFns g_fns = {};
 static bool g_bound = false;
+JK_EXPORT const RunnerFns *jk_runner_fns() { return g_bound ? &g_fns : nullptr; }
 
 JK_EXPORT int jk_runner_bind(const RunnerFns *fns) {
     JK_REQUIRE(fns != nullptr, "runner_bind: no table");
@@ -74,55 +38,16 @@ JK_EXPORT int jk_runner_bind(const RunnerFns *fns) {
                (fns->gemm_tcgen05 != nullptr) == (fns->err_gemm_tcgen05 != nullptr) &&
                (fns->attention_tcgen05 != nullptr) == (fns->err_attention_tcgen05 != nullptr),
                "runner_bind: a module's entries come together");
-    g_fns = *fns;
+    // a table adds to what is bound already (two users of this library in one process may need different
+    // modules): an entry that this caller leaves empty keeps what an earlier caller gave
+    static_assert(sizeof(RunnerFns) % sizeof(void *) == 0, "the table is a list of pointers");
+    void *const *from = (void *const *)fns;
+    void **to = (void **)&g_fns;
+    for (size_t i = 0; i < sizeof(RunnerFns) / sizeof(void *); ++i)
+        if (from[i] != nullptr) to[i] = from[i];
     g_bound = true;
     return JK_OK;
 }
-
-// What never changes from step to step.
-struct RunnerModel {
-    int layers, hidden, heads, kv_heads, head_dim, intermediate, vocab;
-    int page_size, max_blocks, num_pages, window;
-    int sms, tcgen05_min_rows, tcgen05_min_tiles;
-    int attention_tcgen05;          // 1: tiles go to the tcgen05 attention kernel, 0: to the mma.sync kernel
-    int embed_dtype;                // JK_F32 or JK_BF16
-    float embed_scale, residual_scale, logit_scale, softmax_scale, final_eps;
-    const void *embedding;          // [vocab, hidden]
-    const void *lm_head;            // [vocab, hidden] bfloat16
-    const float *final_norm;        // [hidden]
-    const float *cos_table;         // [positions, head_dim / 2] or null
-    const float *sin_table;
-    int *status;                    // the word in which the tcgen05 kernels record a wait that ran out
-};
-
-struct RunnerLayer {
-    const void *w_qkv, *w_o, *w_gate_up, *w_down;      // bfloat16 [N, K]
-    const float *norm1, *norm2;
-    float eps1, eps2;
-    void *k_pages, *v_pages;                           // bfloat16 [pages, kv_heads, page_size, head_dim]
-};
-
-// One step's batch (device arrays of the step's metadata buffer) and where its logits go.
-struct RunnerStep {
-    int ntok, nreq, n_want, n_tiles, n_short, splits;
-    const int *tokens, *positions, *row_req, *req_start, *req_pos, *want_rows, *short_rows, *tiles, *block_table;
-    float *logits;                  // [n_want, vocab]
-};
-
-// Buffers for `max_tokens` rows, made once by the caller.
-struct RunnerScratch {
-    float *x;                       // [T, hidden] the residual stream
-    void *h;                        // bf16 [T, hidden]
-    float *qkv;                     // [T, (heads + 2 kv_heads) * head_dim]
-    void *q, *o;                    // bf16 [T, heads * head_dim]
-    float *delta;                   // [T, hidden]
-    float *gate_up;                 // [T, 2 * intermediate]
-    void *act;                      // bf16 [T, intermediate]
-    void *hw;                       // bf16 [max wanted rows, hidden]
-    float *decode_scratch;          // partial results of the split-key attention
-    void *workspace;                // for the library
-    long long workspace_bytes;
-};
 
 static int g_launches = 0;      // kernels launched by the last jk_runner_forward (the library's count as one each)
 JK_EXPORT int jk_runner_launches() { return g_launches; }

@@ -27,7 +27,8 @@ class _Fns(ctypes.Structure):
     _fields_ = [(n, ctypes.c_void_p) for n in (
         "embed", "add_rmsnorm", "swiglu", "rope_kv", "linear_small", "linear_small_qkv", "gemm_tcgen05",
         "gemm_tcgen05_qkv", "attention_decode", "attention_prefill", "attention_tcgen05",
-        "err_elementwise", "err_linear_small", "err_gemm_tcgen05", "err_attention", "err_attention_tcgen05")]
+        "err_elementwise", "err_linear_small", "err_gemm_tcgen05", "err_attention", "err_attention_tcgen05",
+        "argmax", "sample", "err_sampling")]
 
 
 class _Model(ctypes.Structure):
@@ -190,7 +191,7 @@ class NativeRunner:
         need_tc = any(rt.takes_tcgen05(self.max_step_tokens, n, k) for n, k in self._products)
         if self._bound_tcgen05 is not None and (self._bound_tcgen05 or not need_tc):
             return
-        names = ["elementwise", "linear_small", "attention"] + (["gemm_tcgen05"] if need_tc else []) \
+        names = ["elementwise", "linear_small", "attention", "sampling"] + (["gemm_tcgen05"] if need_tc else []) \
             + (["attention_tcgen05"] if self._attention_tcgen05 else [])
         mods = {m: _build.load(m) for m in names}
         get = lambda module, name: _addr(mods[module], name) if module in mods else None
@@ -205,7 +206,10 @@ class NativeRunner:
             err_linear_small=get("linear_small", "jk_linear_small_last_error"),
             err_gemm_tcgen05=get("gemm_tcgen05", "jk_gemm_tcgen05_last_error"),
             err_attention=get("attention", "jk_attention_last_error"),
-            err_attention_tcgen05=get("attention_tcgen05", "jk_attention_tcgen05_last_error"))
+            err_attention_tcgen05=get("attention_tcgen05", "jk_attention_tcgen05_last_error"),
+            # the C interface of the same library (csrc/model_api.h) samples through these
+            argmax=get("sampling", "jk_argmax"), sample=get("sampling", "jk_sample"),
+            err_sampling=get("sampling", "jk_sampling_last_error"))
         self._check(self.lib.jk_runner_bind(ctypes.byref(fns)))
         self._bound_tcgen05 = need_tc
 
