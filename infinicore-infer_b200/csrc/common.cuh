@@ -81,22 +81,38 @@ static inline void jk_prefer_shared(const void *kernel) {
 }
 #endif
 
+// `cluster` > 1 launches thread-block clusters of that many blocks along x (the grid is a multiple of it).
 template <typename... KArgs, typename... Args>
-static inline cudaError_t jk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                    Args &&...args) {
+static inline cudaError_t jk_launch_clusters(void (*kernel)(KArgs...), int cluster, dim3 grid, dim3 block, size_t smem,
+                                             cudaStream_t stream, Args &&...args) {
 #ifndef __CUDA_ARCH__
     jk_prefer_shared(reinterpret_cast<const void *>(kernel));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)cluster; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (jk_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = jk_pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
 #else
     return cudaSuccess;
 #endif
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t jk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args &&...args) {
+    return jk_launch_clusters(kernel, 1, grid, block, smem, stream, std::forward<Args>(args)...);
 }
 
 // ---- element access: storage type T (float or __nv_bfloat16), arithmetic in float ----

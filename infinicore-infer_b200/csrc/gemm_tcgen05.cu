@@ -99,6 +99,48 @@ __device__ __forceinline__ void tmem_alloc(unsigned *slot, unsigned columns) {  
 __device__ __forceinline__ void tmem_dealloc(unsigned addr, unsigned columns) {     // the same warp
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(addr), "r"(columns) : "memory");
 }
+// ---- the same for a pair of blocks (a cluster of two) that share one product: cta_group::2 ----
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// The address, in the cluster's shared window, of what `p` is in block `rank` of the cluster.
+__device__ __forceinline__ unsigned cluster_addr(const void *p, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {      // every thread of both blocks
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// A block's own load into its own shared memory whose bytes are counted by a barrier of the pair's first block.
+__device__ __forceinline__ void tma_load_2d_pair(void *smem, const CUtensorMap *map, unsigned bar_addr, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(smem_u32(smem)), "l"(map), "r"(bar_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned bar_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(bar_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(unsigned *slot, unsigned columns) {      // the same warp of both blocks
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(slot)), "r"(columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(unsigned addr, unsigned columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(addr), "r"(columns) : "memory");
+}
+// M = 256 over the pair: each block gives its 128 rows of A and its half of B's rows and receives its 128 rows of D.
+__device__ __forceinline__ void umma_bf16_pair(unsigned tmem_c, unsigned long long adesc, unsigned long long bdesc,
+                                               unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}\n"
+                 ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// Arrives, once the MMAs issued so far are complete, on the barrier at this offset in both blocks of the pair.
+__device__ __forceinline__ void umma_commit_pair(unsigned long long *bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+                 ::"r"(smem_u32(bar)), "h"((unsigned short)3) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void umma_bf16(unsigned tmem_c, unsigned long long adesc, unsigned long long bdesc,
@@ -146,15 +188,18 @@ __device__ __forceinline__ unsigned long long smem_desc_sw128(const void *tile) 
     return ((addr & 0x3FFFFull) >> 4) | (1ull << 16) | ((1024ull >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 // Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = bn.
-__host__ __device__ constexpr unsigned instr_desc_bf16(int bn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(TG_BM >> 4) << 24);
+__host__ __device__ constexpr unsigned instr_desc_bf16(int bn, int bm = TG_BM) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(bm >> 4) << 24);
 }
 
-template <int BN> struct TgSmem {
-    __nv_bfloat16 a[TG_STAGES][TG_BM * TG_BK];       // 16 KB each, 1024-byte aligned
-    __nv_bfloat16 b[TG_STAGES][BN * TG_BK];
+// CTAS = 2: a pair of blocks works on a tile of 256 x BN; each holds its 128 rows of A and BN / 2 rows of B,
+// which leaves room for a deeper ring.
+template <int BN, int CTAS> struct TgSmem {
+    static constexpr int STAGES = CTAS == 2 ? 6 : TG_STAGES;
+    __nv_bfloat16 a[STAGES][TG_BM * TG_BK];          // 16 KB each, 1024-byte aligned
+    __nv_bfloat16 b[STAGES][BN / CTAS * TG_BK];
     unsigned char stage_out[4][4096];                // per epilogue warp: 32 rows x 128 bytes, swizzled
-    unsigned long long full[TG_STAGES], empty[TG_STAGES], acc_full[2], acc_empty[2];
+    unsigned long long full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
     unsigned tmem_base;
 };
 
@@ -164,28 +209,39 @@ __device__ __forceinline__ void stage_write(unsigned char *tile, int row, int ch
     *reinterpret_cast<uint4 *>(tile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, int CTAS>
 __global__ void __launch_bounds__(TG_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, TgArgs a) {
     extern __shared__ unsigned char tg_raw[];
-    TgSmem<BN> &s = *reinterpret_cast<TgSmem<BN> *>((reinterpret_cast<uintptr_t>(tg_raw) + 1023) & ~uintptr_t(1023));
+    using Smem = TgSmem<BN, CTAS>;
+    Smem &s = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(tg_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int STAGES = Smem::STAGES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // EPI_SWIGLU: a tile's B rows are BN/2 gate rows and the BN/2 up rows that belong to them
     constexpr int OUT_COLS = EPI == EPI_SWIGLU ? BN / 2 : BN;
-    constexpr unsigned STAGE_BYTES = (TG_BM + BN) * TG_BK * sizeof(__nv_bfloat16);
+    // bytes that land per stage, over the pair when there is one (the first block's barrier counts both)
+    constexpr unsigned STAGE_BYTES = CTAS * (TG_BM + BN / CTAS) * TG_BK * sizeof(__nv_bfloat16);
+    // a worker is a block, or a pair of blocks (a cluster of two: blocks 2c and 2c + 1) on a tile of 256 rows
+    const int rank = CTAS == 2 ? (int)cluster_rank() : 0;
+    const int worker = blockIdx.x / CTAS, workers = gridDim.x / CTAS;
+    constexpr int TILE_M = TG_BM * CTAS;
     const int tiles_n = (a.N + OUT_COLS - 1) / OUT_COLS;
-    const int num_tiles = tiles_n * ((a.M + TG_BM - 1) / TG_BM);
+    const int num_tiles = tiles_n * ((a.M + TILE_M - 1) / TILE_M);
     const int nk = (a.K + TG_BK - 1) / TG_BK;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < TG_STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&s.acc_full[i], 1); mbar_init(&s.acc_empty[i], 4); }
+        for (int i = 0; i < STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&s.acc_full[i], 1); mbar_init(&s.acc_empty[i], 4 * CTAS); }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(&s.tmem_base, 2 * BN);
+    if (warp == 1) {
+        if (CTAS == 2) tmem_alloc_pair(&s.tmem_base, 2 * BN);
+        else tmem_alloc(&s.tmem_base, 2 * BN);
+    }
     tc_fence_before();
     __syncthreads();
+    if (CTAS == 2) cluster_sync();      // the other block's barriers exist before anything arrives on them
     tc_fence_after();
     const unsigned tmem = s.tmem_base;
     int failed = 0;
@@ -199,11 +255,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ---- TMA producer ----
         if (lane == 0) {
             int it = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
-                const int m0 = (tile / tiles_n) * TG_BM, n0 = (tile % tiles_n) * OUT_COLS;
+            for (int tile = worker; tile < num_tiles && !failed; tile += workers) {
+                const int m0 = (tile / tiles_n) * TILE_M + rank * TG_BM, n0 = (tile % tiles_n) * OUT_COLS;
                 for (int i = 0; i < nk; ++i, ++it) {
-                    const int st = it % TG_STAGES;
-                    if (it >= TG_STAGES && !mbar_wait(&s.empty[st], ((it / TG_STAGES) - 1) & 1)) { failed = 1; break; }
+                    const int st = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(&s.empty[st], ((it / STAGES) - 1) & 1)) { failed = 1; break; }
+                    if (CTAS == 2) {
+                        // each block loads its own rows of A and its half of the tile's rows of B (gate rows in the
+                        // first block, up rows in the second for SwiGLU); the first block's barrier counts all bytes
+                        if (rank == 0) mbar_expect_tx(&s.full[st], STAGE_BYTES);
+                        const unsigned bar = cluster_addr(&s.full[st], 0);
+                        const int w0 = EPI == EPI_SWIGLU ? (rank ? a.N + n0 : n0) : n0 + rank * (BN / 2);
+                        tma_load_2d_pair(s.a[st], &map_a, bar, i * TG_BK, m0);
+                        tma_load_2d_pair(s.b[st], &map_w, bar, i * TG_BK, w0);
+                        continue;
+                    }
                     mbar_expect_tx(&s.full[st], STAGE_BYTES);
                     tma_load_2d(s.a[st], &map_a, &s.full[st], i * TG_BK, m0);
                     tma_load_2d(s.b[st], &map_w, &s.full[st], i * TG_BK, n0);
@@ -215,25 +281,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     } else if (warp == 1) {
         // ---- MMA issuer ----
-        if (lane == 0) {
-            constexpr unsigned idesc = instr_desc_bf16(BN);
+        if (lane == 0 && rank == 0) {      // of a pair, the first block issues for both
+            constexpr unsigned idesc = instr_desc_bf16(BN, TILE_M);
             int it = 0, j = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x, ++j) {
+            for (int tile = worker; tile < num_tiles && !failed; tile += workers, ++j) {
                 const int buf = j & 1;
                 if (j >= 2 && !mbar_wait(&s.acc_empty[buf], ((j >> 1) - 1) & 1)) { failed = 2; break; }
                 tc_fence_after();
                 const unsigned acc = tmem + buf * BN;
                 for (int i = 0; i < nk; ++i, ++it) {
-                    const int st = it % TG_STAGES;
-                    if (!mbar_wait(&s.full[st], (it / TG_STAGES) & 1)) { failed = 2; break; }
+                    const int st = it % STAGES;
+                    if (!mbar_wait(&s.full[st], (it / STAGES) & 1)) { failed = 2; break; }
                     tc_fence_after();
                     const unsigned long long ad = smem_desc_sw128(s.a[st]), bd = smem_desc_sw128(s.b[st]);
 #pragma unroll
-                    for (int k = 0; k < TG_BK / 16; ++k)      // 32 bytes further along K per instruction
-                        umma_bf16(acc, ad + 2 * k, bd + 2 * k, idesc, (i | k) ? 1u : 0u);
-                    umma_commit(&s.empty[st]);                 // the stage is free once these MMAs have read it
+                    for (int k = 0; k < TG_BK / 16; ++k) {    // 32 bytes further along K per instruction
+                        if (CTAS == 2) umma_bf16_pair(acc, ad + 2 * k, bd + 2 * k, idesc, (i | k) ? 1u : 0u);
+                        else umma_bf16(acc, ad + 2 * k, bd + 2 * k, idesc, (i | k) ? 1u : 0u);
+                    }
+                    // the stage is free (in both blocks) once these MMAs have read it
+                    if (CTAS == 2) umma_commit_pair(&s.empty[st]);
+                    else umma_commit(&s.empty[st]);
                 }
-                if (!failed) umma_commit(&s.acc_full[buf]);
+                if (!failed) {
+                    if (CTAS == 2) umma_commit_pair(&s.acc_full[buf]);
+                    else umma_commit(&s.acc_full[buf]);
+                }
             }
             if (failed) atomicExch(a.status, 2);
         }
@@ -242,8 +315,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quarter = warp & 3;
         unsigned char *stage = s.stage_out[quarter];
         int j = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
-            const int m0 = (tile / tiles_n) * TG_BM, n0 = (tile % tiles_n) * OUT_COLS;
+        // handing an accumulator back: the issuing block's barrier counts the epilogue warps of the whole pair
+        auto release_accumulator = [&](int buf) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (CTAS == 2) mbar_arrive_cluster(cluster_addr(&s.acc_empty[buf], 0));
+                else mbar_arrive(&s.acc_empty[buf]);
+            }
+        };
+        for (int tile = worker; tile < num_tiles; tile += workers, ++j) {
+            const int m0 = (tile / tiles_n) * TILE_M + rank * TG_BM, n0 = (tile % tiles_n) * OUT_COLS;
             const int buf = j & 1;
             if (!mbar_wait(&s.acc_full[buf], (j >> 1) & 1)) { failed = 3; if (lane == 0) atomicExch(a.status, 3); break; }
             tc_fence_after();
@@ -314,9 +396,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
+                release_accumulator(buf);
                 continue;
             }
             // columns per pass: a staging row is 128 bytes = 32 floats or 64 bfloat16
@@ -385,21 +465,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             }
             // this warp has read all it needs of the accumulator: hand the buffer back to the MMA warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
+            release_accumulator(buf);
         }
         if (lane == 0) bulk_wait_all();
     }
     // A role that gave up leaves copies or MMAs in flight: give them a bounded time to land before
     // the block's shared and tensor memory are released.
     if (failed && lane == 0) {
-        for (int st = 0; st < TG_STAGES; ++st) mbar_wait(&s.full[st], 0);
+        for (int st = 0; st < STAGES; ++st) mbar_wait(&s.full[st], 0);
     }
     tc_fence_before();
     __syncthreads();
+    // of a pair, neither block leaves (or frees tensor memory) while the other may still read its shared
+    // memory, write its accumulators or arrive on its barriers
+    if (CTAS == 2) cluster_sync();
     tc_fence_after();
-    if (warp == 1) tmem_dealloc(tmem, 2 * BN);
+    if (warp == 1) {
+        if (CTAS == 2) tmem_dealloc_pair(tmem, 2 * BN);
+        else tmem_dealloc(tmem, 2 * BN);
+    }
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -452,14 +536,69 @@ static int tensor_map_2d(const void *ptr, int rows, int cols, int ld, int box_ro
 template <int BN, int EPI>
 static int launch_tg(const CUtensorMap &ma, const CUtensorMap &mw, const CUtensorMap &mo, const TgArgs &a, int sms,
                      cudaStream_t stream) {
-    const size_t smem = sizeof(TgSmem<BN>) + 1024;
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = sizeof(TgSmem<BN, 1>) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: %s", cudaGetErrorString(e));
     const int out_cols = EPI == EPI_SWIGLU ? BN / 2 : BN;
     const int tiles = ((a.N + out_cols - 1) / out_cols) * ((a.M + TG_BM - 1) / TG_BM);
-    jk_launch(gemm_tcgen05_kernel<BN, EPI>, dim3(tiles < sms ? tiles : sms), dim3(TG_THREADS), smem, stream, ma, mw, mo, a);
+    jk_launch(gemm_tcgen05_kernel<BN, EPI, 1>, dim3(tiles < sms ? tiles : sms), dim3(TG_THREADS), smem, stream, ma, mw, mo, a);
     JK_CHECK_LAUNCH("gemm_tcgen05");
     return JK_OK;
+}
+
+// The same product by pairs of blocks (clusters of two) on tiles of 256 x 256: `mw` has boxes of 128 rows.
+template <int EPI>
+static int launch_tg_pair(const CUtensorMap &ma, const CUtensorMap &mw, const CUtensorMap &mo, const TgArgs &a, int sms,
+                          cudaStream_t stream) {
+    auto kernel = gemm_tcgen05_kernel<256, EPI, 2>;
+    const size_t smem = sizeof(TgSmem<256, 2>) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: %s", cudaGetErrorString(e));
+    const int out_cols = EPI == EPI_SWIGLU ? 128 : 256;
+    const int tiles = ((a.N + out_cols - 1) / out_cols) * ((a.M + 2 * TG_BM - 1) / (2 * TG_BM));
+    // as many pairs as the device holds at once (each block takes an SM's whole shared memory)
+    static int resident = 0;
+    if (resident == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (sms / 2)); cfg.blockDim = dim3(TG_THREADS); cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n < 1) {
+            cudaGetLastError();
+            n = sms / 2;
+        }
+        resident = n < sms / 2 ? n : sms / 2;
+    }
+    const int pairs = tiles < resident ? tiles : resident;
+    e = jk_launch_clusters(kernel, 2, dim3(2 * pairs), dim3(TG_THREADS), smem, stream, ma, mw, mo, a);
+    if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05 (pairs): %s", cudaGetErrorString(e));
+    return JK_OK;
+}
+
+// Pairs of blocks take a product whose tiles of 256 x 256 make more than one wave over the SM pairs (each SM then
+// reads half of B's bytes per flop from its shared memory, which is what bounds single blocks); a product of
+// one wave is no faster that way, and single blocks spread it over more SMs.  JK_GEMM_PAIR=0 keeps every
+// product on single blocks, JK_GEMM_PAIR=2 sends every product of more than 128 rows to pairs
+// (jk_gemm_tcgen05_set_pairs does the same at run time, for tests).
+static int g_pair_mode = -1;      // -1: not read yet
+JK_EXPORT int jk_gemm_tcgen05_set_pairs(int mode) {      // 0, 1 (the rule above) or 2; returns the mode before
+    const int before = g_pair_mode;
+    g_pair_mode = mode < 0 ? 0 : mode > 2 ? 2 : mode;
+    return before;
+}
+static bool takes_pairs(int M, int N, int out_cols, int sms) {
+    if (g_pair_mode < 0) {
+        const char *v = getenv("JK_GEMM_PAIR");
+        g_pair_mode = v && v[0] >= '0' && v[0] <= '2' ? v[0] - '0' : 1;
+    }
+    const int mode = g_pair_mode;
+    if (mode == 0 || M <= TG_BM) return false;
+    if (mode == 2) return true;
+    const long long tiles = (long long)((N + out_cols - 1) / out_cols) * ((M + 2 * TG_BM - 1) / (2 * TG_BM));
+    return tiles > sms / 2;
 }
 
 // The fused [q | k | v] projection with rotation and cache write in its epilogue.  Head sizes 64 and 128
@@ -482,10 +621,12 @@ JK_EXPORT int jk_gemm_tcgen05_qkv(const void *act, const void *w, int M, int K, 
     if (sms <= 0) sms = 148;
     CUtensorMap ma, mw;
     if (int rc = tensor_map_2d(act, M, K, K, TG_BM, TG_BK, 2, &ma)) return rc;
-    if (int rc = tensor_map_2d(w, N, K, K, 256, TG_BK, 2, &mw)) return rc;
+    const bool pair = takes_pairs(M, N, 256, sms);
+    if (int rc = tensor_map_2d(w, N, K, K, pair ? 128 : 256, TG_BK, 2, &mw)) return rc;
     TgArgs a{nullptr, M, N, K, N, 1.f, status, 0,
              QkvDest{(__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_pages, (__nv_bfloat16 *)v_pages, cos_table, sin_table,
                      positions, row_req, block_table, nh, nkvh, dh, page_size, max_blocks}};
+    if (pair) return launch_tg_pair<EPI_QKV>(ma, mw, ma, a, sms, stream);
     return launch_tg<256, EPI_QKV>(ma, mw, ma, a, sms, stream);
 }
 
@@ -509,13 +650,23 @@ JK_EXPORT int jk_gemm_tcgen05(const void *act, const void *w, void *out, int M, 
     a.direct = ((size_t)ldo * out_bytes) % 16 != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0;
     if (a.direct) mo = ma;
     else if (int rc = tensor_map_2d(out, M, N, ldo, 32, 128 / out_bytes, out_bytes, &mo)) return rc;
+    const bool pair = takes_pairs(M, N, epilogue == EPI_SWIGLU ? 128 : 256, sms);
     if (epilogue == EPI_SWIGLU) {
         if (int rc = tensor_map_2d(w, w_rows, K, K, 128, TG_BK, 2, &mw)) return rc;
+        if (pair) return launch_tg_pair<EPI_SWIGLU>(ma, mw, mo, a, sms, stream);
         return launch_tg<256, EPI_SWIGLU>(ma, mw, mo, a, sms, stream);
     }
     // a narrower tile when wide tiles would leave most SMs without one
     const int tiles_m = (M + TG_BM - 1) / TG_BM;
     const bool narrow = N <= 128 || tiles_m * ((N + 255) / 256) < sms * 3 / 4;
+    if (pair && !narrow) {
+        if (int rc = tensor_map_2d(w, w_rows, K, K, 128, TG_BK, 2, &mw)) return rc;
+        switch (epilogue) {
+            case EPI_F32: return launch_tg_pair<EPI_F32>(ma, mw, mo, a, sms, stream);
+            case EPI_BF16: return launch_tg_pair<EPI_BF16>(ma, mw, mo, a, sms, stream);
+            default: return launch_tg_pair<EPI_RESIDUAL>(ma, mw, mo, a, sms, stream);
+        }
+    }
     if (int rc = tensor_map_2d(w, w_rows, K, K, narrow ? 128 : 256, TG_BK, 2, &mw)) return rc;
 #define TG_DISPATCH(BN_)                                                                 \
     switch (epilogue) {                                                                  \

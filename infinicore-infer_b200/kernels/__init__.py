@@ -290,6 +290,13 @@ def gemm_tcgen05_supports(m: int, n: int, k: int) -> bool:
     return m >= 1 and n >= 1 and k >= 8 and k % 8 == 0
 
 
+def gemm_tcgen05_pairs(mode: int) -> int:
+    """Which products run on pairs of blocks (clusters of two sharing one 256 x 256 tile, ``cta_group::2``):
+    0 none, 1 those whose tiles make more than one wave (the default), 2 all of more than 128 rows.  Returns
+    the mode before (-1: the environment's or the default had not been read yet)."""
+    return _build.load("gemm_tcgen05").jk_gemm_tcgen05_set_pairs(ctypes.c_int(mode))
+
+
 def gemm_tcgen05(act: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = TG_F32,
                  scale: float = 1.0) -> torch.Tensor:
     """out (op)= act @ w^T on the tcgen05 tensor cores, operands by TMA.  Epilogues: TG_F32 / TG_BF16 store,

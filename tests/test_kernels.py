@@ -114,7 +114,7 @@ def _scatter_pages(k, v, tables, page, num_pages, dtype):
 
 @pytest.mark.parametrize("nh,nkvh,dh,page,with_rope", [(4, 2, 64, 16, True), (3, 1, 128, 8, True), (5, 5, 64, 32, False),
                                                         (9, 3, 64, 16, True)])
-def test_qkv_product_rotates_and_writes_the_cache_in_its_epilogue(K, nh, nkvh, dh, page, with_rope):
+def test_qkv_product_rotates_and_writes_the_cache_in_its_epilogue(K, pairs, nh, nkvh, dh, page, with_rope):
     """The tcgen05 product of the fused [q | k | v] matrix, rotation and cache write included, against
     a plain product, a plain rotation and a plain scatter."""
     assert K.gemm_tcgen05_qkv_supports(dh) and not K.gemm_tcgen05_qkv_supports(48)
@@ -481,12 +481,21 @@ def test_linear_small_refuses_what_it_cannot_take(K):
                        torch.zeros(4, 8, device=DEV))
 
 
+@pytest.fixture(params=["rule", "pairs"])
+def pairs(K, request):
+    """The tcgen05 products under their own rule for pairs of blocks, and with every product of more than
+    128 rows forced onto pairs (the rule sends only products of more than one wave there)."""
+    before = K.gemm_tcgen05_pairs(2 if request.param == "pairs" else 1)
+    yield request.param
+    K.gemm_tcgen05_pairs(1 if before < 0 else before)
+
+
 TG_SHAPES = [(128, 256, 64), (128, 128, 128), (1, 8, 8), (300, 520, 200), (257, 100, 2304), (512, 6912, 2304), (2048, 2304, 5760)]
 
 
 @pytest.mark.parametrize("M,N,K_", TG_SHAPES)
 @pytest.mark.parametrize("epi", ["f32", "bf16", "residual"])
-def test_gemm_tcgen05_with_store_and_residual_epilogues(K, M, N, K_, epi):
+def test_gemm_tcgen05_with_store_and_residual_epilogues(K, pairs, M, N, K_, epi):
     g = torch.Generator().manual_seed(M + N + K_)
     act = torch.randn(M, K_, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
@@ -511,7 +520,7 @@ def test_gemm_tcgen05_with_store_and_residual_epilogues(K, M, N, K_, epi):
 
 
 @pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (300, 136, 96), (2048, 5760, 2304), (77, 520, 200)])
-def test_gemm_tcgen05_with_swiglu_epilogue(K, M, N, K_):
+def test_gemm_tcgen05_with_swiglu_epilogue(K, pairs, M, N, K_):
     g = torch.Generator().manual_seed(M * 3 + N)
     act = torch.randn(M, K_, generator=g).to(torch.bfloat16)
     w = (torch.randn(2 * N, K_, generator=g) * 2 / math.sqrt(K_)).to(torch.bfloat16)

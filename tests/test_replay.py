@@ -105,11 +105,21 @@ def test_every_product_kernel_gives_the_same_model(tiny_models, name):
         check(got, "r", want, TOL["bfloat16"], f"{name} products by {mode}")
 
 
-def test_the_tcgen05_kernels_carry_a_whole_model(tiny_models):
+@pytest.fixture(params=[1, 2], ids=["single blocks", "pairs of blocks"])
+def product_pairs(request):
+    from infinicore_infer_b200 import kernels
+    before = kernels.gemm_tcgen05_pairs(request.param)
+    yield request.param
+    kernels.gemm_tcgen05_pairs(1 if before < 0 else before)
+
+
+def test_the_tcgen05_kernels_carry_a_whole_model(tiny_models, product_pairs):
     """Heads of 64: portions of more than 8 rows run the tcgen05 attention kernel; with the row limit of
     the tcgen05 product lowered, the q/k/v product rotates and writes the cache in its epilogue, gate/up
     applies SwiGLU in its epilogue and o/down add into the residual stream by TMA.  Whole, in portions
-    (several 128-row tiles, ragged ends) and mixed with decoded tokens, against the plain implementation."""
+    (several 128-row tiles, ragged ends) and mixed with decoded tokens, against the plain implementation;
+    once with every product on single blocks (tiny products never reach pairs by themselves), once with
+    every product of more than 128 rows on pairs of blocks."""
     eng = make_engine(tiny_models["D"][0], "bfloat16", 1024)
     eng.runtime.tcgen05_min_tiles = 1
     eng.runtime.tcgen05_min_rows = 17
