@@ -189,6 +189,8 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
                     help="run a few steps between cudaProfilerStart/Stop (for ncu --profile-from-start off) and exit")
+    ap.add_argument("--shape", default="2b", choices=["2b", "1b", "8b"],
+                    help="layer sizes: 2b is the headline configuration; the others are for profiles and side measurements")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="instead of the decode benchmark: a serving-style workload through the scheduler")
     args = ap.parse_args()
@@ -216,7 +218,8 @@ def main():
     from infinicore_infer_b200 import kernels
 
     peaks, peak_source = load_peaks()
-    shape = dict(SHAPE_2B)
+    shape = dict({"2b": SHAPE_2B, "1b": SHAPE_1B, "8b": SHAPE_8B}[args.shape])
+    shape_name = {"2b": "MiniCPM-2B shape", "1b": "MiniCPM-1B shape", "8b": "FM9G-8B-class shape"}[args.shape]
     full_layers = shape["num_hidden_layers"]
     if args.layers:
         shape["num_hidden_layers"] = args.layers
@@ -229,7 +232,8 @@ def main():
     max_b = max(max_b, args.batch)
     cache_tokens = max_b * (args.context + page)
     t_load = time.time()
-    weights = DeviceRandomWeights(model_manifest(spec), seed=0, compute_dtype=torch.bfloat16, device=dev, std=0.02)
+    weights = DeviceRandomWeights(model_manifest(spec), seed=0, compute_dtype=torch.bfloat16, device=dev, std=0.02,
+                                  untied=not shape["tie_word_embeddings"])
     engine = Engine(spec, weights, dtype=torch.bfloat16, device=dev, cache_tokens=cache_tokens, page_size=page,
                     max_requests=max_b, max_step_tokens=4096)
     engine.config = cfg
@@ -380,12 +384,12 @@ def main():
 
     meta_bytes = 4 * (7 * args.batch + 8 + args.batch * engine.cache.max_blocks * len(engine.cache.groups))
     line = {
-        "metric": "decode tok/s @ batch 8 (MiniCPM-2B shape, context 4096)",
+        "metric": f"decode tok/s @ batch {args.batch} ({shape_name}, context {args.context})",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random-init weights N(0,0.02), uniform random token ids, random cache contents",
         "config": {
-            "model": "MiniCPM-2B shape", "layers": cfg.num_hidden_layers, "layers_of_shape": full_layers,
+            "model": shape_name, "layers": cfg.num_hidden_layers, "layers_of_shape": full_layers,
             "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
             "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
             "tied_embeddings": True, "global_batch": args.batch, "seq_len": args.context,

@@ -433,6 +433,8 @@ static int launch_decode(const DecodeArgs &a, cudaStream_t stream) {
     return JK_OK;
 }
 
+static int decode_gqa(const DecodeArgs &a, cudaStream_t stream, bool *taken);      // further down, beside its helpers
+
 // Scratch floats that `jk_attention_decode` needs for (nrows, nh, dh, splits).
 JK_EXPORT long long jk_attention_decode_scratch_floats(int nrows, int nh, int dh, int splits) {
     if (splits <= 1) return 0;
@@ -462,6 +464,11 @@ JK_EXPORT int jk_attention_decode(const void *q, const void *k_pages, const void
     while ((1 << a.page_shift) < page_size) ++a.page_shift;
     const int g = nh / nkvh;
     const int lanes = dh / 8;
+    {
+        bool taken = false;
+        const int rc = decode_gqa(a, stream, &taken);
+        if (taken) return rc;
+    }
 #define DEC_DISPATCH_P2(LPR, HG) return pow2 ? launch_decode<LPR, HG, true>(a, stream) : launch_decode<LPR, HG, false>(a, stream)
 #define DEC_DISPATCH_HG(LPR)                                         \
     do {                                                             \
@@ -698,6 +705,229 @@ static int launch_prefill(const PrefillArgs &a, cudaStream_t stream) {
     }
     jk_launch(attention_prefill_kernel<DH, BN>, dim3(a.nh, a.ntiles * (a.tile_rows / PF_BM)), dim3(128), smem, stream, a);
     JK_CHECK_LAUNCH("attention_prefill");
+    return JK_OK;
+}
+
+
+// =======================================================================================
+// Decode attention for grouped heads (more than four query heads per key/value head): the group is
+// the M side of mma.sync m16n8k16, so a block reads its keys and values once for up to 16 query heads
+// and does the two products on the tensor cores.  Grid (split, key/value head x head tile, row); a block
+// walks over its range of keys in tiles of 64 that cp.async brings into a swizzled ring (three tiles of
+// keys and values in flight); warp w takes keys 16w..16w+15 of every tile with its own running maximum,
+// sum and accumulator, the four are merged through shared memory at the end.  Output as the kernel
+// above: final rows when there is one split, partial (accumulator, maximum, sum) else.
+// =======================================================================================
+constexpr int GQ_KEYS = 64, GQ_STAGES = 3, GQ_HEADS = 16;
+
+__device__ __forceinline__ void cp_async16_or_zero(void *smem, const void *gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;              // 0 bytes read: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+
+template <int DH>
+__global__ void __launch_bounds__(128)
+attention_decode_gqa_kernel(DecodeArgs a) {
+    static_assert(DH == 64 || DH == 128, "the swizzle chunk ^ (key & 7) needs rows of 8 or 16 chunks");
+    constexpr int CH = DH / 8;                     // 16-byte chunks of a key row
+    constexpr int TILE = GQ_KEYS * CH;             // uint4 per tile of keys (or values)
+    extern __shared__ uint4 gq_smem[];
+    pdl_trigger();
+    const int split = blockIdx.x, kh = blockIdx.y % a.nkvh, ht = blockIdx.y / a.nkvh, ri = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = a.nh / a.nkvh;
+    const int h0 = kh * g + ht * GQ_HEADS;         // first query head of this block
+    const int heads = min(GQ_HEADS, g - ht * GQ_HEADS);
+    pdl_wait();
+    const int t = a.rows ? a.rows[ri] : ri;
+    const int pos = a.positions[t], req = a.row_req[t];
+    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0, hi = pos + 1;
+    const int tiles_all = (hi - lo + GQ_KEYS - 1) / GQ_KEYS;
+    const int per = (tiles_all + a.splits - 1) / a.splits;
+    const int k0 = lo + split * per * GQ_KEYS, k1 = min(hi, k0 + per * GQ_KEYS);
+    const size_t pbase = ((size_t)ri * a.nh + h0) * a.splits + split;      // + head * splits
+    if (k0 >= k1) {                                // nothing for this split: the merge skips it
+        if (a.splits > 1 && threadIdx.x < heads) {
+            a.part_ml[(pbase + (size_t)threadIdx.x * a.splits) * 2] = -INFINITY;
+            a.part_ml[(pbase + (size_t)threadIdx.x * a.splits) * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    const int ntiles = (k1 - k0 + GQ_KEYS - 1) / GQ_KEYS;
+    const int *bt = a.block_table + (size_t)req * a.max_blocks;
+
+    // 16 bytes of key `key` of a tile lie at chunk ^ (key & 7): ldmatrix reads eight rows without conflicts
+    auto load_tile = [&](int i) {
+        uint4 *kd = gq_smem + (size_t)(i % GQ_STAGES) * 2 * TILE, *vd = kd + TILE;
+        const int kb = k0 + i * GQ_KEYS;
+#pragma unroll
+        for (int c = 0; c < TILE / 128; ++c) {
+            const int idx = c * 128 + threadIdx.x, key = idx / CH, ch = idx % CH;
+            const int kj = kb + key;
+            const bool valid = kj < k1;
+            size_t off = 0;
+            if (valid) {
+                const int page = bt[kj / a.page_size];
+                off = (((size_t)page * a.nkvh + kh) * a.page_size + kj % a.page_size) * DH + ch * 8;
+            }
+            const int slot = key * CH + (ch ^ (key & 7));
+            cp_async16_or_zero(kd + slot, a.k_pages + off, valid);
+            cp_async16_or_zero(vd + slot, a.v_pages + off, valid);
+        }
+    };
+    for (int i = 0; i < GQ_STAGES - 1; ++i) {
+        if (i < ntiles) load_tile(i);
+        cp_async_commit();
+    }
+    // the group's queries as A fragments: rows are heads (zero beyond the group), 16 dims per step
+    unsigned qf[DH / 16][4];
+    {
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+        const __nv_bfloat16 *q0 = a.q + ((size_t)t * a.nh + h0 + r0) * DH, *q1 = q0 + (size_t)8 * DH;
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+            qf[kk][0] = r0 < heads ? *reinterpret_cast<const unsigned *>(q0 + kk * 16 + c0) : 0u;
+            qf[kk][1] = r0 + 8 < heads ? *reinterpret_cast<const unsigned *>(q1 + kk * 16 + c0) : 0u;
+            qf[kk][2] = r0 < heads ? *reinterpret_cast<const unsigned *>(q0 + kk * 16 + 8 + c0) : 0u;
+            qf[kk][3] = r0 + 8 < heads ? *reinterpret_cast<const unsigned *>(q1 + kk * 16 + 8 + c0) : 0u;
+        }
+    }
+    float o[DH / 8][4];
+#pragma unroll
+    for (int n = 0; n < DH / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // heads lane / 4 and lane / 4 + 8
+
+    for (int i = 0; i < ntiles; ++i) {
+        cp_async_wait<GQ_STAGES - 2>();
+        __syncthreads();                           // tile i has landed for everyone; tile i - 1 is no longer read
+        if (i + GQ_STAGES - 1 < ntiles) load_tile(i + GQ_STAGES - 1);
+        cp_async_commit();
+        const uint4 *kt = gq_smem + (size_t)(i % GQ_STAGES) * 2 * TILE, *vt = kt + TILE;
+        const int kw = k0 + i * GQ_KEYS + warp * 16;          // this warp's first key of the tile
+        if (kw >= k1) continue;                                // warp-uniform: no key of the tile is this warp's
+        float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+            // matrices: (keys 0-7, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, dims 0-7), (keys 8-15, dims 8-15)
+            const int key = warp * 16 + ((lane >> 4) << 3) + (lane & 7), ch = kk * 2 + ((lane >> 3) & 1);
+            unsigned b[4];
+            ldmatrix_x4(b, kt + key * CH + (ch ^ (key & 7)));
+            mma_bf16(sc[0], qf[kk], b[0], b[1]);
+            mma_bf16(sc[1], qf[kk], b[2], b[3]);
+        }
+        // scores in the log2 domain; keys beyond the range count as minus infinity
+        float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const bool in = kw + j * 8 + (lane & 3) * 2 + e < k1;
+                sc[j][e] = in ? sc[j][e] * a.scale_log2 : -INFINITY;
+                sc[j][2 + e] = in ? sc[j][2 + e] * a.scale_log2 : -INFINITY;
+                t0 = fmaxf(t0, sc[j][e]);
+                t1 = fmaxf(t1, sc[j][2 + e]);
+            }
+        t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1)); t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+        t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1)); t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+        // the warp's first key is in range, so both maxima are finite (a score itself is finite)
+        const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);
+        const float c0 = fast_exp2(m0 - n0), c1 = fast_exp2(m1 - n1);
+        m0 = n0; m1 = n1;
+        unsigned pa[4];
+        float p[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            p[j][0] = fast_exp2(sc[j][0] - n0); p[j][1] = fast_exp2(sc[j][1] - n0);
+            p[j][2] = fast_exp2(sc[j][2] - n1); p[j][3] = fast_exp2(sc[j][3] - n1);
+        }
+        l0 = l0 * c0 + p[0][0] + p[0][1] + p[1][0] + p[1][1];
+        l1 = l1 * c1 + p[0][2] + p[0][3] + p[1][2] + p[1][3];
+        pa[0] = pack_bf16(p[0][0], p[0][1]); pa[1] = pack_bf16(p[0][2], p[0][3]);
+        pa[2] = pack_bf16(p[1][0], p[1][1]); pa[3] = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+        for (int n = 0; n < DH / 8; ++n) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+#pragma unroll
+        for (int d2 = 0; d2 < DH / 16; ++d2) {
+            // transposed: (keys 0-7, dims 16 d2 ..+7), (keys 8-15, same dims), (keys 0-7, dims +8..+15), (keys 8-15, ...)
+            const int key = warp * 16 + (((lane >> 3) & 1) << 3) + (lane & 7), ch = d2 * 2 + (lane >> 4);
+            unsigned b[4];
+            ldmatrix_x4_trans(b, vt + key * CH + (ch ^ (key & 7)));
+            mma_bf16(o[2 * d2], pa, b[0], b[1]);
+            mma_bf16(o[2 * d2 + 1], pa, b[2], b[3]);
+        }
+    }
+    cp_async_wait<0>();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    __syncthreads();                               // the ring is free: it carries the four warps' results
+    float *red = reinterpret_cast<float *>(gq_smem);           // [warp][head][DH + 2]
+    {
+        float *mine = red + (size_t)warp * GQ_HEADS * (DH + 2);
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int n = 0; n < DH / 8; ++n) {
+            mine[r0 * (DH + 2) + n * 8 + c0] = o[n][0]; mine[r0 * (DH + 2) + n * 8 + c0 + 1] = o[n][1];
+            mine[(r0 + 8) * (DH + 2) + n * 8 + c0] = o[n][2]; mine[(r0 + 8) * (DH + 2) + n * 8 + c0 + 1] = o[n][3];
+        }
+        if ((lane & 3) == 0) {
+            mine[r0 * (DH + 2) + DH] = m0; mine[r0 * (DH + 2) + DH + 1] = l0;
+            mine[(r0 + 8) * (DH + 2) + DH] = m1; mine[(r0 + 8) * (DH + 2) + DH + 1] = l1;
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < heads * DH; idx += 128) {
+        const int r = idx / DH, e = idx % DH;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, red[((size_t)w * GQ_HEADS + r) * (DH + 2) + DH]);
+        float L = 0.f, A = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float *src = red + ((size_t)w * GQ_HEADS + r) * (DH + 2);
+            const float f = fast_exp2(src[DH] - M);             // a warp without keys: 2^-inf = 0
+            L += f * src[DH + 1];
+            A += f * src[e];
+        }
+        if (a.splits == 1) {
+            a.out[((size_t)t * a.nh + h0 + r) * DH + e] = __float2bfloat16_rn(A / L);
+        } else {
+            const size_t slot = pbase + (size_t)r * a.splits;
+            a.part_acc[slot * DH + e] = A;
+            if (e == 0) { a.part_ml[slot * 2] = M; a.part_ml[slot * 2 + 1] = L; }
+        }
+    }
+}
+
+template <int DH>
+static int launch_decode_gqa(const DecodeArgs &a, cudaStream_t stream) {
+    const int g = a.nh / a.nkvh;
+    const size_t ring = (size_t)GQ_STAGES * 2 * GQ_KEYS * DH * sizeof(__nv_bfloat16);
+    const size_t merge = (size_t)4 * GQ_HEADS * (DH + 2) * sizeof(float);
+    const size_t smem = ring > merge ? ring : merge;
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_gqa_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_decode: %s", cudaGetErrorString(e));
+    dim3 grid(a.splits, a.nkvh * ((g + GQ_HEADS - 1) / GQ_HEADS), a.nrows);
+    jk_launch(attention_decode_gqa_kernel<DH>, grid, dim3(128), smem, stream, a);
+    JK_CHECK_LAUNCH("attention_decode_gqa");
+    if (a.splits > 1) {
+        jk_launch(attention_combine_kernel, dim3(a.nh, a.nrows), dim3(64), 0, stream, a);
+        JK_CHECK_LAUNCH("attention_combine");
+    }
+    return JK_OK;
+}
+
+// Groups of more than four query heads per key/value head with a head size of 64 or 128 go to the tensor-core
+// decode kernel; everything else stays on the kernel of the CUDA cores.
+static int decode_gqa(const DecodeArgs &a, cudaStream_t stream, bool *taken) {
+    *taken = true;
+    if (a.nh / a.nkvh > 4) {
+        switch (a.dh) {
+            case 64: return launch_decode_gqa<64>(a, stream);       // rows of 8 or 16 chunks: what the swizzle takes
+            case 128: return launch_decode_gqa<128>(a, stream);
+        }
+    }
+    *taken = false;
     return JK_OK;
 }
 

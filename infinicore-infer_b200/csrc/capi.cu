@@ -172,6 +172,9 @@ int bind_from_directory(JkModel *m, const char *dir, bool need_gemm_tcgen05, boo
     f.rope_kv = (RopeKvFn)sym(ew, "jk_rope_kv");
     f.linear_small = (LinearSmallFn)sym(ls, "jk_linear_small");
     f.linear_small_qkv = (LinearSmallQkvFn)sym(ls, "jk_linear_small_qkv");
+    f.linear_small_supports = (SupportsFn)sym(ls, "jk_linear_small_supports");
+    f.linear_small_qkv_supports = (SupportsFn)sym(ls, "jk_linear_small_qkv_supports");
+    f.gemm_skinny = (GemmTcgen05Fn)sym(gt, "jk_gemm_skinny");
     f.gemm_tcgen05 = (GemmTcgen05Fn)sym(gt, "jk_gemm_tcgen05");
     f.gemm_tcgen05_qkv = (GemmTcgen05QkvFn)sym(gt, "jk_gemm_tcgen05_qkv");
     f.attention_decode = (AttentionDecodeFn)sym(at, "jk_attention_decode");
@@ -195,12 +198,18 @@ bool takes_tcgen05(const RunnerModel &m, int rows, int n, int k) {      // the r
     return (long long)((rows + 127) / 128) * ((n + 127) / 128) >= m.tcgen05_min_tiles;
 }
 
+// The gemm_tcgen05 module is loaded if a step can reach one of its kernels: the tiled one under the runner's
+// routing, or the few-rows one (a block for every SM).
 bool needs_gemm_tcgen05(const RunnerModel &rm, int max_step_tokens) {
     const int nq = (rm.heads + 2 * rm.kv_heads) * rm.head_dim;
-    const int products[5][2] = {{nq, rm.hidden}, {rm.hidden, rm.heads * rm.head_dim}, {2 * rm.intermediate, rm.hidden},
-                                {rm.hidden, rm.intermediate}, {rm.vocab, rm.hidden}};
-    for (auto &p : products)
-        if (takes_tcgen05(rm, max_step_tokens, p[0], p[1])) return true;
+    const int products[5][3] = {{nq, rm.hidden, RUNNER_F32}, {rm.hidden, rm.heads * rm.head_dim, RUNNER_RESIDUAL},
+                                {rm.intermediate, rm.hidden, RUNNER_SWIGLU}, {rm.hidden, rm.intermediate, RUNNER_RESIDUAL},
+                                {rm.vocab, rm.hidden, RUNNER_F32}};
+    const long long need = rm.skinny_min_blocks > 0 ? rm.skinny_min_blocks : rm.sms;
+    for (auto &p : products) {
+        if (takes_tcgen05(rm, max_step_tokens, p[2] == RUNNER_SWIGLU ? 2 * p[0] : p[0], p[1])) return true;
+        if (p[1] % 8 == 0 && runner_skinny_blocks(rm.sms, p[0], p[1], p[2]) >= need) return true;
+    }
     return false;
 }
 
@@ -211,8 +220,9 @@ bool tcgen05_attention_takes(int dh, int page) {
 // How many ways the decode kernel cuts each row's key range: full waves of blocks (three fit an SM)
 // against a block's fixed cost of about 128 keys' worth of time, at half the longest context.
 int decode_splits(int nrows, int nkvh, int group, int max_positions, int sms) {
-    const long long blocks = std::max(1, nrows * nkvh * (group > 4 ? (group + 3) / 4 : 1));
-    const long long slots = (long long)sms * 3;
+    // groups of more than four query heads run on the tensor-core kernel: 16 heads and two blocks an SM
+    const long long blocks = std::max(1, nrows * nkvh * (group > 4 ? (group + 15) / 16 : 1));
+    const long long slots = (long long)sms * (group > 4 ? 2 : 3);
     const double keys = std::max(1, max_positions / 2);
     int best = 1;
     double best_cost = -1;

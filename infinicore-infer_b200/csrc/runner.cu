@@ -32,9 +32,10 @@ JK_EXPORT int jk_runner_bind(const RunnerFns *fns) {
     // the tcgen05 modules may be left out by a caller whose model or step size never reaches them (they are
     // then not even compiled); everything else is needed by every model
     JK_REQUIRE(fns->embed && fns->add_rmsnorm && fns->swiglu && fns->rope_kv && fns->linear_small && fns->linear_small_qkv &&
-               fns->attention_decode && fns->attention_prefill && fns->err_elementwise && fns->err_linear_small &&
+               fns->linear_small_supports && fns->linear_small_qkv_supports && fns->attention_decode && fns->attention_prefill && fns->err_elementwise && fns->err_linear_small &&
                fns->err_attention, "runner_bind: an entry that every model needs is empty");
     JK_REQUIRE((fns->gemm_tcgen05 != nullptr) == (fns->gemm_tcgen05_qkv != nullptr) &&
+               (fns->gemm_tcgen05 != nullptr) == (fns->gemm_skinny != nullptr) &&
                (fns->gemm_tcgen05 != nullptr) == (fns->err_gemm_tcgen05 != nullptr) &&
                (fns->attention_tcgen05 != nullptr) == (fns->err_attention_tcgen05 != nullptr),
                "runner_bind: a module's entries come together");
@@ -90,11 +91,30 @@ static bool takes_tcgen05(const RunnerModel &m, int rows, int n, int k) {
     return tiles >= m.tcgen05_min_tiles;
 }
 
+// Which kernel takes a product of at most 128 rows (the same rule as Runtime.few_rows_route of the parts): the
+// few-rows tcgen05 kernel once it has a block for every SM; up to 16 rows the small-row kernel where it has a
+// second block on the SM to overlap its load phase with (a slice of 16 rows x K fits twice), or so few tiles that
+// they make one wave, or nothing better; else the library.
+enum Route { ROUTE_LIBRARY, ROUTE_SMALL, ROUTE_SKINNY };
+static Route few_rows_route(const RunnerModel &m, int rows, int n, int k, int kind) {
+    if (rows > 128) return ROUTE_LIBRARY;
+    const long long need = m.skinny_min_blocks > 0 ? m.skinny_min_blocks : m.sms;
+    const bool skinny = g_fns.gemm_skinny != nullptr && k % 8 == 0 && runner_skinny_blocks(m.sms, n, k, kind) >= need;
+    if (rows <= 16 && g_fns.linear_small_supports(rows, n, k)) {
+        const long long out_rows = kind == RUNNER_SWIGLU ? 2LL * n : n;
+        if (!skinny || 2 * (32LL * k + 8192) <= 227 * 1024 || (out_rows + 15) / 16 <= m.sms) return ROUTE_SMALL;
+    }
+    return skinny ? ROUTE_SKINNY : ROUTE_LIBRARY;
+}
+
 // out (float32 [rows, n]) = act * w^T by whichever kernel takes `rows`
 static int product_f32(const RunnerModel &m, const RunnerScratch &s, const void *act, const void *w, float *out, int rows, int n,
                        int k, cudaStream_t stream) {
-    if (rows <= 16 && k % 32 == 0) {
+    const Route route = few_rows_route(m, rows, n, k, RUNNER_F32);
+    if (route == ROUTE_SMALL) {
         RUN(linear_small, g_fns.linear_small(act, w, out, rows, n, k, n, 0, m.sms, stream));
+    } else if (route == ROUTE_SKINNY) {
+        RUN(gemm_tcgen05, g_fns.gemm_skinny(act, w, out, rows, n, k, n, 0, 1.f, m.status, m.sms, stream));
     } else if (takes_tcgen05(m, rows, n, k)) {
         RUN(gemm_tcgen05, g_fns.gemm_tcgen05(act, w, out, rows, n, k, n, 0, 1.f, m.status, m.sms, stream));
     } else {
@@ -106,9 +126,13 @@ static int product_f32(const RunnerModel &m, const RunnerScratch &s, const void 
 // x += scale * (act * w^T): in the product's epilogue where that exists, else left pending for the next norm
 static int product_into_residual(const RunnerModel &m, const RunnerScratch &s, const void *act, const void *w, int rows, int n,
                                  int k, bool *pending, cudaStream_t stream) {
+    *pending = false;
+    if (few_rows_route(m, rows, n, k, RUNNER_RESIDUAL) == ROUTE_SKINNY) {
+        RUN(gemm_tcgen05, g_fns.gemm_skinny(act, w, s.x, rows, n, k, n, 2, m.residual_scale, m.status, m.sms, stream));
+        return JK_OK;
+    }
     if (takes_tcgen05(m, rows, n, k)) {
         RUN(gemm_tcgen05, g_fns.gemm_tcgen05(act, w, s.x, rows, n, k, n, 2, m.residual_scale, m.status, m.sms, stream));
-        *pending = false;
         return JK_OK;
     }
     *pending = true;
@@ -138,7 +162,7 @@ JK_EXPORT int jk_runner_forward(const RunnerModel *mp, const RunnerLayer *layers
             RUN(gemm_tcgen05, g_fns.gemm_tcgen05_qkv(s.h, L.w_qkv, T, d, s.q, L.k_pages, L.v_pages, m.cos_table, m.sin_table,
                                                      st.positions, st.row_req, st.block_table, m.max_blocks, m.page_size, nh,
                                                      nkvh, dh, m.status, m.sms, stream));
-        } else if (T <= 16 && d % 32 == 0 && dh % 16 == 0) {
+        } else if (T <= 16 && g_fns.linear_small_qkv_supports(T, d, dh)) {
             RUN(linear_small, g_fns.linear_small_qkv(s.h, L.w_qkv, T, d, s.q, L.k_pages, L.v_pages, m.cos_table, m.sin_table,
                                                      st.positions, st.row_req, st.block_table, m.max_blocks, m.page_size, nh,
                                                      nkvh, dh, m.sms, stream));
@@ -168,8 +192,11 @@ JK_EXPORT int jk_runner_forward(const RunnerModel *mp, const RunnerLayer *layers
         RUN(elementwise, g_fns.add_rmsnorm(s.x, pending ? s.delta : nullptr, JK_F32, m.residual_scale, L.norm2, L.eps2, 1.f, s.h,
                                            JK_BF16, nullptr, T, d, stream));
         pending = false;
-        if (T <= 16 && d % 32 == 0) {
+        const Route gate_up = few_rows_route(m, T, di, d, RUNNER_SWIGLU);
+        if (gate_up == ROUTE_SMALL) {
             RUN(linear_small, g_fns.linear_small(s.h, L.w_gate_up, s.act, T, di, d, di, 1, m.sms, stream));
+        } else if (gate_up == ROUTE_SKINNY) {
+            RUN(gemm_tcgen05, g_fns.gemm_skinny(s.h, L.w_gate_up, s.act, T, di, d, di, 3, 1.f, m.status, m.sms, stream));
         } else if (takes_tcgen05(m, T, di, d)) {
             RUN(gemm_tcgen05, g_fns.gemm_tcgen05(s.h, L.w_gate_up, s.act, T, di, d, di, 3, 1.f, m.status, m.sms, stream));
         } else {

@@ -24,6 +24,7 @@ typedef int (*AttentionPrefillFn)(const void *, const void *, const void *, void
                                   const int *, const int *, int, int, int, int, int, float, int, cudaStream_t);
 typedef int (*AttentionTcgen05Fn)(const void *, const void *, const void *, void *, const int *, int, int, const int *,
                                   const int *, const int *, int, int, int, int, int, int, float, int, int *, cudaStream_t);
+typedef int (*SupportsFn)(int, int, int);
 typedef const char *(*LastErrorFn)();
 typedef int (*ArgmaxFn)(const float *, long long, int, int, int *, void *, cudaStream_t);
 typedef int (*SampleFn)(const float *, long long, int, int, const float *, const int *, const float *, const float *, int *,
@@ -43,6 +44,10 @@ struct RunnerFns {
     AttentionPrefillFn attention_prefill;
     AttentionTcgen05Fn attention_tcgen05;
     LastErrorFn err_elementwise, err_linear_small, err_gemm_tcgen05, err_attention, err_attention_tcgen05;
+    // products of few rows: what the small-row kernels take, and the tcgen05 kernel with the weights on the MMA's M side
+    // (part of the gemm_tcgen05 module: bound with it or not at all)
+    SupportsFn linear_small_supports, linear_small_qkv_supports;
+    GemmTcgen05Fn gemm_skinny;
     // sampling (used by the C interface only; may be empty for a caller that samples by itself)
     ArgmaxFn argmax;
     SampleFn sample;
@@ -54,6 +59,7 @@ struct RunnerModel {
     int layers, hidden, heads, kv_heads, head_dim, intermediate, vocab;
     int page_size, max_blocks, num_pages, window;
     int sms, tcgen05_min_rows, tcgen05_min_tiles;
+    int skinny_min_blocks;          // fewest blocks for which the few-rows tcgen05 kernel is used (0: one per SM)
     int attention_tcgen05;          // 1: tiles go to the tcgen05 attention kernel, 0: to the mma.sync kernel
     int embed_dtype;                // JK_F32 or JK_BF16
     float embed_scale, residual_scale, logit_scale, softmax_scale, final_eps;
@@ -94,6 +100,23 @@ struct RunnerScratch {
     long long workspace_bytes;
 };
 
+// Blocks that the few-rows tcgen05 kernel (jk_gemm_skinny) starts for a product with `n` output features over `k`:
+// tiles of 128 features (64 for SwiGLU, whose tile holds as many up rows again); a product that is added into
+// the residual stream splits K until the blocks fill the SMs twice, as long as a block keeps 8 steps of 64.
+enum RunnerProductKind { RUNNER_F32 = 0, RUNNER_RESIDUAL = 1, RUNNER_SWIGLU = 2 };
+static inline long long runner_skinny_blocks(int sms, int n, int k, int kind) {
+    const int nk = (k + 63) / 64;
+    if (kind == RUNNER_SWIGLU) return (n + 63) / 64;
+    const int tiles = (n + 127) / 128;
+    int splits = 1;
+    if (kind == RUNNER_RESIDUAL) {
+        splits = 2 * sms / tiles;
+        if (splits > nk / 8) splits = nk / 8;
+        if (splits < 1) splits = 1;
+    }
+    const int ksteps = (nk + splits - 1) / splits;
+    return (long long)tiles * ((nk + ksteps - 1) / ksteps);
+}
 
 extern "C" {
 int jk_runner_bind(const RunnerFns *fns);

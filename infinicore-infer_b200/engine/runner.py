@@ -28,14 +28,14 @@ class _Fns(ctypes.Structure):
         "embed", "add_rmsnorm", "swiglu", "rope_kv", "linear_small", "linear_small_qkv", "gemm_tcgen05",
         "gemm_tcgen05_qkv", "attention_decode", "attention_prefill", "attention_tcgen05",
         "err_elementwise", "err_linear_small", "err_gemm_tcgen05", "err_attention", "err_attention_tcgen05",
-        "argmax", "sample", "err_sampling")]
+        "linear_small_supports", "linear_small_qkv_supports", "gemm_skinny", "argmax", "sample", "err_sampling")]
 
 
 class _Model(ctypes.Structure):
     _fields_ = ([(n, ctypes.c_int) for n in (
         "layers", "hidden", "heads", "kv_heads", "head_dim", "intermediate", "vocab",
         "page_size", "max_blocks", "num_pages", "window",
-        "sms", "tcgen05_min_rows", "tcgen05_min_tiles", "attention_tcgen05", "embed_dtype")]
+        "sms", "tcgen05_min_rows", "tcgen05_min_tiles", "skinny_min_blocks", "attention_tcgen05", "embed_dtype")]
                 + [(n, ctypes.c_float) for n in ("embed_scale", "residual_scale", "logit_scale", "softmax_scale", "final_eps")]
                 + [(n, ctypes.c_void_p) for n in ("embedding", "lm_head", "final_norm", "cos_table", "sin_table", "status")])
 
@@ -123,7 +123,10 @@ class NativeRunner:
             return "no tensor-core attention kernel for this head size"
         nq = (s.num_heads + 2 * s.num_kv_heads) * dh
         small = [(nq, d), (d, s.num_heads * dh), (di, d), (d, di), (spec.vocab_size, d)]
-        if any(k % 32 for _, k in small) or dh % 16 or not all(kernels.linear_small_supports(16, n, k) for n, k in small) \
+        # every product of few rows has a home: the small-row kernels, or (K too long for their shared memory)
+        # the few-rows tcgen05 kernel
+        if any(k % 32 for _, k in small) or dh % 16 \
+                or not all(kernels.linear_small_supports(16, n, k) or kernels.gemm_skinny_supports(16, n, k) for n, k in small) \
                 or not kernels.linear_small_qkv_supports(16, d, dh):
             return "a product is outside what the small-row kernels take"
         if model.embedding.dtype != torch.bfloat16 or model.lm_head.dtype != torch.bfloat16:
@@ -142,7 +145,8 @@ class NativeRunner:
         a = first.mixer.spec
         d, di, dh = spec.hidden_size, first.feed_forward.spec.intermediate_size, a.head_dim
         nq = (a.num_heads + 2 * a.num_kv_heads) * dh
-        self._products = [(nq, d), (d, a.num_heads * dh), (di, d), (d, di), (spec.vocab_size, d)]
+        self._products = [(nq, d, "f32"), (d, a.num_heads * dh, "residual"), (di, d, "swiglu"), (d, di, "residual"),
+                          (spec.vocab_size, d, "f32")]
         self._attention_tcgen05 = kernels.attention_tcgen05_supports(dh, cache.page_size)
         self._bound_tcgen05 = None
         self._bind()
@@ -153,14 +157,14 @@ class NativeRunner:
             layers=len(model.layers), hidden=d, heads=a.num_heads, kv_heads=a.num_kv_heads, head_dim=dh, intermediate=di,
             vocab=spec.vocab_size, page_size=cache.page_size, max_blocks=cache.max_blocks, num_pages=k0.shape[0],
             window=a.window or 0, sms=kernels._sm_count(dev), tcgen05_min_rows=rt.tcgen05_min_rows,
-            tcgen05_min_tiles=rt.tcgen05_min_tiles,
+            tcgen05_min_tiles=rt.tcgen05_min_tiles, skinny_min_blocks=rt.skinny_min_blocks or 0,
             attention_tcgen05=1 if self._attention_tcgen05 else 0,
             embed_dtype=kernels.dtype_code(model.embedding.dtype), embed_scale=spec.embed_scale,
             residual_scale=first.spec.residual_scale, logit_scale=spec.logit_scale, softmax_scale=a.softmax_scale,
             final_eps=model.final_norm.spec.eps, embedding=model.embedding.data_ptr(), lm_head=model.lm_head.data_ptr(),
             final_norm=model.final_norm.weight.data_ptr(), cos_table=pos.cos.data_ptr() if pos else 0,
             sin_table=pos.sin.data_ptr() if pos else 0, status=kernels.gemm_status(dev).data_ptr())
-        self._routing = (rt.tcgen05_min_rows, rt.tcgen05_min_tiles)
+        self._routing = (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.skinny_min_blocks)
         self._layers = (_Layer * len(model.layers))()
         for i, blk in enumerate(model.layers):
             view = cache.views[spec.order[i].cache]
@@ -188,7 +192,10 @@ class NativeRunner:
         compiled) only if a step of this engine can reach it under the runtime's routing, the tcgen05
         attention only for the head and page sizes it is built for."""
         rt = self.runtime
-        need_tc = any(rt.takes_tcgen05(self.max_step_tokens, n, k) for n, k in self._products)
+        rows = self.max_step_tokens
+        need_tc = any(rt.takes_tcgen05(rows, n, k)
+                      or "skinny" in (rt.few_rows_route(min(16, rows), n, k, kind), rt.few_rows_route(min(128, rows), n, k, kind))
+                      for n, k, kind in self._products)
         if self._bound_tcgen05 is not None and (self._bound_tcgen05 or not need_tc):
             return
         names = ["elementwise", "linear_small", "attention", "sampling"] + (["gemm_tcgen05"] if need_tc else []) \
@@ -200,6 +207,9 @@ class NativeRunner:
             swiglu=get("elementwise", "jk_swiglu"), rope_kv=get("elementwise", "jk_rope_kv"),
             linear_small=get("linear_small", "jk_linear_small"), linear_small_qkv=get("linear_small", "jk_linear_small_qkv"),
             gemm_tcgen05=get("gemm_tcgen05", "jk_gemm_tcgen05"), gemm_tcgen05_qkv=get("gemm_tcgen05", "jk_gemm_tcgen05_qkv"),
+            gemm_skinny=get("gemm_tcgen05", "jk_gemm_skinny"),
+            linear_small_supports=get("linear_small", "jk_linear_small_supports"),
+            linear_small_qkv_supports=get("linear_small", "jk_linear_small_qkv_supports"),
             attention_decode=get("attention", "jk_attention_decode"), attention_prefill=get("attention", "jk_attention_prefill"),
             attention_tcgen05=get("attention_tcgen05", "jk_attention_tcgen05"),
             err_elementwise=get("elementwise", "jk_elementwise_last_error"),
@@ -220,9 +230,10 @@ class NativeRunner:
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Logits (float32 ``[n_want, vocab]``) of the step that ``ctx`` describes."""
         rt = self.runtime
-        if (rt.tcgen05_min_rows, rt.tcgen05_min_tiles) != self._routing:       # a test moved the thresholds
-            self._routing = (rt.tcgen05_min_rows, rt.tcgen05_min_tiles)
+        if (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.skinny_min_blocks) != self._routing:       # a test moved the thresholds
+            self._routing = (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.skinny_min_blocks)
             self._model.tcgen05_min_rows, self._model.tcgen05_min_tiles = rt.tcgen05_min_rows, rt.tcgen05_min_tiles
+            self._model.skinny_min_blocks = rt.skinny_min_blocks or 0
             self._bind()
         d, di, nh, nkvh, dh = self.dims
         T = ctx.ntok

@@ -315,6 +315,31 @@ def gemm_tcgen05(act: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue
     return out
 
 
+def gemm_skinny_supports(m: int, n: int, k: int) -> bool:
+    """Up to 128 activation rows; K must keep rows 16-byte aligned for TMA."""
+    return 1 <= m <= 128 and n >= 1 and k >= 8 and k % 8 == 0
+
+
+def gemm_skinny(act: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = TG_F32, scale: float = 1.0) -> torch.Tensor:
+    """The product of few activation rows (decode batches, short portions) on the tcgen05 tensor cores with the
+    weights on the MMA's M side, so that the kernel streams W once at memory speed: TG_F32 ``out = product``
+    (float32), TG_RESIDUAL ``out += scale * product`` (float32, blocks split K and add their partial sums),
+    TG_SWIGLU ``w`` is [2N, K] and ``out`` bfloat16 = silu(gate) * up."""
+    if epilogue not in (TG_F32, TG_RESIDUAL, TG_SWIGLU):
+        raise KernelError(f"gemm_skinny: epilogue {epilogue}")
+    _need(act, "act", torch.bfloat16); _need(w, "w", torch.bfloat16)
+    _need(out, "out", torch.bfloat16 if epilogue == TG_SWIGLU else torch.float32, contiguous=False)
+    m, k = act.shape
+    n = w.shape[0] // (2 if epilogue == TG_SWIGLU else 1)
+    if w.shape[1] != k or tuple(out.shape) != (m, n) or out.stride(1) != 1:
+        raise KernelError(f"gemm_skinny: act {tuple(act.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    lib = _build.load("gemm_tcgen05")
+    _check("gemm_tcgen05", lib.jk_gemm_skinny(_ptr(act), _ptr(w), _ptr(out), _c_int(m), _c_int(n), _c_int(k),
+                                              _c_int(out.stride(0)), _c_int(epilogue), _c_float(scale),
+                                              _ptr(gemm_status(act.device)), _c_int(_sm_count(act.device)), _stream()))
+    return out
+
+
 _SMS = {}
 
 
@@ -351,8 +376,9 @@ def attention_decode_splits(nrows: int, nkvh: int, group: int, max_positions: in
     full waves of blocks (a last wave that is nearly empty costs as much as a full one) against the
     fixed cost of a block (about 128 keys' worth of time for set-up and the merge of its groups), at
     half the longest context."""
-    blocks = max(1, nrows * nkvh * ((group + 3) // 4 if group > 4 else 1))
-    slots = sms * 3
+    # groups of more than four query heads run on the tensor-core kernel: 16 heads and two blocks an SM
+    blocks = max(1, nrows * nkvh * ((group + 15) // 16 if group > 4 else 1))
+    slots = sms * (2 if group > 4 else 3)
     keys = max(1, max_positions // 2)
     best, best_cost = 1, None
     for s in range(1, 33):

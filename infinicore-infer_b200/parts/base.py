@@ -69,6 +69,7 @@ class Runtime:
         self.legacy_tensor_cores = False     # True: prefill attention on mma.sync even where tcgen05 is built
         self.tcgen05_min_tiles = 96          # fewest 128x128 output tiles for which the tcgen05 kernel is used
         self.tcgen05_min_rows = 1024         # ... and fewest rows: below, the library's split-K kernels win
+        self.skinny_min_blocks: Optional[int] = None   # fewest blocks for the few-rows tcgen05 kernel (None: one per SM)
 
     def empty(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
@@ -84,8 +85,12 @@ class Runtime:
         m, k = h.shape
         n = weight.shape[0]
         if not self.library_products_only:
-            if out_dtype == torch.float32 and m <= 16 and kernels.linear_small_supports(m, n, k):
+            route = self.few_rows_route(m, n, k, "f32") if out_dtype == torch.float32 else "library"
+            if route == "small":
                 out = kernels.linear_small(h, weight, self.empty(m, n, dtype=torch.float32))
+                return out if bias is None else out.add_(bias)
+            if route == "skinny":
+                out = kernels.gemm_skinny(h, weight, self.empty(m, n, dtype=torch.float32), kernels.TG_F32)
                 return out if bias is None else out.add_(bias)
             if self.takes_tcgen05(m, n, k):
                 out = kernels.gemm_tcgen05(h, weight, self.empty(m, n, dtype=out_dtype),
@@ -107,8 +112,11 @@ class Runtime:
         di = w_gate_up.shape[0] // 2
         act = self.empty(m, di)
         if self.dtype == torch.bfloat16 and not self.library_products_only:
-            if m <= 16 and kernels.linear_small_supports(m, di, k):
+            route = self.few_rows_route(m, di, k, "swiglu")
+            if route == "small":
                 return kernels.linear_small(h, w_gate_up, act, kernels.EPI_SWIGLU)
+            if route == "skinny":
+                return kernels.gemm_skinny(h, w_gate_up, act, kernels.TG_SWIGLU)
             if self.takes_tcgen05(m, di, k):
                 return kernels.gemm_tcgen05(h, w_gate_up, act, kernels.TG_SWIGLU)
         gu = self.linear(h, w_gate_up, out_dtype=torch.float32)
@@ -118,6 +126,35 @@ class Runtime:
         """act @ weight^T that has not run yet: whoever takes it decides where the result goes (a
         tensor of its own, or straight into the residual stream)."""
         return PendingProduct(self, act, weight)
+
+    def few_rows_route(self, m: int, n: int, k: int, kind: str) -> str:
+        """Which kernel takes a bfloat16 product of at most 128 rows: ``"small"`` (the weight-streaming kernels of
+        the CUDA cores, up to 16 rows), ``"skinny"`` (the tcgen05 kernel with the weights on the MMA's M side)
+        or ``"library"``.  ``kind``: "f32" (plain output), "residual" (added into the stream), "swiglu" (``n`` is
+        the width after the activation).  Measured on the 2B and 8B shapes: the skinny kernel reads at 5 to 6 TB/s
+        once it has a block for every SM (output tiles of 128 features, 64 for SwiGLU, times the splits of K that a
+        residual product allows); the small kernel loads a tile's whole slice of K before it computes, so it needs
+        a second block on the SM to overlap with (a slice of 16 rows x K fits twice) or so few tiles that they
+        make one wave."""
+        from .. import kernels
+        if self.dtype != torch.bfloat16 or self.library_products_only or m > 128:
+            return "library"
+        sms = kernels._sm_count(self.device)
+        need = sms if self.skinny_min_blocks is None else self.skinny_min_blocks
+        nk = -(-k // 64)
+        if kind == "swiglu":
+            blocks = -(-n // 64)
+        else:
+            tiles = -(-n // 128)
+            splits = max(1, min(2 * sms // tiles, nk // 8)) if kind == "residual" else 1
+            blocks = tiles * (-(-nk // -(-nk // splits)))
+        skinny = blocks >= need and kernels.gemm_skinny_supports(m, n, k)
+        if m <= 16:
+            rows = 2 * n if kind == "swiglu" else n
+            if kernels.linear_small_supports(m, n, k):
+                if not skinny or 2 * (32 * k + 8192) <= 227 * 1024 or -(-rows // 16) <= sms:
+                    return "small"
+        return "skinny" if skinny else "library"
 
     def takes_tcgen05(self, m: int, n: int, k: int) -> bool:
         """The tcgen05 kernel works on 128 x 256 tiles with one block per SM: it takes a product that has
@@ -135,7 +172,7 @@ class Runtime:
         return tiles >= self.tcgen05_min_tiles and kernels.gemm_tcgen05_supports(m, n, k)
 
     def fuses_residual(self, m: int, n: int, k: int) -> bool:
-        return self.takes_tcgen05(m, n, k)
+        return self.few_rows_route(m, n, k, "residual") == "skinny" or self.takes_tcgen05(m, n, k)
 
 
 class PendingProduct:
@@ -152,7 +189,10 @@ class PendingProduct:
         from .. import kernels
         m, k = self.act.shape
         n = self.weight.shape[0]
-        if not self.runtime.fuses_residual(m, n, k):
+        if self.runtime.few_rows_route(m, n, k, "residual") == "skinny":
+            kernels.gemm_skinny(self.act, self.weight, x, kernels.TG_RESIDUAL, scale)
+            return True
+        if not self.runtime.takes_tcgen05(m, n, k):
             return False
         kernels.gemm_tcgen05(self.act, self.weight, x, kernels.TG_RESIDUAL, scale)
         return True

@@ -321,8 +321,13 @@ def test_attention_rows_over_pages(K, dtype, nh, nkvh, dh, page, window):
     _close(got, want, dtype, scale=2.0)
 
 
+# groups of more than four query heads with heads of 64 or 128: the decode kernel that puts the group on the
+# tensor cores (16 heads fill a tile; 20 need a second one; 5 and 6 leave most of it empty)
+GROUPED = [(32, 2, 128, 16, None), (10, 2, 64, 16, 70), (40, 2, 128, 8, None), (6, 1, 64, 32, 33), (7, 1, 128, 5, None)]
+
+
 @pytest.mark.parametrize("splits", [1, 2, 5, 32])
-@pytest.mark.parametrize("nh,nkvh,dh,page,window", SHAPES)
+@pytest.mark.parametrize("nh,nkvh,dh,page,window", SHAPES + GROUPED)
 def test_attention_decode_kernel_with_split_keys(K, nh, nkvh, dh, page, window, splits):
     lens = [37, 1, 300, 64, 2]
     queries = [list(range(30, 37)), [0], [299], [62, 63], [0, 1]]
@@ -355,10 +360,13 @@ def test_attention_prefill_kernel_on_tcgen05(K, nh, nkvh, dh, page, window):
 
 
 @pytest.mark.parametrize("impl,dtype", [("rows", torch.float32), ("rows", torch.bfloat16), ("decode", torch.bfloat16),
-                                         ("prefill", torch.bfloat16), ("tcgen05", torch.bfloat16)])
+                                         ("decode grouped", torch.bfloat16), ("prefill", torch.bfloat16),
+                                         ("tcgen05", torch.bfloat16)])
 @pytest.mark.parametrize("window", [None, 50])
 def test_attention_finds_one_far_key_among_hundreds(K, impl, dtype, window):
     nh, nkvh, dh, page = 4, 2, 64, 16
+    if impl == "decode grouped":                 # six query heads per key/value head: the tensor-core decode kernel
+        nh, impl = 12, "decode"
     lens = [700]
     # the query at 699 must find key 3 (or, with a window, the key at the window's far edge); the query
     # at 320 the key at 319, across a page's edge
@@ -371,14 +379,15 @@ def test_attention_finds_one_far_key_among_hundreds(K, impl, dtype, window):
     kw = dict(impl=impl, splits=3) if impl != "rows" else {}
     got, want, v = _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, plant, seed=5, **kw)
     _close(got, want, dtype, scale=2.0)
-    assert torch.allclose(got[i699, 1].float().cpu(), v[0][far, 0], atol=2e-2)
-    assert torch.allclose(got[i320, 2].float().cpu(), v[0][319, 1], atol=2e-2)
+    group = nh // nkvh
+    assert torch.allclose(got[i699, 1].float().cpu(), v[0][far, 1 // group], atol=2e-2)
+    assert torch.allclose(got[i320, 2].float().cpu(), v[0][319, 2 // group], atol=2e-2)
     if window:
         # one position beyond the window's edge must NOT be seen
         plant = [(0, 699, far - 1, 1)]
         got, want, v = _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, plant, seed=5, **kw)
         _close(got, want, dtype, scale=2.0)
-        assert not torch.allclose(got[i699, 1].float().cpu(), v[0][far - 1, 0], atol=0.2)
+        assert not torch.allclose(got[i699, 1].float().cpu(), v[0][far - 1, 1 // group], atol=0.2)
 
 
 @pytest.mark.parametrize("V", [5, 301, 122753])
@@ -529,6 +538,42 @@ def test_gemm_tcgen05_with_swiglu_epilogue(K, pairs, M, N, K_):
     K.check_gemm_status(DEV)
     gu = act.double() @ w.double().T
     _close(out, gu[:, :N] * torch.sigmoid(gu[:, :N]) * gu[:, N:], torch.bfloat16, scale=2.0)
+
+
+@pytest.mark.parametrize("M,N,K_", [(32, 128, 64), (17, 256, 512), (64, 520, 200), (1, 100, 72), (100, 333, 4096), (128, 1200, 2304),
+                                    (9, 77, 16384)])
+@pytest.mark.parametrize("epi", ["f32", "residual", "swiglu"])
+def test_gemm_of_few_rows_with_the_weights_on_the_m_side(K, M, N, K_, epi):
+    """jk_gemm_skinny: up to 128 rows, any width (ragged tiles of 128 features, 64 for SwiGLU), K with a tail and
+    long enough to be split among blocks whose partial sums meet in the output."""
+    g = torch.Generator().manual_seed(M + N + K_)
+    act = torch.randn(M, K_, generator=g).to(torch.bfloat16)
+    rows = 2 * N if epi == "swiglu" else N
+    w = (torch.randn(rows, K_, generator=g) * (2 if epi == "swiglu" else 1) / math.sqrt(K_)).to(torch.bfloat16)
+    ref = act.double() @ w.double().T
+    assert K.gemm_skinny_supports(M, N, K_) and not K.gemm_skinny_supports(129, N, K_) and not K.gemm_skinny_supports(M, N, 20)
+    if epi == "f32":
+        out = torch.full((M, N), 9.0, device=DEV)
+        K.gemm_skinny(act.to(DEV), w.to(DEV), out, K.TG_F32)
+        K.check_gemm_status(DEV)
+        torch.testing.assert_close(out.double().cpu(), ref, rtol=1e-4, atol=1e-4)
+    elif epi == "residual":
+        x = torch.randn(M, N, generator=g)
+        out = x.to(DEV).clone()
+        K.gemm_skinny(act.to(DEV), w.to(DEV), out, K.TG_RESIDUAL, scale=0.7)
+        K.check_gemm_status(DEV)
+        torch.testing.assert_close(out.double().cpu(), x.double() + 0.7 * ref, rtol=1e-4, atol=1e-4)
+    else:
+        out = torch.full((M, N), 9.0, dtype=torch.bfloat16, device=DEV)
+        K.gemm_skinny(act.to(DEV), w.to(DEV), out, K.TG_SWIGLU)
+        K.check_gemm_status(DEV)
+        _close(out, ref[:, :N] * torch.sigmoid(ref[:, :N]) * ref[:, N:], torch.bfloat16, scale=2.0)
+    # an output with padded rows
+    if epi == "f32":
+        wide = torch.full((M, N + 5), 9.0, device=DEV)
+        K.gemm_skinny(act.to(DEV), w.to(DEV), wide[:, :N], K.TG_F32)
+        torch.testing.assert_close(wide[:, :N].double().cpu(), ref, rtol=1e-4, atol=1e-4)
+        assert float(wide[:, N:].min()) == 9.0
 
 
 def test_gemm_tcgen05_refuses_rows_that_tma_cannot_address(K):

@@ -87,18 +87,21 @@ def test_whole_tail_and_portions_agree_with_the_plain_implementation(tiny_models
         assert not eng.cache.lengths and all(g.pool.in_use == 0 for g in eng.cache.groups)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_every_product_kernel_gives_the_same_model(tiny_models, name):
-    """The bfloat16 products have three homes: the tcgen05 kernel (many rows; here forced on for any
-    step of more than 16 rows), the weight-streaming kernel (few rows) and the library.  The model's
-    logits must not care."""
+    """The bfloat16 products have four homes: the tiled tcgen05 kernel (many rows; here forced on for any
+    step of more than 16 rows), the few-rows tcgen05 kernel with the weights on the MMA's M side (17 to 128
+    rows once it has a block per SM; here forced on for any size), the weight-streaming kernel (up to 16
+    rows) and the library.  The model's logits must not care."""
     toks, want = expected(tiny_models, name, 150, 120)
     steps = portions("r", toks, sizes=(70, 3, 33, 14))       # 70 and 33 rows: tcgen05; 3 and 14: weight streaming
-    for mode in ("tcgen05", "library"):
+    for mode in ("tcgen05", "few rows", "library"):
         eng = make_engine(tiny_models[name][0], "bfloat16", 256)
         if mode == "tcgen05":
             eng.runtime.tcgen05_min_tiles = 1
             eng.runtime.tcgen05_min_rows = 17
+        elif mode == "few rows":
+            eng.runtime.skinny_min_blocks = 1
         else:
             eng.runtime.library_products_only = True
         got = run(eng, steps)

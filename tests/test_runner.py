@@ -39,6 +39,28 @@ def test_native_runner_and_parts_give_the_same_logits(tiny_models, name):
     native.check()
 
 
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_runner_and_parts_route_few_rows_alike(tiny_models, name):
+    """With the few-rows tcgen05 kernel forced on for every size (a tiny model never has a block per SM), steps of
+    17 to 128 rows take it on both ways of running a step: o and down add into the residual stream from several
+    blocks that split K, gate/up applies SwiGLU, the logits are stored."""
+    folder = tiny_models[name][0]
+    native = make_engine(folder, "bfloat16", 1024)
+    parts = make_engine(folder, "bfloat16", 1024, native_runner=False)
+    native.runtime.skinny_min_blocks = parts.runtime.skinny_min_blocks = 1
+    toks, want = expected(tiny_models, name, 510, 180)
+    for what, steps in (("portions", portions("a", toks, sizes=(100, 17, 30, 5, 28))), ("tail", tail_decode("a", toks))):
+        got_n, got_p = run(native, steps), run(parts, steps)
+        scale = np.abs(want).max()
+        for key in got_n:
+            # partial sums of the blocks that split K are added in the order the blocks finish: rounding only
+            assert np.abs(got_n[key] - got_p[key]).max() <= 2e-3 * scale, (name, what, key)
+        check(got_n, "a", want, TOL["bfloat16"], f"{name} few rows {what}")
+        check(got_p, "a", want, TOL["bfloat16"], f"{name} few rows {what} (parts)")
+    native.check()
+    assert native.runner is not None and native.runner._model.skinny_min_blocks == 1
+
+
 def test_native_runner_leaves_other_models_to_the_parts(tiny_models):
     from infinicore_infer_b200.engine.runner import NativeRunner
     eng = make_engine(tiny_models["C"][0], "bfloat16", 256)          # hidden 80: outside the small-row kernels
