@@ -757,40 +757,71 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     const int ntiles = (k1 - k0 + GQ_KEYS - 1) / GQ_KEYS;
     const int *bt = a.block_table + (size_t)req * a.max_blocks;
 
-    // 16 bytes of key `key` of a tile lie at chunk ^ (key & 7): ldmatrix reads eight rows without conflicts
-    auto load_tile = [&](int i) {
-        uint4 *kd = gq_smem + (size_t)(i % GQ_STAGES) * 2 * TILE, *vd = kd + TILE;
-        const int kb = k0 + i * GQ_KEYS;
-#pragma unroll
-        for (int c = 0; c < TILE / 128; ++c) {
-            const int idx = c * 128 + threadIdx.x, key = idx / CH, ch = idx % CH;
-            const int kj = kb + key;
-            const bool valid = kj < k1;
-            size_t off = 0;
-            if (valid) {
-                const int page = bt[kj / a.page_size];
-                off = (((size_t)page * a.nkvh + kh) * a.page_size + kj % a.page_size) * DH + ch * 8;
-            }
-            const int slot = key * CH + (ch ^ (key & 7));
-            cp_async16_or_zero(kd + slot, a.k_pages + off, valid);
-            cp_async16_or_zero(vd + slot, a.v_pages + off, valid);
+    // Where a tile's 64 keys lie (element offset of the key's row in the pages, -1 beyond the range) is worked out
+    // once per tile by 64 threads into a table of two turns; the copies then cost a table read each.
+    long long *tab = reinterpret_cast<long long *>(gq_smem + (size_t)GQ_STAGES * 2 * TILE);       // [2][GQ_KEYS]
+    // in two halves: the read of the block table is issued at the start of an iteration and used at its end, so
+    // that the warp does not sit on it
+    auto locate_begin = [&](int i) -> int {
+        const int kj = k0 + i * GQ_KEYS + threadIdx.x;
+        return threadIdx.x < GQ_KEYS && kj < k1 ? bt[kj / a.page_size] : -1;
+    };
+    auto locate_end = [&](int i, int page) {
+        if (threadIdx.x < GQ_KEYS) {
+            const int kj = k0 + i * GQ_KEYS + threadIdx.x;
+            tab[(i & 1) * GQ_KEYS + threadIdx.x] =
+                page < 0 ? -1 : (((long long)page * a.nkvh + kh) * a.page_size + kj % a.page_size) * DH;
         }
     };
+    auto locate_tile = [&](int i) { locate_end(i, locate_begin(i)); };
+    // 16 bytes of key `key` of a tile lie at chunk ^ (key & 7): ldmatrix reads eight rows without conflicts.  A
+    // thread copies the same chunk of every (128 / CH)-th key, so its swizzled chunk never changes.
+    constexpr int KEYS_PER_PASS = 128 / CH;
+    const int my_key = threadIdx.x / CH, my_ch = threadIdx.x % CH;
+    const int my_slot = my_key * CH + (my_ch ^ (my_key & 7));
+    auto load_tile = [&](int i) {
+        uint4 *kd = gq_smem + (size_t)(i % GQ_STAGES) * 2 * TILE + my_slot, *vd = kd + TILE;
+        const long long *where = tab + (i & 1) * GQ_KEYS + my_key;
+#pragma unroll
+        for (int c = 0; c < GQ_KEYS / KEYS_PER_PASS; ++c) {
+            const long long off = where[c * KEYS_PER_PASS];
+            const bool valid = off >= 0;
+            const size_t src = valid ? (size_t)off + my_ch * 8 : 0;
+            cp_async16_or_zero(kd + c * KEYS_PER_PASS * CH, a.k_pages + src, valid);
+            cp_async16_or_zero(vd + c * KEYS_PER_PASS * CH, a.v_pages + src, valid);
+        }
+    };
+    locate_tile(0);
+    locate_tile(1);
+    __syncthreads();
+    {
+        // the queries of the group's heads are one contiguous piece of q; heads beyond the group read as zeros
+        uint4 *qs = gq_smem + (size_t)GQ_STAGES * 2 * TILE + 2 * GQ_KEYS * sizeof(long long) / sizeof(uint4);
+        const uint4 *qg = reinterpret_cast<const uint4 *>(a.q + ((size_t)t * a.nh + h0) * DH);
+        for (int idx = threadIdx.x; idx < GQ_HEADS * CH; idx += 128) {
+            const int head = idx / CH, ch = idx % CH;
+            cp_async16_or_zero(qs + head * CH + (ch ^ (head & 7)), head < heads ? qg + idx : qg, head < heads);
+        }
+    }
     for (int i = 0; i < GQ_STAGES - 1; ++i) {
         if (i < ntiles) load_tile(i);
         cp_async_commit();
     }
-    // the group's queries as A fragments: rows are heads (zero beyond the group), 16 dims per step
+    __syncthreads();                               // the first tables have been read
+    locate_tile(2);
+    // the group's queries as A fragments: rows are heads (zero beyond the group), 16 dims per step; they came
+    // with the first tile's group of copies into their own 16 x DH corner of shared memory
     unsigned qf[DH / 16][4];
     {
-        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
-        const __nv_bfloat16 *q0 = a.q + ((size_t)t * a.nh + h0 + r0) * DH, *q1 = q0 + (size_t)8 * DH;
+        cp_async_wait<GQ_STAGES - 2>();
+        __syncthreads();
+        const uint4 *qs = gq_smem + (size_t)GQ_STAGES * 2 * TILE + 2 * GQ_KEYS * sizeof(long long) / sizeof(uint4);
+        // matrices: (heads 0-7, dims 0-7), (heads 8-15, dims 0-7), (heads 0-7, dims 8-15), (heads 8-15, dims 8-15)
+        const int head = (((lane >> 3) & 1) << 3) + (lane & 7);
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
-            qf[kk][0] = r0 < heads ? *reinterpret_cast<const unsigned *>(q0 + kk * 16 + c0) : 0u;
-            qf[kk][1] = r0 + 8 < heads ? *reinterpret_cast<const unsigned *>(q1 + kk * 16 + c0) : 0u;
-            qf[kk][2] = r0 < heads ? *reinterpret_cast<const unsigned *>(q0 + kk * 16 + 8 + c0) : 0u;
-            qf[kk][3] = r0 + 8 < heads ? *reinterpret_cast<const unsigned *>(q1 + kk * 16 + 8 + c0) : 0u;
+            const int ch = kk * 2 + (lane >> 4);
+            ldmatrix_x4(qf[kk], qs + head * CH + (ch ^ (head & 7)));
         }
     }
     float o[DH / 8][4];
@@ -801,20 +832,33 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     for (int i = 0; i < ntiles; ++i) {
         cp_async_wait<GQ_STAGES - 2>();
         __syncthreads();                           // tile i has landed for everyone; tile i - 1 is no longer read
+        const int page_ahead = locate_begin(i + GQ_STAGES);
         if (i + GQ_STAGES - 1 < ntiles) load_tile(i + GQ_STAGES - 1);
         cp_async_commit();
         const uint4 *kt = gq_smem + (size_t)(i % GQ_STAGES) * 2 * TILE, *vt = kt + TILE;
         const int kw = k0 + i * GQ_KEYS + warp * 16;          // this warp's first key of the tile
-        if (kw >= k1) continue;                                // warp-uniform: no key of the tile is this warp's
+        if (kw >= k1) {                                        // warp-uniform: no key of the tile is this warp's
+            locate_end(i + GQ_STAGES, page_ahead);
+            continue;
+        }
         float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+            float sd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};      // odd steps: two chains of half the length
+            const int key = warp * 16 + ((lane >> 4) << 3) + (lane & 7);
+            const uint4 *krow = kt + key * CH;
 #pragma unroll
-        for (int kk = 0; kk < DH / 16; ++kk) {
-            // matrices: (keys 0-7, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, dims 0-7), (keys 8-15, dims 8-15)
-            const int key = warp * 16 + ((lane >> 4) << 3) + (lane & 7), ch = kk * 2 + ((lane >> 3) & 1);
-            unsigned b[4];
-            ldmatrix_x4(b, kt + key * CH + (ch ^ (key & 7)));
-            mma_bf16(sc[0], qf[kk], b[0], b[1]);
-            mma_bf16(sc[1], qf[kk], b[2], b[3]);
+            for (int kk = 0; kk < DH / 16; ++kk) {
+                // matrices: (keys 0-7, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, dims 0-7), (keys 8-15, dims 8-15)
+                const int ch = kk * 2 + ((lane >> 3) & 1);
+                unsigned b[4];
+                ldmatrix_x4(b, krow + (ch ^ (key & 7)));
+                mma_bf16(kk & 1 ? sd[0] : sc[0], qf[kk], b[0], b[1]);
+                mma_bf16(kk & 1 ? sd[1] : sc[1], qf[kk], b[2], b[3]);
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[j][e] += sd[j][e];
         }
         // scores in the log2 domain; keys beyond the range count as minus infinity
         float t0 = -INFINITY, t1 = -INFINITY;
@@ -845,8 +889,10 @@ attention_decode_gqa_kernel(DecodeArgs a) {
         l1 = l1 * c1 + p[0][2] + p[0][3] + p[1][2] + p[1][3];
         pa[0] = pack_bf16(p[0][0], p[0][1]); pa[1] = pack_bf16(p[0][2], p[0][3]);
         pa[2] = pack_bf16(p[1][0], p[1][1]); pa[3] = pack_bf16(p[1][2], p[1][3]);
+        if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {           // a maximum moved: seldom after the first tiles
 #pragma unroll
-        for (int n = 0; n < DH / 8; ++n) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+            for (int n = 0; n < DH / 8; ++n) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+        }
 #pragma unroll
         for (int d2 = 0; d2 < DH / 16; ++d2) {
             // transposed: (keys 0-7, dims 16 d2 ..+7), (keys 8-15, same dims), (keys 0-7, dims +8..+15), (keys 8-15, ...)
@@ -856,23 +902,27 @@ attention_decode_gqa_kernel(DecodeArgs a) {
             mma_bf16(o[2 * d2], pa, b[0], b[1]);
             mma_bf16(o[2 * d2 + 1], pa, b[2], b[3]);
         }
+        locate_end(i + GQ_STAGES, page_ahead);     // into the table that the copies of tile i + 1 have read
     }
     cp_async_wait<0>();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     __syncthreads();                               // the ring is free: it carries the four warps' results
-    float *red = reinterpret_cast<float *>(gq_smem);           // [warp][head][DH + 2]
+    // [warp][head][DH + 8]: the accumulator, then maximum and sum; with this stride the 8-byte stores of a half warp
+    // (four heads, dims 0..7) fall into 32 different banks
+    constexpr int RS = DH + 8;
+    float *red = reinterpret_cast<float *>(gq_smem);
     {
-        float *mine = red + (size_t)warp * GQ_HEADS * (DH + 2);
+        float *mine = red + (size_t)warp * GQ_HEADS * RS;
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
 #pragma unroll
         for (int n = 0; n < DH / 8; ++n) {
-            mine[r0 * (DH + 2) + n * 8 + c0] = o[n][0]; mine[r0 * (DH + 2) + n * 8 + c0 + 1] = o[n][1];
-            mine[(r0 + 8) * (DH + 2) + n * 8 + c0] = o[n][2]; mine[(r0 + 8) * (DH + 2) + n * 8 + c0 + 1] = o[n][3];
+            *reinterpret_cast<float2 *>(mine + r0 * RS + n * 8 + c0) = make_float2(o[n][0], o[n][1]);
+            *reinterpret_cast<float2 *>(mine + (r0 + 8) * RS + n * 8 + c0) = make_float2(o[n][2], o[n][3]);
         }
         if ((lane & 3) == 0) {
-            mine[r0 * (DH + 2) + DH] = m0; mine[r0 * (DH + 2) + DH + 1] = l0;
-            mine[(r0 + 8) * (DH + 2) + DH] = m1; mine[(r0 + 8) * (DH + 2) + DH + 1] = l1;
+            *reinterpret_cast<float2 *>(mine + r0 * RS + DH) = make_float2(m0, l0);
+            *reinterpret_cast<float2 *>(mine + (r0 + 8) * RS + DH) = make_float2(m1, l1);
         }
     }
     __syncthreads();
@@ -880,11 +930,11 @@ attention_decode_gqa_kernel(DecodeArgs a) {
         const int r = idx / DH, e = idx % DH;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, red[((size_t)w * GQ_HEADS + r) * (DH + 2) + DH]);
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, red[((size_t)w * GQ_HEADS + r) * RS + DH]);
         float L = 0.f, A = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float *src = red + ((size_t)w * GQ_HEADS + r) * (DH + 2);
+            const float *src = red + ((size_t)w * GQ_HEADS + r) * RS;
             const float f = fast_exp2(src[DH] - M);             // a warp without keys: 2^-inf = 0
             L += f * src[DH + 1];
             A += f * src[e];
@@ -902,8 +952,9 @@ attention_decode_gqa_kernel(DecodeArgs a) {
 template <int DH>
 static int launch_decode_gqa(const DecodeArgs &a, cudaStream_t stream) {
     const int g = a.nh / a.nkvh;
-    const size_t ring = (size_t)GQ_STAGES * 2 * GQ_KEYS * DH * sizeof(__nv_bfloat16);
-    const size_t merge = (size_t)4 * GQ_HEADS * (DH + 2) * sizeof(float);
+    const size_t ring = (size_t)GQ_STAGES * 2 * GQ_KEYS * DH * sizeof(__nv_bfloat16) + 2 * GQ_KEYS * sizeof(long long)
+                        + (size_t)GQ_HEADS * DH * sizeof(__nv_bfloat16);       // tiles, the two tables, the queries
+    const size_t merge = (size_t)4 * GQ_HEADS * (DH + 8) * sizeof(float);
     const size_t smem = ring > merge ? ring : merge;
     cudaError_t e = cudaFuncSetAttribute(attention_decode_gqa_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_decode: %s", cudaGetErrorString(e));
