@@ -220,9 +220,9 @@ bool tcgen05_attention_takes(int dh, int page) {
 // How many ways the decode kernel cuts each row's key range: full waves of blocks (three fit an SM)
 // against a block's fixed cost of about 128 keys' worth of time, at half the longest context.
 int decode_splits(int nrows, int nkvh, int group, int max_positions, int sms) {
-    // groups of more than four query heads run on the tensor-core kernel: 16 heads and two blocks an SM
-    const long long blocks = std::max(1, nrows * nkvh * (group > 4 ? (group + 15) / 16 : 1));
-    const long long slots = (long long)sms * (group > 4 ? 2 : 3);
+    // grouped heads run on the tensor-core kernel: up to 16 heads a block, two blocks an SM
+    const long long blocks = std::max(1, nrows * nkvh * ((group + 15) / 16));
+    const long long slots = (long long)sms * (group > 1 ? 2 : 3);
     const double keys = std::max(1, max_positions / 2);
     int best = 1;
     double best_cost = -1;

@@ -376,9 +376,9 @@ def attention_decode_splits(nrows: int, nkvh: int, group: int, max_positions: in
     full waves of blocks (a last wave that is nearly empty costs as much as a full one) against the
     fixed cost of a block (about 128 keys' worth of time for set-up and the merge of its groups), at
     half the longest context."""
-    # groups of more than four query heads run on the tensor-core kernel: 16 heads and two blocks an SM
-    blocks = max(1, nrows * nkvh * ((group + 15) // 16 if group > 4 else 1))
-    slots = sms * (2 if group > 4 else 3)
+    # grouped heads run on the tensor-core kernel: up to 16 heads a block, two blocks an SM
+    blocks = max(1, nrows * nkvh * ((group + 15) // 16))
+    slots = sms * (2 if group > 1 else 3)
     keys = max(1, max_positions // 2)
     best, best_cost = 1, None
     for s in range(1, 33):

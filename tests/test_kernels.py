@@ -321,9 +321,10 @@ def test_attention_rows_over_pages(K, dtype, nh, nkvh, dh, page, window):
     _close(got, want, dtype, scale=2.0)
 
 
-# groups of more than four query heads with heads of 64 or 128: the decode kernel that puts the group on the
-# tensor cores (16 heads fill a tile; 20 need a second one; 5 and 6 leave most of it empty)
-GROUPED = [(32, 2, 128, 16, None), (10, 2, 64, 16, 70), (40, 2, 128, 8, None), (6, 1, 64, 32, 33), (7, 1, 128, 5, None)]
+# grouped heads of 64 or 128: the decode kernel that puts the group on the tensor cores (16 heads fill a tile;
+# 20 need a second one; 2 to 7 leave most of it empty)
+GROUPED = [(32, 2, 128, 16, None), (10, 2, 64, 16, 70), (40, 2, 128, 8, None), (6, 1, 64, 32, 33), (7, 1, 128, 5, None),
+           (6, 3, 64, 16, None), (24, 8, 64, 16, 100)]
 
 
 @pytest.mark.parametrize("splits", [1, 2, 5, 32])
@@ -365,7 +366,7 @@ def test_attention_prefill_kernel_on_tcgen05(K, nh, nkvh, dh, page, window):
 @pytest.mark.parametrize("window", [None, 50])
 def test_attention_finds_one_far_key_among_hundreds(K, impl, dtype, window):
     nh, nkvh, dh, page = 4, 2, 64, 16
-    if impl == "decode grouped":                 # six query heads per key/value head: the tensor-core decode kernel
+    if impl == "decode grouped":                 # six query heads per key/value head instead of two
         nh, impl = 12, "decode"
     lens = [700]
     # the query at 699 must find key 3 (or, with a window, the key at the window's far edge); the query
