@@ -968,12 +968,12 @@ static int launch_decode_gqa(const DecodeArgs &a, cudaStream_t stream) {
     return JK_OK;
 }
 
-// Grouped heads (two or more query heads per key/value head; JK_GQA_MIN_GROUP moves the limit) with a head size of
-// 64 or 128 go to the tensor-core decode kernel, which reads keys and values once per group: measured 1.4 to 2 times
-// faster than the kernel of the CUDA cores at groups of 2 to 4, five times at 16.  Everything else stays there.
+// Head sizes 64 and 128 go to the tensor-core decode kernel, which reads keys and values once per group of query
+// heads: measured against the kernel of the CUDA cores it is 1.1 times as fast without groups, 1.4 to 2 times at groups
+// of 2 to 4 and five times at 16 (JK_GQA_MIN_GROUP=n keeps groups below n on the old kernel).  Other head sizes stay there.
 static int decode_gqa(const DecodeArgs &a, cudaStream_t stream, bool *taken) {
     *taken = true;
-    static const int min_group = [] { const char *v = getenv("JK_GQA_MIN_GROUP"); return v ? atoi(v) : 2; }();
+    static const int min_group = [] { const char *v = getenv("JK_GQA_MIN_GROUP"); return v ? atoi(v) : 1; }();
     if (a.nh / a.nkvh >= min_group) {
         switch (a.dh) {
             case 64: return launch_decode_gqa<64>(a, stream);       // rows of 8 or 16 chunks: what the swizzle takes

@@ -217,19 +217,28 @@ bool tcgen05_attention_takes(int dh, int page) {
     return (dh == 64 || dh == 128) && (page == 8 || page == 16 || page == 32 || page == 64 || page == 128);
 }
 
-// How many ways the decode kernel cuts each row's key range: full waves of blocks (three fit an SM)
-// against a block's fixed cost of about 128 keys' worth of time, at half the longest context.
-int decode_splits(int nrows, int nkvh, int group, int max_positions, int sms) {
-    // grouped heads run on the tensor-core kernel: up to 16 heads a block, two blocks an SM
-    const long long blocks = std::max(1, nrows * nkvh * ((group + 15) / 16));
-    const long long slots = (long long)sms * (group > 1 ? 2 : 3);
-    const double keys = std::max(1, max_positions / 2);
+// How many ways the decode kernels cut each row's key range (the same rule as kernels.attention_decode_splits of
+// the Python side).  Head sizes 64 and 128, the tensor-core kernel: cut until the blocks nearly fill the SMs (two
+// blocks an SM) as long as a block keeps 256 keys, then up to two rounds of blocks as long as it keeps 1024.  Other
+// head sizes: full waves of blocks (three an SM) against a block's fixed cost of about 128 keys' worth of time.
+int decode_splits(int nrows, int nkvh, int group, int max_positions, int sms, int dh) {
+    const int keys = std::max(1, max_positions / 2);
+    if (dh == 64 || dh == 128) {
+        const long long blocks = std::max(1, nrows * nkvh * ((group + 15) / 16));
+        const long long slots = 2LL * sms;
+        int s = 1;
+        while (blocks * s < 0.85 * slots && keys / (s + 1) >= 256 && s < 32) ++s;
+        while (blocks * (s + 1) <= 2 * slots && keys / (s + 1) >= 1024 && s < 32) ++s;
+        return s;
+    }
+    const long long blocks = std::max(1, nrows * nkvh * (group > 4 ? (group + 3) / 4 : 1));
+    const long long slots = (long long)sms * 3;
     int best = 1;
     double best_cost = -1;
     for (int s = 1; s <= 32; ++s) {
-        if (s > 1 && keys / s < 64) break;
+        if (s > 1 && (double)keys / s < 64) break;
         const long long waves = (blocks * s + slots - 1) / slots;
-        const double cost = waves * (128 + keys / s);
+        const double cost = waves * (128 + (double)keys / s);
         if (best_cost < 0 || cost < best_cost * 0.97) best = s, best_cost = cost;
     }
     return best;
@@ -451,7 +460,7 @@ int run_batch(JkModel *m, const uint32_t *tokens, uint32_t ntok, const uint32_t 
 
     int splits = 1;
     if (n_short) {
-        splits = decode_splits(n_short, m->meta.nkvh, m->meta.nh / m->meta.nkvh, m->meta.dctx, m->rm.sms);
+        splits = decode_splits(n_short, m->meta.nkvh, m->meta.nh / m->meta.nkvh, m->meta.dctx, m->rm.sms, m->meta.dh);
         const long long need = splits > 1 ? (long long)n_short * m->meta.nh * splits * (m->meta.dh + 2) : 0;
         if (int rc = grow(m, (void **)&m->decode_scratch, &m->decode_floats, need, sizeof(float), "batch: attention scratch")) return rc;
         m->scratch.decode_scratch = m->decode_scratch;

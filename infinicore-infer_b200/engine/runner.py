@@ -241,7 +241,8 @@ class NativeRunner:
             raise kernels.KernelError(f"the native runner holds buffers for {self.max_step_tokens} rows, the step has {T}")
         splits = 1
         if ctx.n_short:
-            splits = kernels.attention_decode_splits(ctx.n_short, nkvh, nh // nkvh, self._model.window or self._max_positions)
+            splits = kernels.attention_decode_splits(ctx.n_short, nkvh, nh // nkvh, self._model.window or self._max_positions,
+                                                     kernels._sm_count(rt.device), dh)
             need = self._attn_lib.jk_attention_decode_scratch_floats(ctypes.c_int(ctx.n_short), ctypes.c_int(nh), ctypes.c_int(dh),
                                                                      ctypes.c_int(splits))
             if need > self._decode_scratch.numel():

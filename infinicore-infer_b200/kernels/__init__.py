@@ -370,16 +370,31 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
     return out
 
 
-def attention_decode_splits(nrows: int, nkvh: int, group: int, max_positions: int, sms: int = 148) -> int:
-    """How many ways the decode kernel cuts each row's key range.  It depends on the batch's size only
-    (not on the lengths), so a captured step keeps its grid.  Three blocks fit an SM; the choice weighs
-    full waves of blocks (a last wave that is nearly empty costs as much as a full one) against the
-    fixed cost of a block (about 128 keys' worth of time for set-up and the merge of its groups), at
-    half the longest context."""
-    # grouped heads run on the tensor-core kernel: up to 16 heads a block, two blocks an SM
-    blocks = max(1, nrows * nkvh * ((group + 15) // 16))
-    slots = sms * (2 if group > 1 else 3)
+def attention_decode_splits(nrows: int, nkvh: int, group: int, max_positions: int, sms: int = 148,
+                            dh: Optional[int] = None) -> int:
+    """How many ways the decode kernels cut each row's key range.  It depends on the batch's size only
+    (not on the lengths), so a captured step keeps its grid; half the longest context stands for the lengths.
+
+    Head sizes 64 and 128 (the tensor-core kernel: a block per row, key/value head and up to 16 query heads,
+    two blocks an SM), from measurements on the 1B, 2B and 8B shapes: cut until the blocks nearly fill the
+    SMs, as long as a block keeps 256 keys; then further, up to two rounds of blocks, as long as a block
+    keeps 1024 keys (a block's fixed part costs about as much as a few hundred keys, and blocks that all
+    start and end together read slower than blocks that overlap).
+
+    Other head sizes (the kernel of the CUDA cores, three blocks an SM): the choice weighs full waves of
+    blocks against a block's fixed cost of about 128 keys' worth of time."""
     keys = max(1, max_positions // 2)
+    if dh in (64, 128):
+        blocks = max(1, nrows * nkvh * ((group + 15) // 16))
+        slots = 2 * sms
+        s = 1
+        while blocks * s < 0.85 * slots and keys // (s + 1) >= 256 and s < 32:
+            s += 1
+        while blocks * (s + 1) <= 2 * slots and keys // (s + 1) >= 1024 and s < 32:
+            s += 1
+        return s
+    blocks = max(1, nrows * nkvh * ((group + 3) // 4 if group > 4 else 1))
+    slots = sms * 3
     best, best_cost = 1, None
     for s in range(1, 33):
         if s > 1 and keys / s < 64:

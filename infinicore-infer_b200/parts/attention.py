@@ -103,6 +103,7 @@ class Attention:
                                           ctx.req_pos, table, s.num_heads, s.softmax_scale, s.window or 0)
         if ctx.n_short:
             splits = kernels.attention_decode_splits(ctx.n_short, s.num_kv_heads, s.num_heads // s.num_kv_heads,
-                                                     s.window or (s.position.max_positions if s.position else 1 << 20))
+                                                     s.window or (s.position.max_positions if s.position else 1 << 20),
+                                                     kernels._sm_count(q.device), s.head_dim)
             kernels.attention_decode(q, view.k_pages, view.v_pages, o, ctx.short_rows, ctx.n_short, ctx.positions,
                                      ctx.row_req, table, s.num_heads, s.softmax_scale, s.window or 0, splits)
