@@ -744,7 +744,9 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     const int pos = a.positions[t], req = a.row_req[t];
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0, hi = pos + 1;
     const int tiles_all = (hi - lo + GQ_KEYS - 1) / GQ_KEYS;
-    const int per = (tiles_all + a.splits - 1) / a.splits;
+    // at least two tiles per split (a block's fixed part costs more than a tile): short contexts use fewer of the
+    // splits that the grid was sized for, the others report that they saw nothing
+    const int per = max(2, (tiles_all + a.splits - 1) / a.splits);
     const int k0 = lo + split * per * GQ_KEYS, k1 = min(hi, k0 + per * GQ_KEYS);
     const size_t pbase = ((size_t)ri * a.nh + h0) * a.splits + split;      // + head * splits
     if (k0 >= k1) {                                // nothing for this split: the merge skips it

@@ -218,18 +218,17 @@ bool tcgen05_attention_takes(int dh, int page) {
 }
 
 // How many ways the decode kernels cut each row's key range (the same rule as kernels.attention_decode_splits of
-// the Python side).  Head sizes 64 and 128, the tensor-core kernel: cut until the blocks nearly fill the SMs (two
-// blocks an SM) as long as a block keeps 256 keys, then up to two rounds of blocks as long as it keeps 1024.  Other
+// the Python side).  Head sizes 64 and 128, the tensor-core kernel: as many cuts as make the blocks fill the SMs once
+// (two blocks an SM, rounded) as long as a block keeps 256 keys, then up to two rounds of blocks as long as it keeps 1024.  Other
 // head sizes: full waves of blocks (three an SM) against a block's fixed cost of about 128 keys' worth of time.
 int decode_splits(int nrows, int nkvh, int group, int max_positions, int sms, int dh) {
     const int keys = std::max(1, max_positions / 2);
     if (dh == 64 || dh == 128) {
         const long long blocks = std::max(1, nrows * nkvh * ((group + 15) / 16));
         const long long slots = 2LL * sms;
-        int s = 1;
-        while (blocks * s < 0.85 * slots && keys / (s + 1) >= 256 && s < 32) ++s;
+        long long s = std::max(1LL, std::min({(2 * slots + blocks) / (2 * blocks), (long long)keys / 256, 32LL}));      // slots / blocks, rounded
         while (blocks * (s + 1) <= 2 * slots && keys / (s + 1) >= 1024 && s < 32) ++s;
-        return s;
+        return (int)s;
     }
     const long long blocks = std::max(1, nrows * nkvh * (group > 4 ? (group + 3) / 4 : 1));
     const long long slots = (long long)sms * 3;

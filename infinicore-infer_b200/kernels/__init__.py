@@ -376,8 +376,8 @@ def attention_decode_splits(nrows: int, nkvh: int, group: int, max_positions: in
     (not on the lengths), so a captured step keeps its grid; half the longest context stands for the lengths.
 
     Head sizes 64 and 128 (the tensor-core kernel: a block per row, key/value head and up to 16 query heads,
-    two blocks an SM), from measurements on the 1B, 2B and 8B shapes: cut until the blocks nearly fill the
-    SMs, as long as a block keeps 256 keys; then further, up to two rounds of blocks, as long as a block
+    two blocks an SM), from measurements on the 1B, 2B and 8B shapes: as many cuts as make the blocks fill the
+    SMs once (rounded), as long as a block keeps 256 keys; then further, up to two rounds of blocks, as long as a block
     keeps 1024 keys (a block's fixed part costs about as much as a few hundred keys, and blocks that all
     start and end together read slower than blocks that overlap).
 
@@ -387,9 +387,7 @@ def attention_decode_splits(nrows: int, nkvh: int, group: int, max_positions: in
     if dh in (64, 128):
         blocks = max(1, nrows * nkvh * ((group + 15) // 16))
         slots = 2 * sms
-        s = 1
-        while blocks * s < 0.85 * slots and keys // (s + 1) >= 256 and s < 32:
-            s += 1
+        s = max(1, min((2 * slots + blocks) // (2 * blocks), keys // 256, 32))     # slots / blocks, rounded
         while blocks * (s + 1) <= 2 * slots and keys // (s + 1) >= 1024 and s < 32:
             s += 1
         return s
