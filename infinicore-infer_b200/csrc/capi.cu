@@ -175,6 +175,9 @@ int bind_from_directory(JkModel *m, const char *dir, bool need_gemm_tcgen05, boo
     f.linear_small_supports = (SupportsFn)sym(ls, "jk_linear_small_supports");
     f.linear_small_qkv_supports = (SupportsFn)sym(ls, "jk_linear_small_qkv_supports");
     f.gemm_skinny = (GemmTcgen05Fn)sym(gt, "jk_gemm_skinny");
+    f.linear_small_norm_supports = (SupportsFn)sym(ls, "jk_linear_small_norm_supports");
+    f.linear_small_norm = (LinearSmallNormFn)sym(ls, "jk_linear_small_norm");
+    f.linear_small_qkv_norm = (LinearSmallQkvNormFn)sym(ls, "jk_linear_small_qkv_norm");
     f.gemm_tcgen05 = (GemmTcgen05Fn)sym(gt, "jk_gemm_tcgen05");
     f.gemm_tcgen05_qkv = (GemmTcgen05QkvFn)sym(gt, "jk_gemm_tcgen05_qkv");
     f.attention_decode = (AttentionDecodeFn)sym(at, "jk_attention_decode");
@@ -288,6 +291,7 @@ int create(JkModel *m, const JkModelMeta *meta, const JkModelWeights *w, const J
     rm.tcgen05_min_rows = 1024;      // below this many rows the library's product is faster (measured), but for very wide outputs
     rm.tcgen05_min_tiles = 96;
     rm.attention_tcgen05 = tcgen05_attention_takes(dh, m->page_size);
+    rm.fused_norms = getenv("JK_NO_FUSED_NORM") == nullptr || getenv("JK_NO_FUSED_NORM")[0] != '1';
     rm.embed_dtype = JK_BF16;
     rm.embed_scale = meta->embed_scale; rm.residual_scale = meta->residual_scale; rm.logit_scale = meta->logit_scale;
     rm.softmax_scale = 1.f / std::sqrt((float)dh);
@@ -356,6 +360,8 @@ int create(JkModel *m, const JkModelMeta *meta, const JkModelWeights *w, const J
     if (int rc = device_alloc(m, &s.hw, T * d * 2, "hw")) return rc;
     if (int rc = device_alloc(m, &s.workspace, WORKSPACE_BYTES, "workspace")) return rc;
     s.workspace_bytes = WORKSPACE_BYTES;
+    if (int rc = device_alloc(m, &p, sizeof(unsigned long long) * 2 * L * 16, "sums of squares")) return rc;
+    s.sumsq = (unsigned long long *)p;
     m->max_requests = m->max_step_tokens;
     m->meta_words = MetaLayout(m->max_step_tokens, m->max_requests, m->max_blocks).total;
     CUDA_TRY(cudaMallocHost((void **)&m->meta_host, sizeof(int) * m->meta_words), "pinned metadata");

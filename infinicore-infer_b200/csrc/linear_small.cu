@@ -24,7 +24,23 @@
 
 JK_DEFINE_ERROR_BUFFER(jk_linear_small)
 
-enum { EPI_F32 = 0, EPI_SWIGLU = 1, EPI_QKV = 2 };
+enum { EPI_F32 = 0, EPI_SWIGLU = 1, EPI_QKV = 2, EPI_RESIDUAL = 3 };
+
+// RMSNorm without a kernel of its own, for a chain of few-row products (decode steps).  The product before a norm
+// (EPI_RESIDUAL) adds itself into the float32 residual stream, writes bfloat16(x * next norm's weight) as the next
+// product's activations and adds its tile's share of sum(x^2) per row to a counter; the product after the norm reads
+// those activations as they are and multiplies its accumulators by 1 / sqrt(sum / K + eps) per row before its own
+// epilogue.  The counter is a 64-bit fixed-point number (26 fractional bits): integer additions give the same sum
+// in whatever order the tiles arrive, so a step's results do not vary from run to run.
+constexpr float SUMSQ_TO_FIXED = 67108864.f, SUMSQ_FROM_FIXED = 1.f / 67108864.f;
+struct SmallNormFuse {
+    const unsigned long long *in_sumsq;   // [M] of the activation rows, or null: no scaling
+    float in_eps;
+    __nv_bfloat16 *xb;                    // EPI_RESIDUAL: [M, N] activations for the next product, or null
+    const float *next_w;                  // [N] the next norm's weight
+    unsigned long long *out_sumsq;        // [M], or null
+    float scale;                          // x += scale * product
+};
 
 // EPI_QKV: where the fused [q | k | v] projection's columns go (bfloat16 all).
 struct SmallQkvDest {
@@ -45,6 +61,7 @@ struct SmallLinearArgs {
     void *out;                  // EPI_F32: float [M, ldo]; EPI_SWIGLU: bfloat16 [M, ldo]
     int M, N, K, ldo, ksplit, n_units;
     SmallQkvDest qkv;           // EPI_QKV only
+    SmallNormFuse norm;         // the tile kernel only
 };
 
 constexpr int SL_MAX_WARPS = 8;
@@ -268,6 +285,32 @@ small_linear_tile_kernel(SmallLinearArgs a) {
     for (int j = (per_slice + per_group - 1) / per_group; j < ST_GROUPS; ++j) cp_async_commit();
     pdl_wait();          // the weights do not depend on the kernel before this one; the activations do
 
+    // what the epilogue of the first warp needs from memory is asked for now, so that it has arrived by then
+    float pre_ss[MT][2], pre_x[MT][4], pre_w[2];
+    if (warp == 0) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int row = m * 8 + 2 * t + j;
+                pre_ss[m][j] = a.norm.in_sumsq != nullptr && row < a.M ? __ull2float_rn(a.norm.in_sumsq[row]) * SUMSQ_FROM_FIXED : 0.f;
+            }
+        if (EPI == EPI_RESIDUAL) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int n = n0 + g + h * 8;
+                pre_w[h] = a.norm.next_w != nullptr && n < a.N ? a.norm.next_w[n] : 0.f;
+            }
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int row = m * 8 + 2 * t + (c & 1), n = n0 + g + (c >> 1) * 8;
+                    pre_x[m][c] = n < a.N && row < a.M ? reinterpret_cast<const float *>(a.out)[(size_t)row * a.ldo + n] : 0.f;
+                }
+        }
+    }
+
     const __nv_bfloat16 *ap[MT];
     bool arow[MT];
 #pragma unroll
@@ -325,7 +368,46 @@ small_linear_tile_kernel(SmallLinearArgs a) {
                     for (int c = 0; c < 4; ++c) acc[m][c] += red_s[((s * MT + m) * 4 + c) * 32 + lane];
         }
     }
-    if (warp == 0 && EPI == EPI_QKV) {
+    if (warp == 0 && a.norm.in_sumsq != nullptr) {
+        // the activations came without their norm's 1 / rms: it is a factor of the whole row of the product
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float inv = rsqrtf(pre_ss[m][j] / (float)a.K + a.norm.in_eps);
+                acc[m][j] *= inv;
+                acc[m][j + 2] *= inv;
+            }
+    }
+    if (warp == 0 && EPI == EPI_RESIDUAL) {
+        // element c of tile m: feature n0 + g (+8 for c >= 2), activation row m*8 + 2t + (c & 1)
+        float *x = reinterpret_cast<float *>(a.out);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float ss[2] = {0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int row = m * 8 + 2 * t + (c & 1), n = n0 + g + (c >> 1) * 8;
+                if (n < a.N && row < a.M) {
+                    const float v = pre_x[m][c] + a.norm.scale * acc[m][c];
+                    x[(size_t)row * a.ldo + n] = v;
+                    if (a.norm.xb != nullptr) a.norm.xb[(size_t)row * a.N + n] = __float2bfloat16_rn(v * pre_w[c >> 1]);
+                    ss[c & 1] += v * v;
+                }
+            }
+            if (a.norm.out_sumsq != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    float v = ss[j];                                     // over the eight lanes that share t
+                    v += __shfl_xor_sync(0xffffffffu, v, 4);
+                    v += __shfl_xor_sync(0xffffffffu, v, 8);
+                    v += __shfl_xor_sync(0xffffffffu, v, 16);
+                    const int row = m * 8 + 2 * t + j;
+                    if (g == 0 && row < a.M) atomicAdd(a.norm.out_sumsq + row, __float2ull_rn(v * SUMSQ_TO_FIXED));
+                }
+            }
+        }
+    } else if (warp == 0 && EPI == EPI_QKV) {
         const SmallQkvDest &d = a.qkv;
         const int half = d.dh / 2, j = qkv_j0 + g, h = qkv_head;
 #pragma unroll
@@ -419,6 +501,10 @@ static int launch_small(const SmallLinearArgs &a, int ctas, int warps, size_t sm
 JK_EXPORT int jk_linear_small_supports(int M, int N, int K) {
     if (M < 1 || M > 16 || N < 1 || K < 32 || K % 32) return 0;
     const int MT = M <= 8 ? 1 : 2;
+    // the tile kernel (a 16-row tile of W in shared memory) or the ring kernel (the activations in shared memory)
+    int ksplit = ST_MAX_WARPS;
+    while (ksplit > 1 && (K / 32) / ksplit < 2) ksplit /= 2;
+    if (small_tile_smem(K, MT, ksplit) <= 200 * 1024) return 1;
     return small_linear_smem(K, MT, 8, small_linear_ring(K, MT, 8)) <= 200 * 1024;
 }
 
@@ -431,10 +517,10 @@ JK_EXPORT int jk_linear_small_qkv_supports(int M, int K, int dh) {
     return small_tile_smem(K, M <= 8 ? 1 : 2, ksplit) <= 200 * 1024;
 }
 
-JK_EXPORT int jk_linear_small_qkv(const void *act, const void *w, int M, int K, void *q_out, void *k_pages, void *v_pages,
-                                  const float *cos_table, const float *sin_table, const int *positions,
-                                  const int *row_req, const int *block_table, int max_blocks, int page_size, int nh,
-                                  int nkvh, int dh, int sms, cudaStream_t stream) {
+static int linear_small_qkv_impl(const void *act, const void *w, int M, int K, void *q_out, void *k_pages, void *v_pages,
+                                 const float *cos_table, const float *sin_table, const int *positions,
+                                 const int *row_req, const int *block_table, int max_blocks, int page_size, int nh,
+                                 int nkvh, int dh, int sms, const SmallNormFuse &norm, cudaStream_t stream) {
     JK_REQUIRE(jk_linear_small_qkv_supports(M, K, dh), "linear_small_qkv: M %d K %d head size %d is outside what the kernel takes", M, K, dh);
     JK_REQUIRE(nh >= 1 && nkvh >= 1 && q_out && k_pages && v_pages && positions && row_req && block_table && max_blocks > 0 && page_size > 0,
                "linear_small_qkv: a destination or index array is missing");
@@ -447,16 +533,54 @@ JK_EXPORT int jk_linear_small_qkv(const void *act, const void *w, int M, int K, 
     const size_t smem = small_tile_smem(K, MT, ksplit);
     SmallLinearArgs a{(const __nv_bfloat16 *)act, (const __nv_bfloat16 *)w, nullptr, M, N, K, N, ksplit, 0,
                       SmallQkvDest{(__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_pages, (__nv_bfloat16 *)v_pages, cos_table,
-                                   sin_table, positions, row_req, block_table, nh, nkvh, dh, page_size, max_blocks}};
+                                   sin_table, positions, row_req, block_table, nh, nkvh, dh, page_size, max_blocks}, norm};
     if (MT == 1) return launch_tile<1, EPI_QKV>(a, smem, stream);
     return launch_tile<2, EPI_QKV>(a, smem, stream);
 }
 
-JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, int N, int K, int ldo,
-                              int epilogue, int sms, cudaStream_t stream) {
+JK_EXPORT int jk_linear_small_qkv(const void *act, const void *w, int M, int K, void *q_out, void *k_pages, void *v_pages,
+                                  const float *cos_table, const float *sin_table, const int *positions,
+                                  const int *row_req, const int *block_table, int max_blocks, int page_size, int nh,
+                                  int nkvh, int dh, int sms, cudaStream_t stream) {
+    return linear_small_qkv_impl(act, w, M, K, q_out, k_pages, v_pages, cos_table, sin_table, positions, row_req, block_table,
+                                 max_blocks, page_size, nh, nkvh, dh, sms, SmallNormFuse{}, stream);
+}
+
+// The same with activations that came without their norm's 1 / rms (see SmallNormFuse): `in_sumsq` holds the rows'
+// sums of squares as the product before the norm left them, K is the norm's width.
+JK_EXPORT int jk_linear_small_qkv_norm(const void *act, const void *w, int M, int K, void *q_out, void *k_pages, void *v_pages,
+                                       const float *cos_table, const float *sin_table, const int *positions,
+                                       const int *row_req, const int *block_table, int max_blocks, int page_size, int nh,
+                                       int nkvh, int dh, const unsigned long long *in_sumsq, float in_eps, int sms,
+                                       cudaStream_t stream) {
+    JK_REQUIRE(in_sumsq != nullptr, "linear_small_qkv_norm: no sums of squares");
+    SmallNormFuse norm{};
+    norm.in_sumsq = in_sumsq;
+    norm.in_eps = in_eps;
+    return linear_small_qkv_impl(act, w, M, K, q_out, k_pages, v_pages, cos_table, sin_table, positions, row_req, block_table,
+                                 max_blocks, page_size, nh, nkvh, dh, sms, norm, stream);
+}
+
+static size_t tile_kernel_smem(int M, int N, int K, int epilogue, int sms, int *ksplit_out) {
+    const int n_tiles = epilogue == EPI_SWIGLU ? (N + 7) / 8 : (N + 15) / 16;
+    int ksplit = n_tiles < 2 * (sms > 0 ? sms : 148) ? ST_MAX_WARPS : SL_MAX_WARPS;
+    while (ksplit > 1 && (K / 32) / ksplit < 2) ksplit /= 2;
+    if (ksplit_out) *ksplit_out = ksplit;
+    return small_tile_smem(K, M <= 8 ? 1 : 2, ksplit);
+}
+
+// The products of a chain without norm kernels run on the tile kernel only (K up to what a 16-row tile may take
+// of shared memory).
+JK_EXPORT int jk_linear_small_norm_supports(int M, int N, int K) {
+    if (M < 1 || M > 16 || N < 1 || K < 32 || K % 32) return 0;
+    return tile_kernel_smem(M, N, K, EPI_F32, 148, nullptr) <= 200 * 1024 && tile_kernel_smem(M, N, K, EPI_SWIGLU, 148, nullptr) <= 200 * 1024;
+}
+
+static int linear_small_impl(const void *act, const void *w, void *out, int M, int N, int K, int ldo,
+                             int epilogue, int sms, const SmallNormFuse &norm, bool fused, cudaStream_t stream) {
     JK_REQUIRE(jk_linear_small_supports(M, N, K), "linear_small: M %d N %d K %d is outside what the kernel takes "
                "(1..16 rows, K a multiple of 32)", M, N, K);
-    JK_REQUIRE(epilogue == EPI_F32 || epilogue == EPI_SWIGLU, "linear_small: epilogue %d", epilogue);
+    JK_REQUIRE(epilogue == EPI_F32 || epilogue == EPI_SWIGLU || (fused && epilogue == EPI_RESIDUAL), "linear_small: epilogue %d", epilogue);
     JK_REQUIRE(ldo >= N, "linear_small: output stride %d < N %d", ldo, N);
     const int MT = M <= 8 ? 1 : 2;
     {
@@ -469,12 +593,15 @@ JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, 
         while (ksplit > 1 && (K / 32) / ksplit < 2) ksplit /= 2;
         const size_t smem = small_tile_smem(K, MT, ksplit);
         if (smem <= 200 * 1024) {
-            SmallLinearArgs a{(const __nv_bfloat16 *)act, (const __nv_bfloat16 *)w, out, M, N, K, ldo, ksplit, 0, SmallQkvDest{}};
+            SmallLinearArgs a{(const __nv_bfloat16 *)act, (const __nv_bfloat16 *)w, out, M, N, K, ldo, ksplit, 0, SmallQkvDest{}, norm};
             if (MT == 1 && epilogue == EPI_F32) return launch_tile<1, EPI_F32>(a, smem, stream);
             if (MT == 2 && epilogue == EPI_F32) return launch_tile<2, EPI_F32>(a, smem, stream);
+            if (MT == 1 && epilogue == EPI_RESIDUAL) return launch_tile<1, EPI_RESIDUAL>(a, smem, stream);
+            if (MT == 2 && epilogue == EPI_RESIDUAL) return launch_tile<2, EPI_RESIDUAL>(a, smem, stream);
             if (MT == 1) return launch_tile<1, EPI_SWIGLU>(a, smem, stream);
             return launch_tile<2, EPI_SWIGLU>(a, smem, stream);
         }
+        JK_REQUIRE(!fused, "linear_small_norm: K %d is beyond the tile kernel", K);
     }
     const int tiles = (N + 15) / 16;
     if (sms <= 0) sms = 148;
@@ -502,4 +629,25 @@ JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, 
     if (MT == 1) SL_LAUNCH(1, EPI_SWIGLU);
     SL_LAUNCH(2, EPI_SWIGLU);
 #undef SL_LAUNCH
+}
+
+JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, int N, int K, int ldo,
+                              int epilogue, int sms, cudaStream_t stream) {
+    return linear_small_impl(act, w, out, M, N, K, ldo, epilogue, sms, SmallNormFuse{}, false, stream);
+}
+
+// A product of a chain without norm kernels (see SmallNormFuse).  epilogue EPI_F32 or EPI_SWIGLU with `in_sumsq`: the
+// activations came without their norm's 1 / rms, which the accumulators get per row before the epilogue (K is the norm's
+// width).  epilogue EPI_RESIDUAL: `out` is the float32 residual stream x [M, ldo]: x += scale * product; if `xb` is given
+// it receives bfloat16(x * next_w) [M, N] and `out_sumsq` [M] this product's share of sum(x^2) per row (the caller
+// zeroes the counters before the first product of a step that adds to them).
+JK_EXPORT int jk_linear_small_norm(const void *act, const void *w, void *out, int M, int N, int K, int ldo, int epilogue,
+                                   const unsigned long long *in_sumsq, float in_eps, void *xb, const float *next_w,
+                                   unsigned long long *out_sumsq, float scale, int sms, cudaStream_t stream) {
+    JK_REQUIRE(jk_linear_small_norm_supports(M, N, K), "linear_small_norm: M %d N %d K %d is outside what the tile kernel takes", M, N, K);
+    JK_REQUIRE(out != nullptr && (xb == nullptr) == (next_w == nullptr) && (xb == nullptr) == (out_sumsq == nullptr),
+               "linear_small_norm: the next product's activations, the norm's weight and the counters come together");
+    JK_REQUIRE(epilogue == EPI_RESIDUAL || xb == nullptr, "linear_small_norm: only the residual epilogue writes activations");
+    SmallNormFuse norm{in_sumsq, in_eps, (__nv_bfloat16 *)xb, next_w, out_sumsq, scale};
+    return linear_small_impl(act, w, out, M, N, K, ldo, epilogue, sms, norm, true, stream);
 }

@@ -32,7 +32,8 @@ JK_EXPORT int jk_runner_bind(const RunnerFns *fns) {
     // the tcgen05 modules may be left out by a caller whose model or step size never reaches them (they are
     // then not even compiled); everything else is needed by every model
     JK_REQUIRE(fns->embed && fns->add_rmsnorm && fns->swiglu && fns->rope_kv && fns->linear_small && fns->linear_small_qkv &&
-               fns->linear_small_supports && fns->linear_small_qkv_supports && fns->attention_decode && fns->attention_prefill && fns->err_elementwise && fns->err_linear_small &&
+               fns->linear_small_supports && fns->linear_small_qkv_supports && fns->linear_small_norm_supports &&
+               fns->linear_small_norm && fns->linear_small_qkv_norm && fns->attention_decode && fns->attention_prefill && fns->err_elementwise && fns->err_linear_small &&
                fns->err_attention, "runner_bind: an entry that every model needs is empty");
     JK_REQUIRE((fns->gemm_tcgen05 != nullptr) == (fns->gemm_tcgen05_qkv != nullptr) &&
                (fns->gemm_tcgen05 != nullptr) == (fns->gemm_skinny != nullptr) &&
@@ -151,10 +152,30 @@ JK_EXPORT int jk_runner_forward(const RunnerModel *mp, const RunnerLayer *layers
     g_launches = 0;
     if (T == 0) return JK_OK;
     RUN(elementwise, g_fns.embed(st.tokens, T, m.embedding, m.embed_dtype, d, m.embed_scale, s.x, stream));
+    // Steps of few rows run without norm kernels when all four products of a layer are the small-row tile kernel's:
+    // o and down add themselves into x, leave bfloat16(x * next norm's weight) in s.h and the rows' sums of squares in
+    // s.sumsq; q/k/v and gate/up scale their rows by 1 / rms.  Two kernels fewer in a layer's chain of nine.
+    const bool fused = m.fused_norms && T <= 16 && s.sumsq != nullptr && g_fns.linear_small_qkv_supports(T, d, dh) &&
+                       g_fns.linear_small_norm_supports(T, d, nh * dh) && g_fns.linear_small_norm_supports(T, di, d) &&
+                       g_fns.linear_small_norm_supports(T, d, di) && few_rows_route(m, T, d, nh * dh, RUNNER_RESIDUAL) == ROUTE_SMALL &&
+                       few_rows_route(m, T, di, d, RUNNER_SWIGLU) == ROUTE_SMALL && few_rows_route(m, T, d, di, RUNNER_RESIDUAL) == ROUTE_SMALL;
+    if (fused) {
+        ++g_launches;
+        if (cudaMemsetAsync(s.sumsq, 0, sizeof(unsigned long long) * 2 * m.layers * 16, stream) != cudaSuccess)
+            JK_FAIL(JK_CUDA_ERROR, "runner: clearing the sums of squares failed");
+    }
     bool pending = false;       // s.delta holds a product that has not been added to x yet
     for (int l = 0; l < m.layers; ++l) {
         const RunnerLayer &L = layers[l];
+        unsigned long long *ss1 = fused ? s.sumsq + (size_t)(2 * l) * 16 : nullptr;       // rows before norm1 of this layer
+        unsigned long long *ss2 = fused ? s.sumsq + (size_t)(2 * l + 1) * 16 : nullptr;   // before norm2
         // ---- attention ----
+        if (fused && l > 0) {
+            // s.h and ss1 were left by the layer before
+            RUN(linear_small, g_fns.linear_small_qkv_norm(s.h, L.w_qkv, T, d, s.q, L.k_pages, L.v_pages, m.cos_table, m.sin_table,
+                                                          st.positions, st.row_req, st.block_table, m.max_blocks, m.page_size,
+                                                          nh, nkvh, dh, ss1, L.eps1, m.sms, stream));
+        } else {
         RUN(elementwise, g_fns.add_rmsnorm(s.x, pending ? s.delta : nullptr, JK_F32, m.residual_scale, L.norm1, L.eps1, 1.f, s.h,
                                            JK_BF16, nullptr, T, d, stream));
         pending = false;
@@ -172,6 +193,7 @@ JK_EXPORT int jk_runner_forward(const RunnerModel *mp, const RunnerLayer *layers
                                            m.page_size, m.cos_table, m.sin_table, 0, s.q, L.k_pages, L.v_pages, JK_BF16, T, nh,
                                            nkvh, dh, 1, stream));
         }
+        }
         if (st.n_tiles > 0) {
             if (m.attention_tcgen05 && g_fns.attention_tcgen05 != nullptr)
                 RUN(attention_tcgen05, g_fns.attention_tcgen05(s.q, L.k_pages, L.v_pages, s.o, st.tiles, st.n_tiles, T, st.req_start,
@@ -187,6 +209,19 @@ JK_EXPORT int jk_runner_forward(const RunnerModel *mp, const RunnerLayer *layers
                                                   st.short_rows, st.n_short, st.positions, st.row_req, st.block_table,
                                                   m.max_blocks, m.page_size, nh, nkvh, dh, m.softmax_scale, m.window, st.splits,
                                                   stream));
+        if (fused) {
+            // x += scale * o; s.h = bfloat16(x * norm2), ss2 = sum(x^2); gate/up reads them; down does the same for the
+            // next layer's norm1 (the last layer's down only adds: the final norm has its own kernel)
+            RUN(linear_small, g_fns.linear_small_norm(s.o, L.w_o, s.x, T, d, nh * dh, d, 3, nullptr, 0.f, s.h, L.norm2, ss2,
+                                                      m.residual_scale, m.sms, stream));
+            RUN(linear_small, g_fns.linear_small_norm(s.h, L.w_gate_up, s.act, T, di, d, di, 1, ss2, L.eps2, nullptr, nullptr, nullptr,
+                                                      1.f, m.sms, stream));
+            const bool last = l + 1 == m.layers;
+            RUN(linear_small, g_fns.linear_small_norm(s.act, L.w_down, s.x, T, d, di, d, 3, nullptr, 0.f, last ? nullptr : s.h,
+                                                      last ? nullptr : layers[l + 1].norm1, last ? nullptr : ss1 + 32,
+                                                      m.residual_scale, m.sms, stream));
+            continue;
+        }
         if (int rc = product_into_residual(m, s, s.o, L.w_o, T, d, nh * dh, &pending, stream)) return rc;
         // ---- feed-forward ----
         RUN(elementwise, g_fns.add_rmsnorm(s.x, pending ? s.delta : nullptr, JK_F32, m.residual_scale, L.norm2, L.eps2, 1.f, s.h,

@@ -25,6 +25,11 @@ typedef int (*AttentionPrefillFn)(const void *, const void *, const void *, void
 typedef int (*AttentionTcgen05Fn)(const void *, const void *, const void *, void *, const int *, int, int, const int *,
                                   const int *, const int *, int, int, int, int, int, int, float, int, int *, cudaStream_t);
 typedef int (*SupportsFn)(int, int, int);
+typedef int (*LinearSmallNormFn)(const void *, const void *, void *, int, int, int, int, int, const unsigned long long *, float,
+                                 void *, const float *, unsigned long long *, float, int, cudaStream_t);
+typedef int (*LinearSmallQkvNormFn)(const void *, const void *, int, int, void *, void *, void *, const float *, const float *,
+                                    const int *, const int *, const int *, int, int, int, int, int,
+                                    const unsigned long long *, float, int, cudaStream_t);
 typedef const char *(*LastErrorFn)();
 typedef int (*ArgmaxFn)(const float *, long long, int, int, int *, void *, cudaStream_t);
 typedef int (*SampleFn)(const float *, long long, int, int, const float *, const int *, const float *, const float *, int *,
@@ -48,6 +53,10 @@ struct RunnerFns {
     // (part of the gemm_tcgen05 module: bound with it or not at all)
     SupportsFn linear_small_supports, linear_small_qkv_supports;
     GemmTcgen05Fn gemm_skinny;
+    // few-row products of a chain in which RMSNorm has no kernel of its own
+    SupportsFn linear_small_norm_supports;
+    LinearSmallNormFn linear_small_norm;
+    LinearSmallQkvNormFn linear_small_qkv_norm;
     // sampling (used by the C interface only; may be empty for a caller that samples by itself)
     ArgmaxFn argmax;
     SampleFn sample;
@@ -60,6 +69,7 @@ struct RunnerModel {
     int page_size, max_blocks, num_pages, window;
     int sms, tcgen05_min_rows, tcgen05_min_tiles;
     int skinny_min_blocks;          // fewest blocks for which the few-rows tcgen05 kernel is used (0: one per SM)
+    int fused_norms;                // 1: steps of at most 16 rows run without norm kernels where the small-row kernels allow
     int attention_tcgen05;          // 1: tiles go to the tcgen05 attention kernel, 0: to the mma.sync kernel
     int embed_dtype;                // JK_F32 or JK_BF16
     float embed_scale, residual_scale, logit_scale, softmax_scale, final_eps;
@@ -98,6 +108,7 @@ struct RunnerScratch {
     float *decode_scratch;          // partial results of the split-key attention
     void *workspace;                // for the library
     long long workspace_bytes;
+    unsigned long long *sumsq;      // [2 * layers, 16] fixed-point sums of squares of the rows before each norm
 };
 
 // Blocks that the few-rows tcgen05 kernel (jk_gemm_skinny) starts for a product with `n` output features over `k`:

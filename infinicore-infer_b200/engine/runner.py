@@ -28,14 +28,15 @@ class _Fns(ctypes.Structure):
         "embed", "add_rmsnorm", "swiglu", "rope_kv", "linear_small", "linear_small_qkv", "gemm_tcgen05",
         "gemm_tcgen05_qkv", "attention_decode", "attention_prefill", "attention_tcgen05",
         "err_elementwise", "err_linear_small", "err_gemm_tcgen05", "err_attention", "err_attention_tcgen05",
-        "linear_small_supports", "linear_small_qkv_supports", "gemm_skinny", "argmax", "sample", "err_sampling")]
+        "linear_small_supports", "linear_small_qkv_supports", "gemm_skinny",
+        "linear_small_norm_supports", "linear_small_norm", "linear_small_qkv_norm", "argmax", "sample", "err_sampling")]
 
 
 class _Model(ctypes.Structure):
     _fields_ = ([(n, ctypes.c_int) for n in (
         "layers", "hidden", "heads", "kv_heads", "head_dim", "intermediate", "vocab",
         "page_size", "max_blocks", "num_pages", "window",
-        "sms", "tcgen05_min_rows", "tcgen05_min_tiles", "skinny_min_blocks", "attention_tcgen05", "embed_dtype")]
+        "sms", "tcgen05_min_rows", "tcgen05_min_tiles", "skinny_min_blocks", "fused_norms", "attention_tcgen05", "embed_dtype")]
                 + [(n, ctypes.c_float) for n in ("embed_scale", "residual_scale", "logit_scale", "softmax_scale", "final_eps")]
                 + [(n, ctypes.c_void_p) for n in ("embedding", "lm_head", "final_norm", "cos_table", "sin_table", "status")])
 
@@ -55,7 +56,7 @@ class _Step(ctypes.Structure):
 class _Scratch(ctypes.Structure):
     _fields_ = ([(n, ctypes.c_void_p) for n in ("x", "h", "qkv", "q", "o", "delta", "gate_up", "act", "hw",
                                                 "decode_scratch", "workspace")]
-                + [("workspace_bytes", ctypes.c_longlong)])
+                + [("workspace_bytes", ctypes.c_longlong), ("sumsq", ctypes.c_void_p)])
 
 
 def _addr(lib, name: str) -> int:
@@ -158,13 +159,14 @@ class NativeRunner:
             vocab=spec.vocab_size, page_size=cache.page_size, max_blocks=cache.max_blocks, num_pages=k0.shape[0],
             window=a.window or 0, sms=kernels._sm_count(dev), tcgen05_min_rows=rt.tcgen05_min_rows,
             tcgen05_min_tiles=rt.tcgen05_min_tiles, skinny_min_blocks=rt.skinny_min_blocks or 0,
+            fused_norms=1 if rt.fused_norms else 0,
             attention_tcgen05=1 if self._attention_tcgen05 else 0,
             embed_dtype=kernels.dtype_code(model.embedding.dtype), embed_scale=spec.embed_scale,
             residual_scale=first.spec.residual_scale, logit_scale=spec.logit_scale, softmax_scale=a.softmax_scale,
             final_eps=model.final_norm.spec.eps, embedding=model.embedding.data_ptr(), lm_head=model.lm_head.data_ptr(),
             final_norm=model.final_norm.weight.data_ptr(), cos_table=pos.cos.data_ptr() if pos else 0,
             sin_table=pos.sin.data_ptr() if pos else 0, status=kernels.gemm_status(dev).data_ptr())
-        self._routing = (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.skinny_min_blocks)
+        self._routing = (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.skinny_min_blocks, rt.fused_norms)
         self._layers = (_Layer * len(model.layers))()
         for i, blk in enumerate(model.layers):
             view = cache.views[spec.order[i].cache]
@@ -180,7 +182,9 @@ class NativeRunner:
                              delta=f32(T, d), gate_up=f32(T, 2 * di), act=b16(T, di), hw=b16(T, d),
                              workspace=torch.empty(32 << 20, dtype=torch.uint8, device=dev))
         self._decode_scratch = f32(1)
+        self._sumsq = torch.zeros(2 * len(model.layers), 16, dtype=torch.int64, device=dev)
         self._scratch = _Scratch(workspace_bytes=32 << 20, decode_scratch=self._decode_scratch.data_ptr(),
+                                 sumsq=self._sumsq.data_ptr(),
                                  **{k: v.data_ptr() for k, v in self._buffers.items()})
         self._max_positions = a.position.max_positions if a.position else 1 << 20
         self._attn_lib = _build.load("attention")
@@ -210,6 +214,9 @@ class NativeRunner:
             gemm_skinny=get("gemm_tcgen05", "jk_gemm_skinny"),
             linear_small_supports=get("linear_small", "jk_linear_small_supports"),
             linear_small_qkv_supports=get("linear_small", "jk_linear_small_qkv_supports"),
+            linear_small_norm_supports=get("linear_small", "jk_linear_small_norm_supports"),
+            linear_small_norm=get("linear_small", "jk_linear_small_norm"),
+            linear_small_qkv_norm=get("linear_small", "jk_linear_small_qkv_norm"),
             attention_decode=get("attention", "jk_attention_decode"), attention_prefill=get("attention", "jk_attention_prefill"),
             attention_tcgen05=get("attention_tcgen05", "jk_attention_tcgen05"),
             err_elementwise=get("elementwise", "jk_elementwise_last_error"),
@@ -230,8 +237,9 @@ class NativeRunner:
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Logits (float32 ``[n_want, vocab]``) of the step that ``ctx`` describes."""
         rt = self.runtime
-        if (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.skinny_min_blocks) != self._routing:       # a test moved the thresholds
-            self._routing = (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.skinny_min_blocks)
+        if (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.skinny_min_blocks, rt.fused_norms) != self._routing:       # a test moved the thresholds
+            self._routing = (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.skinny_min_blocks, rt.fused_norms)
+            self._model.fused_norms = 1 if rt.fused_norms else 0
             self._model.tcgen05_min_rows, self._model.tcgen05_min_tiles = rt.tcgen05_min_rows, rt.tcgen05_min_tiles
             self._model.skinny_min_blocks = rt.skinny_min_blocks or 0
             self._bind()

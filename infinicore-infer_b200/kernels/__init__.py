@@ -176,7 +176,7 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional
     return out
 
 
-EPI_F32, EPI_SWIGLU = 0, 1
+EPI_F32, EPI_SWIGLU, EPI_RESIDUAL = 0, 1, 3
 
 
 def linear_small_supports(m: int, n: int, k: int) -> bool:
@@ -219,6 +219,61 @@ def linear_small_qkv(act: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_
         _ptr(act), _ptr(w), _c_int(m), _c_int(k), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(cos), _ptr(sin),
         _ptr(positions), _ptr(row_req), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size), _c_int(nh),
         _c_int(nkvh), _c_int(dh), _c_int(_sm_count(act.device)), _stream()))
+    return q_out
+
+
+SUMSQ_FIXED = float(1 << 26)      # the fixed-point scale of the row sums of squares (csrc/linear_small.cu)
+
+
+def linear_small_norm_supports(m: int, n: int, k: int) -> bool:
+    """Whether the products of a chain without norm kernels take this shape (the tile kernel's reach)."""
+    return bool(_build.load("linear_small").jk_linear_small_norm_supports(_c_int(m), _c_int(n), _c_int(k)))
+
+
+def linear_small_norm(act: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_F32,
+                      in_sumsq: Optional[torch.Tensor] = None, in_eps: float = 0.0, xb: Optional[torch.Tensor] = None,
+                      next_w: Optional[torch.Tensor] = None, out_sumsq: Optional[torch.Tensor] = None,
+                      scale: float = 1.0) -> torch.Tensor:
+    """A few-row product of a chain in which RMSNorm has no kernel of its own.  With ``in_sumsq`` (int64 [M],
+    fixed point: sum of squares times ``SUMSQ_FIXED``) the activations are x * norm weight without the 1 / rms,
+    which the rows of the product get before the epilogue (EPI_F32 or EPI_SWIGLU).  ``EPI_RESIDUAL``: ``out`` is
+    the float32 residual stream, ``out += scale * product``; ``xb`` receives bfloat16(out * next_w) and
+    ``out_sumsq`` (zeroed by the caller) this product's sums of squares of the new rows."""
+    _need(act, "act", torch.bfloat16); _need(w, "w", torch.bfloat16)
+    _need(out, "out", torch.bfloat16 if epilogue == EPI_SWIGLU else torch.float32)
+    m, k = act.shape
+    n = w.shape[0] // (2 if epilogue == EPI_SWIGLU else 1)
+    if w.shape[1] != k or tuple(out.shape) != (m, n):
+        raise KernelError(f"linear_small_norm: act {tuple(act.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    for name, t, dt in (("in_sumsq", in_sumsq, torch.int64), ("out_sumsq", out_sumsq, torch.int64), ("xb", xb, torch.bfloat16),
+                        ("next_w", next_w, torch.float32)):
+        if t is not None:
+            _need(t, name, dt)
+    if (in_sumsq is not None and in_sumsq.numel() < m) or (out_sumsq is not None and out_sumsq.numel() < m) \
+            or (xb is not None and tuple(xb.shape) != (m, n)) or (next_w is not None and next_w.numel() != n):
+        raise KernelError("linear_small_norm: a norm array has the wrong size")
+    lib = _build.load("linear_small")
+    _check("linear_small", lib.jk_linear_small_norm(
+        _ptr(act), _ptr(w), _ptr(out), _c_int(m), _c_int(n), _c_int(k), _c_int(out.stride(0)), _c_int(epilogue),
+        _ptr(in_sumsq), _c_float(in_eps), _ptr(xb), _ptr(next_w), _ptr(out_sumsq), _c_float(scale),
+        _c_int(_sm_count(act.device)), _stream()))
+    return out
+
+
+def linear_small_qkv_norm(act: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor,
+                          v_pages: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                          positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor, nh: int,
+                          in_sumsq: torch.Tensor, in_eps: float) -> torch.Tensor:
+    """``linear_small_qkv`` for activations that came without their norm's 1 / rms (see ``linear_small_norm``)."""
+    _check_qkv_args("linear_small_qkv_norm", act, w, q_out, k_pages, v_pages, cos, sin, positions, row_req, block_table, nh)
+    _need(in_sumsq, "in_sumsq", torch.int64)
+    m, k = act.shape
+    _, nkvh, page_size, dh = k_pages.shape
+    lib = _build.load("linear_small")
+    _check("linear_small", lib.jk_linear_small_qkv_norm(
+        _ptr(act), _ptr(w), _c_int(m), _c_int(k), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(cos), _ptr(sin),
+        _ptr(positions), _ptr(row_req), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size), _c_int(nh),
+        _c_int(nkvh), _c_int(dh), _ptr(in_sumsq), _c_float(in_eps), _c_int(_sm_count(act.device)), _stream()))
     return q_out
 
 

@@ -17,6 +17,7 @@ mode are all derived from it.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional
 
@@ -70,6 +71,9 @@ class Runtime:
         self.tcgen05_min_tiles = 96          # fewest 128x128 output tiles for which the tcgen05 kernel is used
         self.tcgen05_min_rows = 1024         # ... and fewest rows: below, the library's split-K kernels win
         self.skinny_min_blocks: Optional[int] = None   # fewest blocks for the few-rows tcgen05 kernel (None: one per SM)
+        # the native runner runs steps of at most 16 rows without norm kernels (the products around a norm share its
+        # work: csrc/linear_small.cu, SmallNormFuse); JK_NO_FUSED_NORM=1 keeps the norm kernels
+        self.fused_norms = os.environ.get("JK_NO_FUSED_NORM") != "1"
 
     def empty(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

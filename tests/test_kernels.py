@@ -201,6 +201,95 @@ def test_small_row_qkv_product_rotates_and_writes_the_cache_in_its_epilogue(K, n
     assert float(kp[0].abs().max()) == 0.0              # the null page was not written
 
 
+@pytest.mark.parametrize("rows,width,kdim", [(8, 96, 160), (1, 40, 64), (16, 333, 2304), (11, 2304, 5760)])
+def test_a_chain_of_few_row_products_carries_the_norm_between_them(K, rows, width, kdim):
+    """The product before a norm adds itself into the residual stream, leaves bfloat16(x * norm weight) and the
+    rows' sums of squares; the product after it scales its rows by 1 / rms: together they are product, residual
+    add, RMSNorm and product, without a norm kernel."""
+    assert K.linear_small_norm_supports(rows, width, kdim) and not K.linear_small_norm_supports(17, width, kdim)
+    g = torch.Generator().manual_seed(rows + width + kdim)
+    act = (torch.randn(rows, kdim, generator=g)).to(torch.bfloat16)
+    w = (torch.randn(width, kdim, generator=g) / math.sqrt(kdim)).to(torch.bfloat16)
+    x0 = torch.randn(rows, width, generator=g) * 3
+    gain = 1 + 0.1 * torch.randn(width, generator=g)
+    eps, scale = 1e-5, 0.7
+    x = x0.to(DEV).clone()
+    xb = torch.full((rows, width), 9.0, dtype=torch.bfloat16, device=DEV)
+    sumsq = torch.zeros(16, dtype=torch.int64, device=DEV)
+    K.linear_small_norm(act.to(DEV), w.to(DEV), x, K.EPI_RESIDUAL, xb=xb, next_w=gain.to(DEV), out_sumsq=sumsq, scale=scale)
+    want_x = x0.double() + scale * (act.double() @ w.double().T)
+    torch.testing.assert_close(x.double().cpu(), want_x, rtol=1e-5, atol=1e-5)
+    _close(xb, want_x * gain.double(), torch.bfloat16, scale=2.0)
+    got_ss = sumsq[:rows].cpu().double() / K.SUMSQ_FIXED
+    torch.testing.assert_close(got_ss, (want_x ** 2).sum(-1), rtol=1e-5, atol=1e-5)
+    assert int(sumsq[rows:].abs().max()) == 0 if rows < 16 else True
+    # the same again gives the same counters to the last bit (integer additions, whatever the order of the tiles)
+    x2, sumsq2 = x0.to(DEV).clone(), torch.zeros_like(sumsq)
+    K.linear_small_norm(act.to(DEV), w.to(DEV), x2, K.EPI_RESIDUAL, xb=torch.empty_like(xb), next_w=gain.to(DEV), out_sumsq=sumsq2, scale=scale)
+    assert torch.equal(sumsq, sumsq2) and torch.equal(x, x2)
+    # without activations for a next product (the last layer): only the addition
+    x3 = x0.to(DEV).clone()
+    K.linear_small_norm(act.to(DEV), w.to(DEV), x3, K.EPI_RESIDUAL, scale=scale)
+    assert torch.equal(x3, x)
+    # the product after the norm: plain output and SwiGLU
+    n2 = 72
+    w2 = (torch.randn(2 * n2, width, generator=g) * 2 / math.sqrt(width)).to(torch.bfloat16)
+    if K.linear_small_norm_supports(rows, n2, width):
+        # the activations are what the first product left (rounded to bfloat16 before the 1 / rms)
+        inv = 1 / torch.sqrt((want_x ** 2).mean(-1, keepdim=True) + eps)
+        out = torch.full((rows, 2 * n2), 9.0, device=DEV)
+        K.linear_small_norm(xb, w2.to(DEV), out, K.EPI_F32, in_sumsq=sumsq, in_eps=eps)
+        ref = (xb.double().cpu() @ w2.double().T) * inv
+        _close(out, ref, torch.bfloat16, scale=2.0)
+        act2 = torch.full((rows, n2), 9.0, dtype=torch.bfloat16, device=DEV)
+        K.linear_small_norm(xb, w2.to(DEV), act2, K.EPI_SWIGLU, in_sumsq=sumsq, in_eps=eps)
+        _close(act2, ref[:, :n2] * torch.sigmoid(ref[:, :n2]) * ref[:, n2:], torch.bfloat16, scale=2.0)
+
+
+def test_small_row_qkv_product_scales_its_rows_by_the_norm(K):
+    nh, nkvh, dh, page, rows, kdim = 4, 2, 64, 16, 7, 192
+    g = torch.Generator().manual_seed(3)
+    width = (nh + 2 * nkvh) * dh
+    x = torch.randn(rows, kdim, generator=g) * 4
+    gain = 1 + 0.1 * torch.randn(kdim, generator=g)
+    eps = 1e-6
+    xb = (x * gain).to(torch.bfloat16)
+    sumsq = torch.zeros(16, dtype=torch.int64)
+    sumsq[:rows] = ((x.double() ** 2).sum(-1) * K.SUMSQ_FIXED).round().long()
+    h = (x.double() * gain.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + eps)).float().to(torch.bfloat16)
+    w = (torch.randn(width, kdim, generator=g) * 0.1).to(torch.bfloat16)
+    max_pos, theta = 96, 5000.0
+    j = torch.arange(dh // 2, dtype=torch.float64)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] / theta ** (j / (dh // 2))
+    cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    max_blocks = max_pos // page
+    table = (torch.randperm(rows * max_blocks, generator=g) + 1).view(rows, max_blocks).to(torch.int32).to(DEV)
+    positions = torch.randint(0, max_pos, (rows,), generator=g).to(torch.int32).to(DEV)
+    row_req = torch.arange(rows, dtype=torch.int32, device=DEV)
+    num_pages = rows * max_blocks + 1
+    kp = torch.zeros(num_pages, nkvh, page, dh, dtype=torch.bfloat16, device=DEV)
+    vp = torch.zeros_like(kp)
+    q_out = torch.full((rows, nh * dh), 9.0, dtype=torch.bfloat16, device=DEV)
+    K.linear_small_qkv_norm(xb.to(DEV), w.to(DEV), q_out, kp, vp, cos, sin, positions, row_req, table, nh, sumsq.to(DEV), eps)
+    # what it has to be: the product of the activations as they are (rounded before the 1 / rms), scaled, rotated
+    inv = 1 / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + eps)
+    y = (xb.double() @ w.double().T) * inv
+    q = y[:, :nh * dh].view(rows, nh, dh)
+    k = y[:, nh * dh:(nh + nkvh) * dh].view(rows, nkvh, dh)
+    v = y[:, (nh + nkvh) * dh:].view(rows, nkvh, dh)
+    pos = positions.cpu()
+    _close(q_out.view(rows, nh, dh), plain_rope(q, pos, theta), torch.bfloat16, scale=2.0)
+    rk = plain_rope(k, pos, theta)
+    for t in range(rows):
+        p = int(table[t, pos[t] // page])
+        _close(kp[p, :, pos[t] % page], rk[t], torch.bfloat16, scale=2.0)
+        _close(vp[p, :, pos[t] % page], v[t], torch.bfloat16, scale=2.0)
+    # and it is the plain kernel's result on normalised activations, up to where those were rounded
+    kp2, vp2, q2 = torch.zeros_like(kp), torch.zeros_like(vp), torch.empty_like(q_out)
+    K.linear_small_qkv(h.to(DEV), w.to(DEV), q2, kp2, vp2, cos, sin, positions, row_req, table, nh)
+    assert float((q2.float() - q_out.float()).abs().max()) <= 0.05 * float(q2.float().abs().max())
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkvh,dh,page,interleaved", [(6, 2, 48, 8, False), (4, 4, 16, 16, True),
                                                           (3, 1, 128, 4, False), (8, 2, 256, 32, False)])
@@ -459,9 +548,8 @@ def test_linear_small_streams_weights_for_few_rows(K, M, N, K_):
     g = torch.Generator().manual_seed(M * N + K_)
     act = torch.randn(M, K_, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
-    if M > 8 and K_ > 5000:          # 16 rows of 5760 activations leave no room in shared memory
-        assert not K.linear_small_supports(M, N, K_)
-        return
+    # (16 rows of 5760 activations leave the ring kernel no room in shared memory; the tile kernel, which keeps a
+    # tile of the weights there instead, takes them)
     assert K.linear_small_supports(M, N, K_)
     out = torch.full((M, N), 9.0, device=DEV)
     K.linear_small(act.to(DEV), w.to(DEV), out)

@@ -14,6 +14,7 @@ pytestmark = pytest.mark.gpu
 def test_native_runner_and_parts_give_the_same_logits(tiny_models, name):
     folder = tiny_models[name][0]
     native = make_engine(folder, "bfloat16", 1024)
+    native.runtime.fused_norms = False       # the same kernels as the parts: the runner's own way for few rows is tested below
     parts = make_engine(folder, "bfloat16", 1024, native_runner=False)
     assert native.runner is not None and parts.runner is None
     toks, want = expected(tiny_models, name, 500, 200)
@@ -39,6 +40,41 @@ def test_native_runner_and_parts_give_the_same_logits(tiny_models, name):
     native.check()
 
 
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_steps_of_few_rows_run_without_norm_kernels(tiny_models, name):
+    """The runner's own way for steps of at most 16 rows: the products around a norm share its work (the one before
+    adds itself into the residual stream and leaves activations and sums of squares, the one after scales its rows),
+    so the activations are rounded to bfloat16 before the 1 / rms instead of after.  Against the plain implementation,
+    however the request is cut; the same bits every time; fewer launches than with the norm kernels."""
+    folder = tiny_models[name][0]
+    fused = make_engine(folder, "bfloat16", 1024)
+    kept = make_engine(folder, "bfloat16", 1024)
+    kept.runtime.fused_norms = False         # before its first step: decode steps are captured once
+    assert fused.runtime.fused_norms and fused.runner is not None
+    toks, want = expected(tiny_models, name, 500, 200)
+    toks2, want2 = expected(tiny_models, name, 501, 90)
+    plan = [{"a": 150}, {"a": 1, "b": 60}, {"a": 2, "b": 1}, {"a": 1, "b": 1}, {"a": 46, "b": 28}]
+    for what, steps in (("tail", tail_decode("a", toks)), ("portions", portions("a", toks, sizes=(40, 3, 130, 9, 2, 16))),
+                        ("mixed", mixed({"a": toks, "b": toks2}, plan)), ("one by one", tail_decode("a", toks[:60], tail=60))):
+        got = run(fused, steps)
+        check(got, "a", want[:60] if what == "one by one" else want, TOL["bfloat16"], f"{name} without norm kernels, {what}")
+        if what == "mixed":
+            check(got, "b", want2, TOL["bfloat16"], f"{name} without norm kernels, {what} (b)")
+        again = run(fused, steps)
+        for key in got:
+            assert np.array_equal(got[key], again[key]), (name, what, key)
+    steps = tail_decode("a", toks[:40], tail=40)
+    counts = []
+    for eng in (fused, kept):
+        before = eng.kernel_launches
+        run(eng, steps)
+        counts.append((eng.kernel_launches - before) // len(steps))
+    layers = tiny_models[name][1]["num_hidden_layers"]
+    # two norm kernels a layer fewer, but the first layer's first; one clearing of the sums more
+    assert counts[1] - counts[0] == 2 * layers - 1 - 1, counts
+    fused.check()
+
+
 @pytest.mark.parametrize("name", ["B", "D"])
 def test_runner_and_parts_route_few_rows_alike(tiny_models, name):
     """With the few-rows tcgen05 kernel forced on for every size (a tiny model never has a block per SM), steps of
@@ -48,6 +84,7 @@ def test_runner_and_parts_route_few_rows_alike(tiny_models, name):
     native = make_engine(folder, "bfloat16", 1024)
     parts = make_engine(folder, "bfloat16", 1024, native_runner=False)
     native.runtime.skinny_min_blocks = parts.runtime.skinny_min_blocks = 1
+    native.runtime.fused_norms = False       # the parts keep their norm kernels; this test is about the products
     toks, want = expected(tiny_models, name, 510, 180)
     for what, steps in (("portions", portions("a", toks, sizes=(100, 17, 30, 5, 28))), ("tail", tail_decode("a", toks))):
         got_n, got_p = run(native, steps), run(parts, steps)
