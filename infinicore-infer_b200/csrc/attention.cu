@@ -185,6 +185,7 @@ struct DecodeArgs {
     const int *block_table;
     int nrows, nh, nkvh, dh, page_size, max_blocks, window, splits, page_shift;
     float scale_log2;              // softmax scale * log2(e)
+    int cluster;                   // 1: the splits of a row are one thread-block cluster and merge among themselves
 };
 
 constexpr int DEC_WARPS = 4;
@@ -726,6 +727,18 @@ __device__ __forceinline__ void cp_async16_or_zero(void *smem, const void *gmem,
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
 }
 
+// A float of another block of this block's cluster, at the place where `local` lies in this block.
+__device__ __forceinline__ float ld_cluster_f32(const float *local, unsigned rank) {
+    unsigned addr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(addr) : "r"((unsigned)__cvta_generic_to_shared(local)), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void cluster_sync_all() {      // every thread of every block of the cluster
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
 template <int DH>
 __global__ void __launch_bounds__(128)
 attention_decode_gqa_kernel(DecodeArgs a) {
@@ -749,7 +762,8 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     const int per = max(2, (tiles_all + a.splits - 1) / a.splits);
     const int k0 = lo + split * per * GQ_KEYS, k1 = min(hi, k0 + per * GQ_KEYS);
     const size_t pbase = ((size_t)ri * a.nh + h0) * a.splits + split;      // + head * splits
-    if (k0 >= k1) {                                // nothing for this split: the merge skips it
+    if (k0 >= k1 && !a.cluster) {                  // nothing for this split: the merge skips it (in a cluster the block
+                                                   // goes on with no tiles: the others wait for it at the barriers)
         if (a.splits > 1 && threadIdx.x < heads) {
             a.part_ml[(pbase + (size_t)threadIdx.x * a.splits) * 2] = -INFINITY;
             a.part_ml[(pbase + (size_t)threadIdx.x * a.splits) * 2 + 1] = 0.f;
@@ -914,6 +928,7 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     // (four heads, dims 0..7) fall into 32 different banks
     constexpr int RS = DH + 8;
     float *red = reinterpret_cast<float *>(gq_smem);
+    float *fin = red + 4 * GQ_HEADS * RS, *fin_ml = fin + GQ_HEADS * DH;      // this block's result, for its cluster
     {
         float *mine = red + (size_t)warp * GQ_HEADS * RS;
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
@@ -937,17 +952,43 @@ attention_decode_gqa_kernel(DecodeArgs a) {
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float *src = red + ((size_t)w * GQ_HEADS + r) * RS;
-            const float f = fast_exp2(src[DH] - M);             // a warp without keys: 2^-inf = 0
+            const float f = M == -INFINITY ? 0.f : fast_exp2(src[DH] - M);      // a warp without keys: 2^-inf = 0
             L += f * src[DH + 1];
             A += f * src[e];
         }
-        if (a.splits == 1) {
+        if (a.cluster) {
+            fin[r * DH + e] = A;
+            if (e == 0) { fin_ml[2 * r] = M; fin_ml[2 * r + 1] = L; }
+        } else if (a.splits == 1) {
             a.out[((size_t)t * a.nh + h0 + r) * DH + e] = __float2bfloat16_rn(A / L);
         } else {
             const size_t slot = pbase + (size_t)r * a.splits;
             a.part_acc[slot * DH + e] = A;
             if (e == 0) { a.part_ml[slot * 2] = M; a.part_ml[slot * 2 + 1] = L; }
         }
+    }
+    if (a.cluster) {
+        // the splits of this row and head group are the blocks of one cluster: the first reads the others' results
+        // out of their shared memory and writes the row (the same sums, in the same order, as the merge kernel)
+        cluster_sync_all();
+        if (split == 0) {
+            for (int idx = threadIdx.x; idx < heads * DH; idx += 128) {
+                const int r = idx / DH;
+                float M = -INFINITY;
+                for (int p = 0; p < a.splits; ++p) M = fmaxf(M, ld_cluster_f32(fin_ml + 2 * r, p));
+                float L = 0.f, A = 0.f;
+                for (int p = 0; p < a.splits; ++p) {
+                    const float mp = ld_cluster_f32(fin_ml + 2 * r, p);
+                    if (mp > -INFINITY) {
+                        const float f = exp2f(mp - M);
+                        L += f * ld_cluster_f32(fin_ml + 2 * r + 1, p);
+                        A += f * ld_cluster_f32(fin + idx, p);
+                    }
+                }
+                a.out[((size_t)t * a.nh + h0 + r) * DH + (idx % DH)] = __float2bfloat16_rn(A / L);
+            }
+        }
+        cluster_sync_all();                        // nobody leaves while its shared memory may still be read
     }
 }
 
@@ -956,11 +997,30 @@ static int launch_decode_gqa(const DecodeArgs &a, cudaStream_t stream) {
     const int g = a.nh / a.nkvh;
     const size_t ring = (size_t)GQ_STAGES * 2 * GQ_KEYS * DH * sizeof(__nv_bfloat16) + 2 * GQ_KEYS * sizeof(long long)
                         + (size_t)GQ_HEADS * DH * sizeof(__nv_bfloat16);       // tiles, the two tables, the queries
-    const size_t merge = (size_t)4 * GQ_HEADS * (DH + 8) * sizeof(float);
+    const size_t merge = (size_t)4 * GQ_HEADS * (DH + 8) * sizeof(float) + (size_t)GQ_HEADS * (DH + 2) * sizeof(float);
     const size_t smem = ring > merge ? ring : merge;
     cudaError_t e = cudaFuncSetAttribute(attention_decode_gqa_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_decode: %s", cudaGetErrorString(e));
     dim3 grid(a.splits, a.nkvh * ((g + GQ_HEADS - 1) / GQ_HEADS), a.nrows);
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    // Measured: with heads of 64 (52 KB of shared memory a block) clusters of two are faster than the merge kernel
+    // (48.6 against 50.0 us at 8 x 4096 keys, 36 heads), and larger ones as long as all blocks are resident at once (a
+    // single row: 14.1 us at eight splits); larger clusters in several waves, and any cluster of the 103 KB blocks of
+    // heads of 128, wait for whole groups of free SMs and lose more than the merge kernel costs (37.6 against 30.9 us).
+    const long long blocks = (long long)grid.x * grid.y * grid.z;
+    if (DH == 64 && a.splits >= 2 && a.splits <= 8 && (a.splits == 2 || blocks <= 2LL * sms)) {
+        // the splits are one cluster and merge through distributed shared memory: no merge kernel, no scratch
+        DecodeArgs c = a;
+        c.cluster = 1;
+        const cudaError_t err = jk_launch_clusters(attention_decode_gqa_kernel<DH>, a.splits, grid, dim3(128), smem, stream, c);
+        if (err != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_decode_gqa (clusters of %d): %s", a.splits, cudaGetErrorString(err));
+        return JK_OK;
+    }
     jk_launch(attention_decode_gqa_kernel<DH>, grid, dim3(128), smem, stream, a);
     JK_CHECK_LAUNCH("attention_decode_gqa");
     if (a.splits > 1) {
