@@ -494,6 +494,9 @@ int check_status(JkModel *m) {
     CUDA_TRY(cudaMemcpy(&status, m->rm.status, sizeof(int), cudaMemcpyDeviceToHost), "batch: status word");
     if (status != 0) {
         cudaMemset(m->rm.status, 0, sizeof(int));
+        if (status == 4)
+            JK_FAIL(JK_CUDA_ERROR, "batch: a row's sum of squares is beyond the range of the fixed-point counters; the results "
+                                   "of this batch are invalid (JK_NO_FUSED_NORM=1 keeps the norm kernels, which have no such limit)");
         JK_FAIL(JK_CUDA_ERROR, "batch: a tcgen05 kernel gave up a bounded wait (status %d); the results of this batch are invalid", status);
     }
     return JK_OK;

@@ -40,7 +40,9 @@ struct SmallNormFuse {
     const float *next_w;                  // [N] the next norm's weight
     unsigned long long *out_sumsq;        // [M], or null
     float scale;                          // x += scale * product
+    int *status;                          // receives 4 if a tile's sum of squares is beyond the counter's range, or null
 };
+constexpr float SUMSQ_TILE_LIMIT = 9007199254740992.f;      // 2^53 in fixed point: a thousand tiles cannot wrap the counter
 
 // EPI_QKV: where the fused [q | k | v] projection's columns go (bfloat16 all).
 struct SmallQkvDest {
@@ -403,7 +405,14 @@ small_linear_tile_kernel(SmallLinearArgs a) {
                     v += __shfl_xor_sync(0xffffffffu, v, 8);
                     v += __shfl_xor_sync(0xffffffffu, v, 16);
                     const int row = m * 8 + 2 * t + j;
-                    if (g == 0 && row < a.M) atomicAdd(a.norm.out_sumsq + row, __float2ull_rn(v * SUMSQ_TO_FIXED));
+                    if (g == 0 && row < a.M) {
+                        float fx = v * SUMSQ_TO_FIXED;
+                        if (!(fx < SUMSQ_TILE_LIMIT)) {                  // also a NaN: say so instead of wrapping around
+                            if (a.norm.status != nullptr) atomicExch(a.norm.status, 4);
+                            fx = SUMSQ_TILE_LIMIT;
+                        }
+                        atomicAdd(a.norm.out_sumsq + row, __float2ull_rn(fx));
+                    }
                 }
             }
         }
@@ -640,14 +649,15 @@ JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, 
 // activations came without their norm's 1 / rms, which the accumulators get per row before the epilogue (K is the norm's
 // width).  epilogue EPI_RESIDUAL: `out` is the float32 residual stream x [M, ldo]: x += scale * product; if `xb` is given
 // it receives bfloat16(x * next_w) [M, N] and `out_sumsq` [M] this product's share of sum(x^2) per row (the caller
-// zeroes the counters before the first product of a step that adds to them).
+// zeroes the counters before the first product of a step that adds to them; `status`, if given, receives 4 when a
+// tile's sum of squares is beyond what the counters hold: activations of several thousand on average).
 JK_EXPORT int jk_linear_small_norm(const void *act, const void *w, void *out, int M, int N, int K, int ldo, int epilogue,
                                    const unsigned long long *in_sumsq, float in_eps, void *xb, const float *next_w,
-                                   unsigned long long *out_sumsq, float scale, int sms, cudaStream_t stream) {
+                                   unsigned long long *out_sumsq, float scale, int *status, int sms, cudaStream_t stream) {
     JK_REQUIRE(jk_linear_small_norm_supports(M, N, K), "linear_small_norm: M %d N %d K %d is outside what the tile kernel takes", M, N, K);
     JK_REQUIRE(out != nullptr && (xb == nullptr) == (next_w == nullptr) && (xb == nullptr) == (out_sumsq == nullptr),
                "linear_small_norm: the next product's activations, the norm's weight and the counters come together");
     JK_REQUIRE(epilogue == EPI_RESIDUAL || xb == nullptr, "linear_small_norm: only the residual epilogue writes activations");
-    SmallNormFuse norm{in_sumsq, in_eps, (__nv_bfloat16 *)xb, next_w, out_sumsq, scale};
+    SmallNormFuse norm{in_sumsq, in_eps, (__nv_bfloat16 *)xb, next_w, out_sumsq, scale, status};
     return linear_small_impl(act, w, out, M, N, K, ldo, epilogue, sms, norm, true, stream);
 }

@@ -213,13 +213,13 @@ JK_EXPORT int jk_runner_forward(const RunnerModel *mp, const RunnerLayer *layers
             // x += scale * o; s.h = bfloat16(x * norm2), ss2 = sum(x^2); gate/up reads them; down does the same for the
             // next layer's norm1 (the last layer's down only adds: the final norm has its own kernel)
             RUN(linear_small, g_fns.linear_small_norm(s.o, L.w_o, s.x, T, d, nh * dh, d, 3, nullptr, 0.f, s.h, L.norm2, ss2,
-                                                      m.residual_scale, m.sms, stream));
+                                                      m.residual_scale, m.status, m.sms, stream));
             RUN(linear_small, g_fns.linear_small_norm(s.h, L.w_gate_up, s.act, T, di, d, di, 1, ss2, L.eps2, nullptr, nullptr, nullptr,
-                                                      1.f, m.sms, stream));
+                                                      1.f, m.status, m.sms, stream));
             const bool last = l + 1 == m.layers;
             RUN(linear_small, g_fns.linear_small_norm(s.act, L.w_down, s.x, T, d, di, d, 3, nullptr, 0.f, last ? nullptr : s.h,
                                                       last ? nullptr : layers[l + 1].norm1, last ? nullptr : ss1 + 32,
-                                                      m.residual_scale, m.sms, stream));
+                                                      m.residual_scale, m.status, m.sms, stream));
             continue;
         }
         if (int rc = product_into_residual(m, s, s.o, L.w_o, T, d, nh * dh, &pending, stream)) return rc;

@@ -26,7 +26,7 @@ typedef int (*AttentionTcgen05Fn)(const void *, const void *, const void *, void
                                   const int *, const int *, int, int, int, int, int, int, float, int, int *, cudaStream_t);
 typedef int (*SupportsFn)(int, int, int);
 typedef int (*LinearSmallNormFn)(const void *, const void *, void *, int, int, int, int, int, const unsigned long long *, float,
-                                 void *, const float *, unsigned long long *, float, int, cudaStream_t);
+                                 void *, const float *, unsigned long long *, float, int *, int, cudaStream_t);
 typedef int (*LinearSmallQkvNormFn)(const void *, const void *, int, int, void *, void *, void *, const float *, const float *,
                                     const int *, const int *, const int *, int, int, int, int, int,
                                     const unsigned long long *, float, int, cudaStream_t);

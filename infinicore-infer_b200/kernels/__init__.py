@@ -256,7 +256,7 @@ def linear_small_norm(act: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi
     _check("linear_small", lib.jk_linear_small_norm(
         _ptr(act), _ptr(w), _ptr(out), _c_int(m), _c_int(n), _c_int(k), _c_int(out.stride(0)), _c_int(epilogue),
         _ptr(in_sumsq), _c_float(in_eps), _ptr(xb), _ptr(next_w), _ptr(out_sumsq), _c_float(scale),
-        _c_int(_sm_count(act.device)), _stream()))
+        _ptr(gemm_status(act.device)), _c_int(_sm_count(act.device)), _stream()))
     return out
 
 
@@ -335,6 +335,10 @@ def check_gemm_status(device) -> None:
         code = int(_tg_status[key].item())
         if code:
             _tg_status[key].zero_()
+            if code == 4:
+                raise KernelError("linear_small: a row's sum of squares is beyond the range of the fixed-point counters "
+                                  "(activations of several thousand on average); the step's results are not valid; "
+                                  "JK_NO_FUSED_NORM=1 keeps the norm kernels, which have no such limit")
             raise KernelError(f"gemm_tcgen05: a bounded wait ran out (role {code}: 1 TMA, 2 MMA, 3 epilogue); "
                               "the step's results are not valid")
 

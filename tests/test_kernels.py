@@ -246,6 +246,24 @@ def test_a_chain_of_few_row_products_carries_the_norm_between_them(K, rows, widt
         _close(act2, ref[:, :n2] * torch.sigmoid(ref[:, :n2]) * ref[:, n2:], torch.bfloat16, scale=2.0)
 
 
+def test_sums_of_squares_beyond_the_counters_are_reported(K):
+    """The counters hold sums up to 2^38 a row; a tile whose share is beyond 2^27 says so in the status word that
+    the engine checks, instead of wrapping around."""
+    rows, width, kdim = 4, 64, 64
+    act = torch.zeros(rows, kdim, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(width, kdim, dtype=torch.bfloat16, device=DEV)
+    x = torch.full((rows, width), 1.0e4, device=DEV)          # 16 features x 1e8 = 1.6e9 a tile and row
+    x[0] = 1.0
+    sumsq = torch.zeros(16, dtype=torch.int64, device=DEV)
+    K.check_gemm_status(DEV)
+    K.linear_small_norm(act, w, x, K.EPI_RESIDUAL, xb=torch.empty(rows, width, dtype=torch.bfloat16, device=DEV),
+                        next_w=torch.ones(width, device=DEV), out_sumsq=sumsq)
+    with pytest.raises(K.KernelError, match="sum of squares"):
+        K.check_gemm_status(DEV)
+    K.check_gemm_status(DEV)                                   # the word was cleared
+    assert int(sumsq[0]) == int(width * K.SUMSQ_FIXED)         # the row within range was counted as ever
+
+
 def test_small_row_qkv_product_scales_its_rows_by_the_norm(K):
     nh, nkvh, dh, page, rows, kdim = 4, 2, 64, 16, 7, 192
     g = torch.Generator().manual_seed(3)
