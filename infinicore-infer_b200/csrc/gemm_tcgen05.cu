@@ -64,6 +64,8 @@ struct TgArgs {
     float scale;
     int *status;       // device word: 0, or the code of the wait that ran out
     int direct;        // 1: the output's rows are not 16-byte aligned, store from registers instead of by TMA
+    int ksplit;        // EPI_RESIDUAL by TMA only: a tile's K is cut into this many units whose partial products all add
+                       // themselves into the output (0 or 1: none)
     QkvDest qkv;       // EPI_QKV only
 };
 
@@ -240,8 +242,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int worker = blockIdx.x / CTAS, workers = gridDim.x / CTAS;
     constexpr int TILE_M = TG_BM * CTAS;
     const int tiles_n = (a.N + OUT_COLS - 1) / OUT_COLS, tiles_m = (a.M + TILE_M - 1) / TILE_M;
-    const int num_tiles = tiles_n * tiles_m;
-    const int nk = (a.K + TG_BK - 1) / TG_BK;
+    // a unit of work is a tile, or one of a tile's `ksplit` ranges of K (units of one tile follow one another, so
+    // they run at the same time on different workers and add into the same tile of the output)
+    const int ksplit = a.ksplit > 1 ? a.ksplit : 1;
+    const int num_tiles = tiles_n * tiles_m * ksplit;
+    const int nk_all = (a.K + TG_BK - 1) / TG_BK, nk_unit = (nk_all + ksplit - 1) / ksplit;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
@@ -270,9 +275,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int it = 0;
             for (int tile = worker; tile < num_tiles && !failed; tile += workers) {
                 int tm, tn;
-                tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                tile_coords(tile / ksplit, tiles_m, tiles_n, tm, tn);
                 const int m0 = tm * TILE_M + rank * TG_BM, n0 = tn * OUT_COLS;
-                for (int i = 0; i < nk; ++i, ++it) {
+                const int k_first = (tile % ksplit) * nk_unit, nk = min(nk_unit, nk_all - k_first);
+                for (int i = k_first; i < k_first + nk; ++i, ++it) {
                     const int st = it % STAGES;
                     if (it >= STAGES && !mbar_wait(&s.empty[st], ((it / STAGES) - 1) & 1)) { failed = 1; break; }
                     if (CTAS == 2) {
@@ -304,6 +310,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (j >= 2 && !mbar_wait(&s.acc_empty[buf], ((j >> 1) - 1) & 1)) { failed = 2; break; }
                 tc_fence_after();
                 const unsigned acc = tmem + buf * BN;
+                const int nk = min(nk_unit, nk_all - (tile % ksplit) * nk_unit);
                 for (int i = 0; i < nk; ++i, ++it) {
                     const int st = it % STAGES;
                     if (!mbar_wait(&s.full[st], (it / STAGES) & 1)) { failed = 2; break; }
@@ -341,7 +348,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         };
         for (int tile = worker; tile < num_tiles; tile += workers, ++j) {
             int tm, tn;
-            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            tile_coords(tile / ksplit, tiles_m, tiles_n, tm, tn);
             const int m0 = tm * TILE_M + rank * TG_BM, n0 = tn * OUT_COLS;
             const int buf = j & 1;
             if (!mbar_wait(&s.acc_full[buf], (j >> 1) & 1)) { failed = 3; if (lane == 0) atomicExch(a.status, 3); break; }
@@ -557,7 +564,7 @@ static int launch_tg(const CUtensorMap &ma, const CUtensorMap &mw, const CUtenso
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: %s", cudaGetErrorString(e));
     const int out_cols = EPI == EPI_SWIGLU ? BN / 2 : BN;
-    const int tiles = ((a.N + out_cols - 1) / out_cols) * ((a.M + TG_BM - 1) / TG_BM);
+    const int tiles = ((a.N + out_cols - 1) / out_cols) * ((a.M + TG_BM - 1) / TG_BM) * (a.ksplit > 1 ? a.ksplit : 1);
     jk_launch(gemm_tcgen05_kernel<BN, EPI, 1>, dim3(tiles < sms ? tiles : sms), dim3(TG_THREADS), smem, stream, ma, mw, mo, a);
     JK_CHECK_LAUNCH("gemm_tcgen05");
     return JK_OK;
@@ -572,7 +579,7 @@ static int launch_tg_pair(const CUtensorMap &ma, const CUtensorMap &mw, const CU
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: %s", cudaGetErrorString(e));
     const int out_cols = EPI == EPI_SWIGLU ? 128 : 256;
-    const int tiles = ((a.N + out_cols - 1) / out_cols) * ((a.M + 2 * TG_BM - 1) / (2 * TG_BM));
+    const int tiles = ((a.N + out_cols - 1) / out_cols) * ((a.M + 2 * TG_BM - 1) / (2 * TG_BM)) * (a.ksplit > 1 ? a.ksplit : 1);
     // as many pairs as the device holds at once (each block takes an SM's whole shared memory)
     static int resident = 0;
     if (resident == 0) {
@@ -606,12 +613,15 @@ JK_EXPORT int jk_gemm_tcgen05_set_pairs(int mode) {      // 0, 1 (the rule above
     g_pair_mode = mode < 0 ? 0 : mode > 2 ? 2 : mode;
     return before;
 }
-static bool takes_pairs(int M, int N, int out_cols, int sms) {
+static int pair_mode() {
     if (g_pair_mode < 0) {
         const char *v = getenv("JK_GEMM_PAIR");
         g_pair_mode = v && v[0] >= '0' && v[0] <= '2' ? v[0] - '0' : 1;
     }
-    const int mode = g_pair_mode;
+    return g_pair_mode;
+}
+static bool takes_pairs(int M, int N, int out_cols, int sms) {
+    const int mode = pair_mode();
     if (mode == 0 || M <= TG_BM) return false;
     if (mode == 2) return true;
     const long long tiles = (long long)((N + out_cols - 1) / out_cols) * ((M + 2 * TG_BM - 1) / (2 * TG_BM));
@@ -640,7 +650,7 @@ JK_EXPORT int jk_gemm_tcgen05_qkv(const void *act, const void *w, int M, int K, 
     if (int rc = tensor_map_2d(act, M, K, K, TG_BM, TG_BK, 2, &ma)) return rc;
     const bool pair = takes_pairs(M, N, 256, sms);
     if (int rc = tensor_map_2d(w, N, K, K, pair ? 128 : 256, TG_BK, 2, &mw)) return rc;
-    TgArgs a{nullptr, M, N, K, N, 1.f, status, 0,
+    TgArgs a{nullptr, M, N, K, N, 1.f, status, 0, 0,
              QkvDest{(__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_pages, (__nv_bfloat16 *)v_pages, cos_table, sin_table,
                      positions, row_req, block_table, nh, nkvh, dh, page_size, max_blocks}};
     if (pair) return launch_tg_pair<EPI_QKV>(ma, mw, ma, a, sms, stream);
@@ -879,12 +889,42 @@ JK_EXPORT int jk_gemm_tcgen05(const void *act, const void *w, void *out, int M, 
     const int out_bytes = (epilogue == EPI_F32 || epilogue == EPI_RESIDUAL) ? 4 : 2;
     CUtensorMap ma, mw, mo;
     if (int rc = tensor_map_2d(act, M, K, K, TG_BM, TG_BK, 2, &ma)) return rc;
-    TgArgs a{out, M, N, K, ldo, scale, status, 0, QkvDest{}};
+    TgArgs a{out, M, N, K, ldo, scale, status, 0, 0, QkvDest{}};
     // the output goes out by TMA when its rows are 16-byte aligned, else straight from registers
     a.direct = ((size_t)ldo * out_bytes) % 16 != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0;
     if (a.direct) mo = ma;
     else if (int rc = tensor_map_2d(out, M, N, ldo, 32, 128 / out_bytes, out_bytes, &mo)) return rc;
-    const bool pair = takes_pairs(M, N, epilogue == EPI_SWIGLU ? 128 : 256, sms);
+    bool pair = takes_pairs(M, N, epilogue == EPI_SWIGLU ? 128 : 256, sms);
+    if (epilogue == EPI_RESIDUAL && !a.direct) {
+        // A product that adds itself into its output may cut K: the units of a tile add their partial products by the
+        // same TMA reduce.  Up to three cuts (JK_GEMM_KSPLIT moves the limit), chosen so that the units fill their waves,
+        // as long as a unit keeps 32 steps of K.  Measured at 768 x 4096 x 16384: 164 -> 112 us; at 1536 rows 168 -> 150 us.
+        // Four cuts of 128 tiles on 74 pairs of SMs look better on paper (seven waves of quarters against two of whole
+        // tiles) and are slower (211 against 190 us): a second wave that is three quarters empty runs faster than a full one.
+        const int nk = (K + TG_BK - 1) / TG_BK;
+        const bool pairs_possible = pair_mode() != 0 && M > TG_BM;
+        double best = 1e30;
+        int best_s = 1;
+        bool best_pair = pair;
+        for (int use_pair = 0; use_pair <= (pairs_possible ? 1 : 0); ++use_pair) {
+            const long long tiles = use_pair ? (long long)((N + 255) / 256) * ((M + 255) / 256) : (long long)((N + 255) / 256) * ((M + 127) / 128);
+            const int workers = use_pair ? sms / 2 : sms;
+            static const int max_cuts = [] { const char *v = getenv("JK_GEMM_KSPLIT"); return v ? atoi(v) : 3; }();
+            for (int sp = 1; sp <= (max_cuts < 1 ? 1 : max_cuts); ++sp) {
+                if (sp > 1 && nk / sp < 32) break;
+                const long long waves = (tiles * sp + workers - 1) / workers;
+                // time in tiles of 128 x 256 per SM; pairs do their share about 7 % faster once there is more than one
+                // wave of them (a single wave is no faster, measured); a cut costs a little
+                const double cost = (double)waves / sp * (use_pair ? (waves > 1 ? 0.93 : 1.03) : 1.0) * (1.0 + 0.03 * (sp - 1));
+                if (cost < best - 1e-9) { best = cost; best_s = sp; best_pair = use_pair != 0; }
+            }
+        }
+        if (pair_mode() == 2 && pairs_possible) best_pair = true;      // forced by a test
+        pair = best_pair;
+        a.ksplit = best_s;
+        const int nk_unit = (nk + a.ksplit - 1) / a.ksplit;
+        a.ksplit = (nk + nk_unit - 1) / nk_unit;                          // no unit without a step
+    }
     if (epilogue == EPI_SWIGLU) {
         if (int rc = tensor_map_2d(w, w_rows, K, K, 128, TG_BK, 2, &mw)) return rc;
         if (pair) return launch_tg_pair<EPI_SWIGLU>(ma, mw, mo, a, sms, stream);

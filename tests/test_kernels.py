@@ -606,7 +606,9 @@ def pairs(K, request):
     K.gemm_tcgen05_pairs(1 if before < 0 else before)
 
 
-TG_SHAPES = [(128, 256, 64), (128, 128, 128), (1, 8, 8), (300, 520, 200), (257, 100, 2304), (512, 6912, 2304), (2048, 2304, 5760)]
+TG_SHAPES = [(128, 256, 64), (128, 128, 128), (1, 8, 8), (300, 520, 200), (257, 100, 2304), (512, 6912, 2304), (2048, 2304, 5760),
+             # long K and few tiles: the residual epilogue cuts K into units that add themselves (four; two with a ragged end)
+             (512, 512, 8192), (300, 520, 4104)]
 
 
 @pytest.mark.parametrize("M,N,K_", TG_SHAPES)
