@@ -31,19 +31,10 @@
 //
 // (The reference sends these products to a library: src/models/inference_context.cpp:59-79; the
 // residual add is its beta = 1, the SwiGLU a separate operator, jiuge.cpp:236-249.)
-#include "common.cuh"
-
-#include <cuda.h>
-#include <map>
-#include <mutex>
-#include <tuple>
+#include "tcgen05.cuh"
 
 JK_DEFINE_ERROR_BUFFER(jk_gemm_tcgen05)
 
-enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_QKV = 4 };
-
-constexpr int TG_BM = 128, TG_BK = 64, TG_STAGES = 4, TG_THREADS = 192;
-constexpr unsigned TG_SPIN_LIMIT = 1u << 20;      // polls of one wait before it gives up
 
 // EPI_QKV: where the fused [q | k | v] projection's columns go (bfloat16 all).
 struct QkvDest {
@@ -69,133 +60,6 @@ struct TgArgs {
     QkvDest qkv;       // EPI_QKV only
 };
 
-// ---- PTX wrappers ------------------------------------------------------------------------------
-__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the limit is reached (the caller records where and drains).
-__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity) {
-    for (unsigned i = 0; i < TG_SPIN_LIMIT; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void *smem, const CUtensorMap *map, unsigned long long *bar, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                 ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(unsigned *slot, unsigned columns) {      // one whole warp
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(slot)), "r"(columns) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(unsigned addr, unsigned columns) {     // the same warp
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(addr), "r"(columns) : "memory");
-}
-// ---- the same for a pair of blocks (a cluster of two) that share one product: cta_group::2 ----
-__device__ __forceinline__ unsigned cluster_rank() {
-    unsigned r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
-    return r;
-}
-// The address, in the cluster's shared window, of what `p` is in block `rank` of the cluster.
-__device__ __forceinline__ unsigned cluster_addr(const void *p, unsigned rank) {
-    unsigned r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync() {      // every thread of both blocks
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-}
-// A block's own load into its own shared memory whose bytes are counted by a barrier of the pair's first block.
-__device__ __forceinline__ void tma_load_2d_pair(void *smem, const CUtensorMap *map, unsigned bar_addr, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                 ::"r"(smem_u32(smem)), "l"(map), "r"(bar_addr), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(unsigned bar_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(bar_addr) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(unsigned *slot, unsigned columns) {      // the same warp of both blocks
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(slot)), "r"(columns) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(unsigned addr, unsigned columns) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(addr), "r"(columns) : "memory");
-}
-// M = 256 over the pair: each block gives its 128 rows of A and its half of B's rows and receives its 128 rows of D.
-__device__ __forceinline__ void umma_bf16_pair(unsigned tmem_c, unsigned long long adesc, unsigned long long bdesc,
-                                               unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}\n"
-                 ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-// Arrives, once the MMAs issued so far are complete, on the barrier at this offset in both blocks of the pair.
-__device__ __forceinline__ void umma_commit_pair(unsigned long long *bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
-                 ::"r"(smem_u32(bar)), "h"((unsigned short)3) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(unsigned tmem_c, unsigned long long adesc, unsigned long long bdesc,
-                                          unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
-                 ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned long long *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(unsigned addr, unsigned (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(addr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void *smem, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
-                 ::"l"(map), "r"(smem_u32(smem)), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, const void *smem, int c0, int c1) {
-    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];\n"
-                 ::"l"(map), "r"(smem_u32(smem)), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile [rows][64 bf16] written by TMA with the
-// 128-byte swizzle: rows are 128 bytes, groups of 8 rows are 1024 bytes apart (stride byte offset),
-// the leading byte offset is unused for swizzled K-major tiles (1), version 1, layout type 2.
-__device__ __forceinline__ unsigned long long smem_desc_sw128(const void *tile) {
-    const unsigned long long addr = smem_u32(tile);
-    return ((addr & 0x3FFFFull) >> 4) | (1ull << 16) | ((1024ull >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = bn.
-__host__ __device__ constexpr unsigned instr_desc_bf16(int bn, int bm = TG_BM) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(bm >> 4) << 24);
-}
-
-// CTAS = 2: a pair of blocks works on a tile of 256 x BN; each holds its 128 rows of A and BN / 2 rows of B,
-// which leaves room for a deeper ring.
 template <int BN, int CTAS> struct TgSmem {
     static constexpr int STAGES = CTAS == 2 ? 6 : TG_STAGES;
     __nv_bfloat16 a[STAGES][TG_BM * TG_BK];          // 16 KB each, 1024-byte aligned
@@ -510,53 +374,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-// ---- host side ---------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
-// Tensor maps are kept by (pointer, shape, box, type): weights and step buffers come back with the
-// same addresses step after step.  (The reference keeps its operator descriptors in an LRU cache
-// keyed by shapes and strides: src/models/cache_manager.hpp:32-138.)
-static int tensor_map_2d(const void *ptr, int rows, int cols, int ld, int box_rows, int box_cols, int elem_bytes,
-                         CUtensorMap *out) {
-    using Key = std::tuple<const void *, int, int, int, int, int, int>;
-    static std::map<Key, CUtensorMap> cache;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    const Key key(ptr, rows, cols, ld, box_rows, box_cols, elem_bytes);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return JK_OK; }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: the driver has no cuTensorMapEncodeTiled");
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
-    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    CUtensorMap m;
-    const CUresult r = fn(&m, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                          const_cast<void *>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: cuTensorMapEncodeTiled failed with %d", (int)r);
-    if (cache.size() > 4096) cache.clear();
-    cache[key] = m;
-    *out = m;
-    return JK_OK;
-}
-
 template <int BN, int EPI>
 static int launch_tg(const CUtensorMap &ma, const CUtensorMap &mw, const CUtensorMap &mo, const TgArgs &a, int sms,
                      cudaStream_t stream) {
@@ -657,224 +474,6 @@ JK_EXPORT int jk_gemm_tcgen05_qkv(const void *act, const void *w, int M, int K, 
     return launch_tg<256, EPI_QKV>(ma, mw, ma, a, sms, stream);
 }
 
-// ---- products of few rows (decode batches, short portions): weights on the MMA's M side -------------------
-//
-// With 17 to 128 activation rows the product is bound by reading W once.  A block takes 128 rows of W (for SwiGLU
-// 64 gate rows and the 64 up rows that belong to them) and a range of K, and computes D^T[n, m] = W[n, :] . A[m, :]:
-// W tiles are the MMA's A operand (M = 128), the activation rows (padded to a multiple of 32, zero-filled by TMA)
-// its B operand (N = rows), so no tensor-core lane is spent on padding rows of a 128-row activation tile.  The first
-// tiles of W are requested before the wait on the preceding kernel (weights are never written by a step).  A thread of
-// the epilogue holds one output feature n and all rows m: for each m a warp writes 32 consecutive features.
-//   SK_STORE   out[m, n]  = acc                      float32 (one block per 128 features, all of K)
-//   SK_ADD     out[m, n] += scale * acc              float32 by red.global.add: blocks split K among themselves and
-//                                                    add their partial sums (into the residual stream, or into an
-//                                                    output that the caller zeroed)
-//   SK_SWIGLU  out[m, n]  = silu(gate) * up          bfloat16; the up half of the lanes hands its values to the gate
-//                                                    half through shared memory
-enum { SK_STORE = 0, SK_ADD = 1, SK_SWIGLU = 2 };
-constexpr int SK_MAX_STAGES = 8;
-
-struct SkArgs {
-    void *out;
-    int M, N, K, ldo;
-    float scale;
-    int *status;
-    int mpad;           // activation rows padded to a multiple of 32 (the MMA's N)
-    int stages;         // depth of the ring
-    int ksteps;         // 64-wide steps of K per block
-};
-
-template <int EPI>
-__global__ void __launch_bounds__(TG_THREADS)
-gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, SkArgs a) {
-    extern __shared__ unsigned char sk_raw[];
-    unsigned char *ring = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(sk_raw) + 1023) & ~uintptr_t(1023));
-    constexpr unsigned W_BYTES = 128 * TG_BK * sizeof(__nv_bfloat16);       // 16 KB
-    constexpr int OUT_ROWS = EPI == SK_SWIGLU ? 64 : 128;                   // output features per block
-    const unsigned act_bytes = (unsigned)a.mpad * TG_BK * sizeof(__nv_bfloat16);
-    const unsigned stage_bytes = W_BYTES + act_bytes;                       // a multiple of 1024: tiles stay aligned
-    struct Bars { unsigned long long full[SK_MAX_STAGES], empty[SK_MAX_STAGES], acc_full; unsigned tmem_base; };
-    Bars &b = *reinterpret_cast<Bars *>(ring + (size_t)a.stages * stage_bytes);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * OUT_ROWS;
-    const int nk = (a.K + TG_BK - 1) / TG_BK;
-    const int ks0 = blockIdx.y * a.ksteps;
-    const int steps = min(a.ksteps, nk - ks0);                              // >= 1 by the host's choice of the grid
-    unsigned tmem_cols = 32;
-    while ((int)tmem_cols < a.mpad) tmem_cols <<= 1;
-
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < a.stages; ++i) { mbar_init(&b.full[i], 1); mbar_init(&b.empty[i], 1); }
-        mbar_init(&b.acc_full, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    }
-    if (warp == 1) tmem_alloc(&b.tmem_base, tmem_cols);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const unsigned tmem = b.tmem_base;
-    int failed = 0;
-    pdl_trigger();
-
-    auto w_tile = [&](int st) { return ring + (size_t)st * stage_bytes; };
-    auto a_tile = [&](int st) { return ring + (size_t)st * stage_bytes + W_BYTES; };
-    if (warp == 0) {
-        if (lane == 0) {
-            auto load_w = [&](int i) {
-                const int st = i % a.stages, kc = (ks0 + i) * TG_BK;
-                mbar_expect_tx(&b.full[st], stage_bytes);
-                if (EPI == SK_SWIGLU) {
-                    tma_load_2d(w_tile(st), &map_w, &b.full[st], kc, n0);
-                    tma_load_2d(w_tile(st) + W_BYTES / 2, &map_w, &b.full[st], kc, a.N + n0);
-                } else {
-                    tma_load_2d(w_tile(st), &map_w, &b.full[st], kc, n0);
-                }
-            };
-            const int ahead = min(steps, a.stages);
-            for (int i = 0; i < ahead; ++i) load_w(i);                     // weights: nothing to wait for
-            pdl_wait();                                                    // the activations come from the kernel before
-            for (int i = 0; i < ahead; ++i) tma_load_2d(a_tile(i), &map_a, &b.full[i], (ks0 + i) * TG_BK, 0);
-            for (int i = ahead; i < steps; ++i) {
-                const int st = i % a.stages;
-                if (!mbar_wait(&b.empty[st], ((i / a.stages) - 1) & 1)) { failed = 1; break; }
-                load_w(i);
-                tma_load_2d(a_tile(st), &map_a, &b.full[st], (ks0 + i) * TG_BK, 0);
-            }
-            if (failed) atomicExch(a.status, 1);
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            const unsigned idesc = instr_desc_bf16(a.mpad);
-            for (int i = 0; i < steps; ++i) {
-                const int st = i % a.stages;
-                if (!mbar_wait(&b.full[st], (i / a.stages) & 1)) { failed = 2; break; }
-                tc_fence_after();
-                const unsigned long long wd = smem_desc_sw128(w_tile(st)), ad = smem_desc_sw128(a_tile(st));
-#pragma unroll
-                for (int k = 0; k < TG_BK / 16; ++k) umma_bf16(tmem, wd + 2 * k, ad + 2 * k, idesc, (i | k) ? 1u : 0u);
-                umma_commit(&b.empty[st]);
-            }
-            if (!failed) umma_commit(&b.acc_full);
-            else atomicExch(a.status, 2);
-        }
-    } else {
-        const int quarter = warp & 3;                                      // lanes (features) quarter * 32 ... of the accumulator
-        pdl_wait();                                                        // before this block's first global write
-        if (!mbar_wait(&b.acc_full, 0)) {
-            failed = 3;
-            if (lane == 0) atomicExch(a.status, 3);
-        }
-        tc_fence_after();
-        const unsigned acc = tmem + ((unsigned)(quarter * 32) << 16);
-        if (EPI == SK_SWIGLU) {
-            // lanes 0..63 hold gate rows, lanes 64..127 the up rows of the same features; the ring is free
-            // (every MMA that read it has completed) and carries the up values over: [row m][feature 0..63]
-            float *xch = reinterpret_cast<float *>(ring);
-            if (quarter >= 2 && !failed) {
-                for (int c0 = 0; c0 < a.mpad; c0 += 32) {
-                    unsigned v[32];
-                    tmem_ld32(acc + c0, v);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) xch[(c0 + i) * 64 + (quarter - 2) * 32 + lane] = __uint_as_float(v[i]);
-                }
-            }
-            asm volatile("bar.sync 1, 128;\n" ::: "memory");             // the four epilogue warps, whatever their wait said
-            if (quarter < 2 && !failed) {
-                const int n = n0 + quarter * 32 + lane;
-                __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(a.out);
-                for (int c0 = 0; c0 < a.mpad; c0 += 32) {
-                    unsigned v[32];
-                    tmem_ld32(acc + c0, v);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int m = c0 + i;
-                        const float g = __uint_as_float(v[i]), u = xch[m * 64 + quarter * 32 + lane];
-                        if (m < a.M && n < a.N) out[(size_t)m * a.ldo + n] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
-                    }
-                }
-            }
-        } else if (!failed) {
-            const int n = n0 + quarter * 32 + lane;
-            float *out = reinterpret_cast<float *>(a.out);
-            for (int c0 = 0; c0 < a.mpad; c0 += 32) {
-                unsigned v[32];
-                tmem_ld32(acc + c0, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int m = c0 + i;
-                    if (m < a.M && n < a.N) {
-                        if (EPI == SK_ADD) atomicAdd(out + (size_t)m * a.ldo + n, a.scale * __uint_as_float(v[i]));
-                        else out[(size_t)m * a.ldo + n] = __uint_as_float(v[i]);
-                    }
-                }
-            }
-        }
-    }
-    if (failed && lane == 0) {
-        for (int st = 0; st < a.stages; ++st) mbar_wait(&b.full[st], 0);
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    if (warp == 1) tmem_dealloc(tmem, tmem_cols);
-}
-
-// 17 to 128 rows (fewer are taken too: the weight-streaming kernels of linear_small.cu are the better home for up to
-// 16 rows unless K is beyond what they hold in shared memory).
-JK_EXPORT int jk_gemm_skinny_supports(int M, int N, int K) { return M >= 1 && M <= 128 && N >= 1 && K >= 8 && K % 8 == 0; }
-
-// epilogue: EPI_F32 (out = product, float32), EPI_RESIDUAL (out += scale * product, float32), EPI_SWIGLU (w is
-// [2N, K]; out = silu(gate) * up, bfloat16).
-JK_EXPORT int jk_gemm_skinny(const void *act, const void *w, void *out, int M, int N, int K, int ldo, int epilogue, float scale,
-                             int *status, int sms, cudaStream_t stream) {
-    JK_REQUIRE(jk_gemm_skinny_supports(M, N, K), "gemm_skinny: M %d N %d K %d (1 to 128 rows, K a multiple of 8)", M, N, K);
-    JK_REQUIRE(epilogue == EPI_F32 || epilogue == EPI_RESIDUAL || epilogue == EPI_SWIGLU, "gemm_skinny: epilogue %d", epilogue);
-    JK_REQUIRE(ldo >= N && status != nullptr && out != nullptr, "gemm_skinny: output stride %d < N %d, or a pointer is missing", ldo, N);
-    JK_REQUIRE((reinterpret_cast<uintptr_t>(act) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
-               "gemm_skinny: operands must be 16-byte aligned");
-    if (sms <= 0) sms = 148;
-    SkArgs a{out, M, N, K, ldo, scale, status, (M + 31) / 32 * 32, 0, 0};
-    const int out_rows = epilogue == EPI_SWIGLU ? 64 : 128;
-    const int tiles = (N + out_rows - 1) / out_rows;
-    const int nk = (K + TG_BK - 1) / TG_BK;
-    // two blocks fit an SM; K is split until the blocks fill the SMs twice over, as long as each keeps 8 steps
-    int splits = 1;
-    if (epilogue != EPI_SWIGLU) {
-        splits = 2 * sms / tiles;
-        if (splits > nk / 8) splits = nk / 8;
-        if (splits < 1) splits = 1;
-    }
-    a.ksteps = (nk + splits - 1) / splits;
-    splits = (nk + a.ksteps - 1) / a.ksteps;                              // no block without a step
-    const size_t stage = 128 * TG_BK * 2 + (size_t)a.mpad * TG_BK * 2;
-    a.stages = (int)((100 * 1024) / stage);                               // two blocks' rings per SM
-    if (a.stages > SK_MAX_STAGES) a.stages = SK_MAX_STAGES;
-    if (a.stages > a.ksteps) a.stages = a.ksteps < 2 ? 2 : a.ksteps;
-    const size_t smem = a.stages * stage + 256 + 1024;
-    CUtensorMap mw, ma;
-    if (int rc = tensor_map_2d(w, epilogue == EPI_SWIGLU ? 2 * N : N, K, K, out_rows, TG_BK, 2, &mw)) return rc;
-    if (int rc = tensor_map_2d(act, M, K, K, a.mpad, TG_BK, 2, &ma)) return rc;
-    int kind = epilogue == EPI_SWIGLU ? SK_SWIGLU : epilogue == EPI_RESIDUAL ? SK_ADD : SK_STORE;
-    if (kind == SK_STORE && splits > 1) {
-        // partial sums of the blocks that share an output tile are added into a zeroed output
-        const cudaError_t e = cudaMemset2DAsync(out, (size_t)ldo * 4, 0, (size_t)N * 4, M, stream);
-        if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "gemm_skinny: %s", cudaGetErrorString(e));
-        kind = SK_ADD;
-        a.scale = 1.f;
-    }
-    auto launch = [&](auto kernel) -> int {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024 + 2048);
-        if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "gemm_skinny: %s", cudaGetErrorString(e));
-        jk_launch(kernel, dim3(tiles, splits), dim3(TG_THREADS), smem, stream, mw, ma, a);
-        JK_CHECK_LAUNCH("gemm_skinny");
-        return JK_OK;
-    };
-    if (kind == SK_SWIGLU) return launch(gemm_skinny_kernel<SK_SWIGLU>);
-    if (kind == SK_ADD) return launch(gemm_skinny_kernel<SK_ADD>);
-    return launch(gemm_skinny_kernel<SK_STORE>);
-}
-
-// K must keep rows 16-byte aligned for TMA; everything else is free.
 JK_EXPORT int jk_gemm_tcgen05_supports(int M, int N, int K) { return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0; }
 
 JK_EXPORT int jk_gemm_tcgen05(const void *act, const void *w, void *out, int M, int N, int K, int ldo, int epilogue,

@@ -26,13 +26,13 @@ MODULES: Dict[str, List[str]] = {
     "attention": ["attention.cu"],
     "sampling": ["sampling.cu"],
     "linear_small": ["linear_small.cu"],
-    "gemm_tcgen05": ["gemm_tcgen05.cu"],
+    "gemm_tcgen05": ["gemm_tcgen05.cu", "gemm_skinny.cu"],
     "attention_tcgen05": ["attention_tcgen05.cu"],
     "runner": ["runner.cu", "capi.cu"],
 }
 # libraries a module links against (the others need the CUDA runtime only)
 LINK: Dict[str, List[str]] = {"runner": ["-lcublas"]}
-HEADERS = ["common.cuh", "attention_static_scratch.h", "runner.h", "model_api.h"]
+HEADERS = ["common.cuh", "attention_static_scratch.h", "runner.h", "model_api.h", "tcgen05.cuh"]
 
 # -use_fast_math is deliberately absent: expf, division and sqrt stay accurate.
 NVCC_FLAGS = [
