@@ -23,6 +23,27 @@ def test_the_header_is_plain_c(tmp_path):
     subprocess.run([cc, "-std=c99", "-Wall", "-Werror", "-fsyntax-only", str(src)], check=True)
 
 
+@pytest.mark.gpu
+def test_a_c_program_runs_the_engine_without_python(tmp_path):
+    """tests/c_api_program.c, compiled by the C compiler against csrc/model_api.h and linked with the runner's shared
+    object only: it finds the kernel modules in the build folder itself, runs a prompt whole and in pieces, generates
+    a few tokens, and exits 0 if the two ways of cutting agree and no page was lost."""
+    from infinicore_infer_b200.kernels import build
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    for module in build.MODULES:
+        build.build(module)
+    folder = build.build_dir()
+    here = os.path.dirname(os.path.abspath(__file__))
+    exe = str(tmp_path / "prog")
+    subprocess.run([cc, "-std=c99", "-Wall", "-I", os.path.dirname(HEADER), os.path.join(here, "c_api_program.c"), "-o", exe,
+                    "-L", folder, "-ljk_runner", f"-Wl,-rpath,{folder}", "-lm"], check=True)
+    run = subprocess.run([exe, folder], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert "greedy:" in run.stdout and "largest difference" in run.stdout
+
+
 def native(models, name, **kw):
     from infinicore_infer_b200.engine.native_model import NativeModel
     kw.setdefault("page_size", 16)
