@@ -195,10 +195,8 @@ int bind_from_directory(JkModel *m, const char *dir, bool need_gemm_tcgen05, boo
     return jk_runner_bind(&f);
 }
 
-bool takes_tcgen05(const RunnerModel &m, int rows, int n, int k) {      // the runner's own rule, for the binding
-    if (rows <= 16 || k % 8) return false;
-    if (rows < m.tcgen05_min_rows && (long long)((rows + 127) / 128) * ((n + 255) / 256) < 3LL * m.sms) return false;
-    return (long long)((rows + 127) / 128) * ((n + 127) / 128) >= m.tcgen05_min_tiles;
+bool takes_tcgen05(const RunnerModel &m, int rows, int n, int k) {
+    return runner_takes_tcgen05(m.sms, m.tcgen05_min_rows, m.tcgen05_min_tiles, m.tcgen05_min_fill_pct, rows, n, k);
 }
 
 // The gemm_tcgen05 module is loaded if a step can reach one of its kernels: the tiled one under the runner's
@@ -288,8 +286,9 @@ int create(JkModel *m, const JkModelMeta *meta, const JkModelWeights *w, const J
     rm.num_pages = (int)m->num_pages + 1;
     rm.window = 0;
     rm.sms = prop.multiProcessorCount;
-    rm.tcgen05_min_rows = 1024;      // below this many rows the library's product is faster (measured), but for very wide outputs
-    rm.tcgen05_min_tiles = 96;
+    rm.tcgen05_min_rows = 129;       // the routing's measured thresholds: see runner_takes_tcgen05
+    rm.tcgen05_min_tiles = 200;
+    rm.tcgen05_min_fill_pct = 80;
     rm.attention_tcgen05 = tcgen05_attention_takes(dh, m->page_size);
     rm.fused_norms = getenv("JK_NO_FUSED_NORM") == nullptr || getenv("JK_NO_FUSED_NORM")[0] != '1';
     rm.embed_dtype = JK_BF16;
@@ -511,7 +510,7 @@ JK_EXPORT int jkKernelModules(const JkModelMeta *meta, const JkModelOptions *opt
     RunnerModel rm{};
     rm.hidden = meta->d; rm.heads = meta->nh; rm.kv_heads = meta->nkvh; rm.head_dim = meta->dh; rm.intermediate = meta->di;
     rm.vocab = meta->dvoc;
-    rm.sms = 148; rm.tcgen05_min_rows = 1024; rm.tcgen05_min_tiles = 96;
+    rm.sms = 148; rm.tcgen05_min_rows = 129; rm.tcgen05_min_tiles = 200; rm.tcgen05_min_fill_pct = 80;
     int device = 0;
     cudaDeviceProp prop;
     if (cudaGetDevice(&device) == cudaSuccess && cudaGetDeviceProperties(&prop, opt ? opt->device : device) == cudaSuccess)

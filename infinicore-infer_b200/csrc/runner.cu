@@ -85,11 +85,7 @@ static int lt_product(const void *act, const void *w, float *out, int M, int N, 
 }
 
 static bool takes_tcgen05(const RunnerModel &m, int rows, int n, int k) {
-    if (rows <= 16 || k % 8 || g_fns.gemm_tcgen05 == nullptr) return false;
-    // fewer rows are taken only if the output is so wide that its tiles make several waves all the same
-    if (rows < m.tcgen05_min_rows && (long long)((rows + 127) / 128) * ((n + 255) / 256) < 3LL * m.sms) return false;
-    const long long tiles = (long long)((rows + 127) / 128) * ((n + 127) / 128);
-    return tiles >= m.tcgen05_min_tiles;
+    return g_fns.gemm_tcgen05 != nullptr && runner_takes_tcgen05(m.sms, m.tcgen05_min_rows, m.tcgen05_min_tiles, m.tcgen05_min_fill_pct, rows, n, k);
 }
 
 // Which kernel takes a product of at most 128 rows (the same rule as Runtime.few_rows_route of the parts): the

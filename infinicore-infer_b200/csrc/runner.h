@@ -67,7 +67,7 @@ struct RunnerFns {
 struct RunnerModel {
     int layers, hidden, heads, kv_heads, head_dim, intermediate, vocab;
     int page_size, max_blocks, num_pages, window;
-    int sms, tcgen05_min_rows, tcgen05_min_tiles;
+    int sms, tcgen05_min_rows, tcgen05_min_tiles, tcgen05_min_fill_pct;
     int skinny_min_blocks;          // fewest blocks for which the few-rows tcgen05 kernel is used (0: one per SM)
     int fused_norms;                // 1: steps of at most 16 rows run without norm kernels where the small-row kernels allow
     int attention_tcgen05;          // 1: tiles go to the tcgen05 attention kernel, 0: to the mma.sync kernel
@@ -110,6 +110,19 @@ struct RunnerScratch {
     long long workspace_bytes;
     unsigned long long *sumsq;      // [2 * layers, 16] fixed-point sums of squares of the rows before each norm
 };
+
+// Whether the tiled tcgen05 product takes a product of `rows` x `n` over `k` (the same rule as Runtime.takes_tcgen05 of
+// the parts).  Measured on the 1B, 2B and 8B shapes against the library's product with separate elementwise kernels:
+// from `min_rows` rows on, a product with at least `min_tiles` output tiles of 128 x 128 whose rows fill their tiles of
+// 128 to `min_fill_pct` per cent (80) is as fast or faster here (fused epilogues, dependent launch); products of fewer tiles go to
+// the library, whose smaller tiles and cuts of K fill the SMs better.  Very wide outputs (the logits) are taken from 17 rows.
+static inline bool runner_takes_tcgen05(int sms, int min_rows, int min_tiles, int min_fill_pct, int rows, int n, int k) {
+    if (rows <= 16 || k % 8) return false;
+    const long long row_tiles = (rows + 127) / 128;
+    if (row_tiles * ((n + 255) / 256) >= 3LL * sms) return true;
+    if (rows < min_rows || rows * 100LL < (long long)min_fill_pct * row_tiles * 128) return false;
+    return row_tiles * ((n + 127) / 128) >= min_tiles;
+}
 
 // Blocks that the few-rows tcgen05 kernel (jk_gemm_skinny) starts for a product with `n` output features over `k`:
 // tiles of 128 features (64 for SwiGLU, whose tile holds as many up rows again); a product that is added into

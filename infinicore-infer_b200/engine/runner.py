@@ -36,7 +36,7 @@ class _Model(ctypes.Structure):
     _fields_ = ([(n, ctypes.c_int) for n in (
         "layers", "hidden", "heads", "kv_heads", "head_dim", "intermediate", "vocab",
         "page_size", "max_blocks", "num_pages", "window",
-        "sms", "tcgen05_min_rows", "tcgen05_min_tiles", "skinny_min_blocks", "fused_norms", "attention_tcgen05", "embed_dtype")]
+        "sms", "tcgen05_min_rows", "tcgen05_min_tiles", "tcgen05_min_fill_pct", "skinny_min_blocks", "fused_norms", "attention_tcgen05", "embed_dtype")]
                 + [(n, ctypes.c_float) for n in ("embed_scale", "residual_scale", "logit_scale", "softmax_scale", "final_eps")]
                 + [(n, ctypes.c_void_p) for n in ("embedding", "lm_head", "final_norm", "cos_table", "sin_table", "status")])
 
@@ -158,7 +158,8 @@ class NativeRunner:
             layers=len(model.layers), hidden=d, heads=a.num_heads, kv_heads=a.num_kv_heads, head_dim=dh, intermediate=di,
             vocab=spec.vocab_size, page_size=cache.page_size, max_blocks=cache.max_blocks, num_pages=k0.shape[0],
             window=a.window or 0, sms=kernels._sm_count(dev), tcgen05_min_rows=rt.tcgen05_min_rows,
-            tcgen05_min_tiles=rt.tcgen05_min_tiles, skinny_min_blocks=rt.skinny_min_blocks or 0,
+            tcgen05_min_tiles=rt.tcgen05_min_tiles, tcgen05_min_fill_pct=rt.tcgen05_min_fill_pct,
+            skinny_min_blocks=rt.skinny_min_blocks or 0,
             fused_norms=1 if rt.fused_norms else 0,
             attention_tcgen05=1 if self._attention_tcgen05 else 0,
             embed_dtype=kernels.dtype_code(model.embedding.dtype), embed_scale=spec.embed_scale,
@@ -166,7 +167,7 @@ class NativeRunner:
             final_eps=model.final_norm.spec.eps, embedding=model.embedding.data_ptr(), lm_head=model.lm_head.data_ptr(),
             final_norm=model.final_norm.weight.data_ptr(), cos_table=pos.cos.data_ptr() if pos else 0,
             sin_table=pos.sin.data_ptr() if pos else 0, status=kernels.gemm_status(dev).data_ptr())
-        self._routing = (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.skinny_min_blocks, rt.fused_norms)
+        self._routing = (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.tcgen05_min_fill_pct, rt.skinny_min_blocks, rt.fused_norms)
         self._layers = (_Layer * len(model.layers))()
         for i, blk in enumerate(model.layers):
             view = cache.views[spec.order[i].cache]
@@ -237,8 +238,10 @@ class NativeRunner:
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Logits (float32 ``[n_want, vocab]``) of the step that ``ctx`` describes."""
         rt = self.runtime
-        if (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.skinny_min_blocks, rt.fused_norms) != self._routing:       # a test moved the thresholds
-            self._routing = (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.skinny_min_blocks, rt.fused_norms)
+        now = (rt.tcgen05_min_rows, rt.tcgen05_min_tiles, rt.tcgen05_min_fill_pct, rt.skinny_min_blocks, rt.fused_norms)
+        if now != self._routing:       # a test moved the thresholds
+            self._routing = now
+            self._model.tcgen05_min_fill_pct = rt.tcgen05_min_fill_pct
             self._model.fused_norms = 1 if rt.fused_norms else 0
             self._model.tcgen05_min_rows, self._model.tcgen05_min_tiles = rt.tcgen05_min_rows, rt.tcgen05_min_tiles
             self._model.skinny_min_blocks = rt.skinny_min_blocks or 0

@@ -68,8 +68,11 @@ class Runtime:
         self.plain_attention = False      # True: bfloat16 attention through the row kernel too
         self.library_products_only = False   # True: every bfloat16 product goes to the library
         self.legacy_tensor_cores = False     # True: prefill attention on mma.sync even where tcgen05 is built
-        self.tcgen05_min_tiles = 96          # fewest 128x128 output tiles for which the tcgen05 kernel is used
-        self.tcgen05_min_rows = 1024         # ... and fewest rows: below, the library's split-K kernels win
+        # the tiled tcgen05 product takes a product from this many rows, output tiles of 128 x 128 and per cent of its
+        # rows of tiles filled (takes_tcgen05 says where the numbers come from)
+        self.tcgen05_min_rows = 129
+        self.tcgen05_min_tiles = 200
+        self.tcgen05_min_fill_pct = 80
         self.skinny_min_blocks: Optional[int] = None   # fewest blocks for the few-rows tcgen05 kernel (None: one per SM)
         # the native runner runs steps of at most 16 rows without norm kernels (the products around a norm share its
         # work: csrc/linear_small.cu, SmallNormFuse); JK_NO_FUSED_NORM=1 keeps the norm kernels
@@ -161,19 +164,21 @@ class Runtime:
         return "skinny" if skinny else "library"
 
     def takes_tcgen05(self, m: int, n: int, k: int) -> bool:
-        """The tcgen05 kernel works on 128 x 256 tiles with one block per SM: it takes a product that has
-        enough rows and tiles to keep every SM on full tiles (measured on the 2B shape: level with the
-        library, epilogue fusions included, from about a thousand rows; at a few hundred rows the
-        library's smaller tiles and split K are up to twice as fast)."""
+        """Whether the tiled tcgen05 product takes this product (the same rule as runner_takes_tcgen05 in csrc/runner.h).
+        Measured on the 1B, 2B and 8B shapes, whole steps of 160 to 2,048 rows against the library's product with
+        separate elementwise kernels: a product with at least 200 output tiles of 128 x 128 whose rows fill their
+        tiles of 128 to four fifths is as fast or faster here (fused epilogues, dependent launch, cuts of K for the
+        products that add into the residual stream); products of fewer tiles go to the library, whose smaller tiles
+        fill the SMs better.  Very wide outputs (the logits) are taken from 17 rows."""
         from .. import kernels
-        if self.dtype != torch.bfloat16 or self.library_products_only or m <= 16:
+        if self.dtype != torch.bfloat16 or self.library_products_only or m <= 16 or not kernels.gemm_tcgen05_supports(m, n, k):
             return False
-        # fewer rows are taken only if the output is so wide that its tiles make several waves all the same
-        # (the output matrix over the vocabulary)
-        if m < self.tcgen05_min_rows and -(-m // 128) * -(-n // 256) < 3 * kernels._sm_count(self.device):
+        row_tiles = -(-m // 128)
+        if row_tiles * -(-n // 256) >= 3 * kernels._sm_count(self.device):
+            return True
+        if m < self.tcgen05_min_rows or m * 100 < self.tcgen05_min_fill_pct * row_tiles * 128:
             return False
-        tiles = -(-m // 128) * -(-n // 128)
-        return tiles >= self.tcgen05_min_tiles and kernels.gemm_tcgen05_supports(m, n, k)
+        return row_tiles * -(-n // 128) >= self.tcgen05_min_tiles
 
     def fuses_residual(self, m: int, n: int, k: int) -> bool:
         return self.few_rows_route(m, n, k, "residual") == "skinny" or self.takes_tcgen05(m, n, k)

@@ -100,6 +100,7 @@ def test_every_product_kernel_gives_the_same_model(tiny_models, name):
         if mode == "tcgen05":
             eng.runtime.tcgen05_min_tiles = 1
             eng.runtime.tcgen05_min_rows = 17
+            eng.runtime.tcgen05_min_fill_pct = 0
         elif mode == "few rows":
             eng.runtime.skinny_min_blocks = 1
         else:
@@ -126,6 +127,7 @@ def test_the_tcgen05_kernels_carry_a_whole_model(tiny_models, product_pairs):
     eng = make_engine(tiny_models["D"][0], "bfloat16", 1024)
     eng.runtime.tcgen05_min_tiles = 1
     eng.runtime.tcgen05_min_rows = 17
+    eng.runtime.tcgen05_min_fill_pct = 0
     toks, want = expected(tiny_models, "D", 400, 300)
     toks2, want2 = expected(tiny_models, "D", 401, 150)
     for what, steps in (("whole", whole("r", toks)), ("portions", portions("r", toks, sizes=(140, 2, 129, 20, 9))),
