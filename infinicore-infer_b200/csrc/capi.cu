@@ -337,9 +337,11 @@ int create(JkModel *m, const JkModelMeta *meta, const JkModelWeights *w, const J
         const size_t bytes = m->page_bytes * (size_t)rm.num_pages;
         if (int rc = device_alloc(m, &y.k_pages, bytes, "key pages")) return rc;
         if (int rc = device_alloc(m, &y.v_pages, bytes, "value pages")) return rc;
-        // page 0 is read by padding; the others are written before they are read
-        CUDA_TRY(cudaMemset(y.k_pages, 0, m->page_bytes), "key pages");
-        CUDA_TRY(cudaMemset(y.v_pages, 0, m->page_bytes), "value pages");
+        // Every page starts as zeros.  Page 0 is read by padding rows; of the others a kernel that loads whole pages
+        // (the tcgen05 attention, by TMA) also reads the slots beyond a request's last position, with weight 0 in
+        // the P V product: what lies there must be finite, and memory that cudaMalloc hands back need not be.
+        CUDA_TRY(cudaMemset(y.k_pages, 0, bytes), "key pages");
+        CUDA_TRY(cudaMemset(y.v_pages, 0, bytes), "value pages");
     }
     m->free_pages.reserve(m->num_pages);
     for (long long p = m->num_pages; p >= 1; --p) m->free_pages.push_back((int)p);      // low pages go out first

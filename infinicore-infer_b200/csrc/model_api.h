@@ -28,7 +28,7 @@ typedef struct {
     float theta;                      /* rotary base; <= 0: no position encoding */
     float embed_scale;                /* embedding rows are multiplied by this (scale_emb; 1 if unscaled) */
     float residual_scale;             /* each branch is multiplied by this before it is added (scale_depth / sqrt(nlayer)) */
-    float logit_scale;                /* the final norm's output is multiplied by this (1 / (d / dim_model_base)) */
+    float logit_scale;                /* the final norm's output is multiplied by this (d / dim_model_base as an integer quotient, i.e. hidden_size // dim_model_base; 1 if unscaled) */
     int32_t end_token;
 } JkModelMeta;
 

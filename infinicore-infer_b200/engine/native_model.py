@@ -55,7 +55,7 @@ class NativeModel:
     """A model created through the C interface from host tensors named as in the checkpoint."""
 
     def __init__(self, config, tensors: Dict[str, torch.Tensor], device: int = 0, page_size: int = 64,
-                 cache_tokens: Optional[int] = None, max_step_tokens: int = 2048):
+                 cache_tokens: Optional[int] = None, max_step_tokens: int = 2048, strict: bool = False):
         spec = config.model_spec()
         blocks = [spec.layers[e.layer] for e in spec.order]
         a, f = blocks[0].mixer, blocks[0].feed_forward
@@ -76,31 +76,37 @@ class NativeModel:
         lib.jkDropKVCache.restype = None
         lib.jkDestroyModel.restype = None
 
-        def host(name: str, dtype) -> torch.Tensor:
-            return tensors[name].to(dtype).contiguous()
-
+        # The same checks and the same packing as the Python engine's: the manifest of the model's parts decides what
+        # the checkpoint must hold, and the parts' own ``pack`` functions fuse q | k | v and gate | up.
+        from ..parts import model_manifest, part_class
+        from ..weights import VECTOR, DictWeights, check_manifest
+        check_manifest(model_manifest(spec), {n: tuple(t.shape) for n, t in tensors.items()}, strict=strict)
+        source = DictWeights(tensors, torch.bfloat16, "cpu")
         keep: List[torch.Tensor] = []          # what the pointers below point into
 
         def mat(t: torch.Tensor) -> int:
             keep.append(t)
             return t.data_ptr()
 
-        def per_layer(make) -> ctypes.Array:
-            return (ctypes.c_void_p * L)(*[mat(make(spec.layer_prefix.format(e.layer), spec.layers[e.layer])) for e in spec.order])
+        packed = []
+        for e in spec.order:
+            b, p = spec.layers[e.layer], spec.layer_prefix.format(e.layer)
+            one = dict(part_class("mixer", b.mixer).pack(b.mixer, source, p + b.mixer_prefix))
+            one.update(part_class("feed_forward", b.feed_forward).pack(b.feed_forward, source, p + b.ffn_prefix))
+            one["norm1"] = source.get(p + b.mixer_norm_prefix + "weight", VECTOR)
+            one["norm2"] = source.get(p + b.ffn_norm_prefix + "weight", VECTOR)
+            packed.append(one)
 
-        bf, f32 = torch.bfloat16, torch.float32
-        embd = mat(host(spec.embed_name, bf))
-        tied = spec.tie_embeddings or spec.lm_head_name not in tensors
+        def per_layer(key: str) -> ctypes.Array:
+            return (ctypes.c_void_p * L)(*[mat(one[key]) for one in packed])
+
+        embd = mat(source.get(spec.embed_name))
+        tied = not source.has(spec.lm_head_name)
         w = _Weights(
-            norm_dtype=0, input_embd=embd, output_norm=mat(host(spec.final_norm_prefix + "weight", f32)),
-            output_embd=embd if tied else mat(host(spec.lm_head_name, bf)),
-            attn_norm=per_layer(lambda p, b: host(p + b.mixer_norm_prefix + "weight", f32)),
-            attn_qkv=per_layer(lambda p, b: torch.cat([host(p + b.mixer_prefix + f"{n}_proj.weight", bf) for n in "qkv"]).contiguous()),
-            attn_o=per_layer(lambda p, b: host(p + b.mixer_prefix + "o_proj.weight", bf)),
-            ffn_norm=per_layer(lambda p, b: host(p + b.ffn_norm_prefix + "weight", f32)),
-            ffn_gate_up=per_layer(lambda p, b: torch.cat([host(p + b.ffn_prefix + "gate_proj.weight", bf),
-                                                          host(p + b.ffn_prefix + "up_proj.weight", bf)]).contiguous()),
-            ffn_down=per_layer(lambda p, b: host(p + b.ffn_prefix + "down_proj.weight", bf)))
+            norm_dtype=0, input_embd=embd, output_norm=mat(source.get(spec.final_norm_prefix + "weight", VECTOR)),
+            output_embd=embd if tied else mat(source.get(spec.lm_head_name)),
+            attn_norm=per_layer("norm1"), attn_qkv=per_layer("w_qkv"), attn_o=per_layer("w_o"),
+            ffn_norm=per_layer("norm2"), ffn_gate_up=per_layer("w_gate_up"), ffn_down=per_layer("w_down"))
         meta = _Meta(nlayer=L, d=spec.hidden_size, nh=a.num_heads, nkvh=a.num_kv_heads, dh=a.head_dim,
                      di=f.intermediate_size, dctx=spec.max_positions, dvoc=spec.vocab_size, epsilon=blocks[0].mixer_norm.eps,
                      theta=a.position.theta if a.position is not None else 0.0, embed_scale=spec.embed_scale,

@@ -182,14 +182,20 @@ class NativeRunner:
         self._buffers = dict(x=f32(T, d), h=b16(T, d), qkv=f32(T, nq), q=b16(T, a.num_heads * dh), o=b16(T, a.num_heads * dh),
                              delta=f32(T, d), gate_up=f32(T, 2 * di), act=b16(T, di), hw=b16(T, d),
                              workspace=torch.empty(32 << 20, dtype=torch.uint8, device=dev))
-        self._decode_scratch = f32(1)
+        self._max_positions = a.position.max_positions if a.position else 1 << 20
+        # The split-key attention's scratch, sized once for the worst step: captured decode steps keep its address,
+        # so it must never move (rows x heads x splits x (head size + 2) floats; more rows mean fewer splits).
+        sms, worst = kernels._sm_count(dev), 1
+        for rows in range(1, T + 1):
+            splits = kernels.attention_decode_splits(rows, a.num_kv_heads, a.num_heads // a.num_kv_heads,
+                                                     a.window or self._max_positions, sms, dh)
+            if splits > 1:
+                worst = max(worst, rows * a.num_heads * splits * (dh + 2))
+        self._decode_scratch = f32(worst)
         self._sumsq = torch.zeros(2 * len(model.layers), 16, dtype=torch.int64, device=dev)
         self._scratch = _Scratch(workspace_bytes=32 << 20, decode_scratch=self._decode_scratch.data_ptr(),
                                  sumsq=self._sumsq.data_ptr(),
                                  **{k: v.data_ptr() for k, v in self._buffers.items()})
-        self._max_positions = a.position.max_positions if a.position else 1 << 20
-        self._attn_lib = _build.load("attention")
-        self._attn_lib.jk_attention_decode_scratch_floats.restype = ctypes.c_longlong
         self.launches = 0
 
     def _bind(self) -> None:
@@ -254,11 +260,8 @@ class NativeRunner:
         if ctx.n_short:
             splits = kernels.attention_decode_splits(ctx.n_short, nkvh, nh // nkvh, self._model.window or self._max_positions,
                                                      kernels._sm_count(rt.device), dh)
-            need = self._attn_lib.jk_attention_decode_scratch_floats(ctypes.c_int(ctx.n_short), ctypes.c_int(nh), ctypes.c_int(dh),
-                                                                     ctypes.c_int(splits))
-            if need > self._decode_scratch.numel():
-                self._decode_scratch = torch.empty(need, dtype=torch.float32, device=rt.device)
-                self._scratch.decode_scratch = self._decode_scratch.data_ptr()
+            if splits > 1 and ctx.n_short * nh * splits * (dh + 2) > self._decode_scratch.numel():
+                raise kernels.KernelError("the split-key attention needs more scratch than was sized for the largest step")
         n_want = ctx.want_rows.numel()
         logits = torch.empty(n_want, self.vocab_size, dtype=torch.float32, device=rt.device)
         table = ctx.block_tables[0]

@@ -70,16 +70,19 @@ class Engine:
 
     def __init__(self, spec, weights, dtype: torch.dtype = torch.bfloat16, device="cuda:0",
                  cache_tokens: int = 4096, page_size: int = 16, max_requests: int = 64,
-                 max_step_tokens: int = 8192, use_graphs: bool = True, native_runner: bool = True):
+                 max_step_tokens: int = 8192, use_graphs: bool = True, native_runner: bool = True,
+                 strict_weights: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
         self.spec = spec
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
         self.runtime = Runtime(dtype, self.device)
-        shapes = weights.shapes()
-        check_manifest(model_manifest(spec), shapes, where=getattr(weights, "model_dir", ""))
+        manifest = model_manifest(spec)
+        check_manifest(manifest, weights.shapes(), where=getattr(weights, "model_dir", ""), strict=strict_weights)
+        weights.plan(manifest)
         self.model = Model(spec, weights, self.runtime)
+        weights.close()
         num_pages = (cache_tokens + page_size - 1) // page_size
         self.cache = CacheManager(cache_needs(spec), num_pages, page_size, max_requests,
                                   spec.max_positions, dtype=dtype, device=self.device)

@@ -8,7 +8,7 @@ head h // (num_heads / num_kv_heads) (jiuge.cpp:210-211).
 """
 from __future__ import annotations
 
-from typing import Dict
+from typing import Dict, Optional
 
 import torch
 
@@ -35,14 +35,23 @@ class Attention:
     def cache_need(spec):
         return PagedKV(spec.num_kv_heads, spec.head_dim, spec.window)
 
+    @staticmethod
+    def pack(spec, weights, prefix: str) -> Dict[str, Optional[torch.Tensor]]:
+        """The layer's tensors as the kernels take them: one fused [q | k | v] matrix with the checkpoint's rows
+        in the checkpoint's order (scripts/jiuge.py:217-240 concatenates the same way, but also permutes the rows
+        of q and k inside each head for its adjacent-pair rotary operator; here the rows stay and the rotation pairs
+        row j with row j + head_dim/2, which is the same function), the output matrix, the fused bias or None.
+        Every holder of these weights (this part, the C interface's wrapper) packs through this one function."""
+        out = {"w_qkv": weights.get_rows([prefix + n + "_proj.weight" for n in "qkv"], MATRIX),
+               "w_o": weights.get(prefix + "o_proj.weight", MATRIX), "b_qkv": None}
+        if spec.bias:
+            out["b_qkv"] = weights.get_rows([prefix + n + "_proj.bias" for n in "qkv"], VECTOR)
+        return out
+
     def __init__(self, spec, weights, prefix: str, runtime):
         self.spec, self.runtime = spec, runtime
-        # one fused [q | k | v] matrix (scripts/jiuge.py:217-240 concatenates the same way)
-        self.w_qkv = torch.cat([weights.get(prefix + n + "_proj.weight", MATRIX) for n in "qkv"], dim=0).contiguous()
-        self.w_o = weights.get(prefix + "o_proj.weight", MATRIX)
-        self.b_qkv = None
-        if spec.bias:
-            self.b_qkv = torch.cat([weights.get(prefix + n + "_proj.bias", VECTOR) for n in "qkv"]).contiguous()
+        packed = self.pack(spec, weights, prefix)
+        self.w_qkv, self.w_o, self.b_qkv = packed["w_qkv"], packed["w_o"], packed["b_qkv"]
         self.position = None
         if spec.position is not None:
             self.position = part_class("position", spec.position)(spec.position, weights, prefix, runtime)

@@ -21,12 +21,17 @@ class SwiGLU:
         return {"gate_proj.weight": TensorDecl((di, d)), "up_proj.weight": TensorDecl((di, d)),
                 "down_proj.weight": TensorDecl((d, di))}
 
+    @staticmethod
+    def pack(spec, weights, prefix: str) -> Dict[str, torch.Tensor]:
+        """The layer's tensors as the kernels take them: one fused matrix of the gate rows followed by the up rows
+        (scripts/jiuge.py:311-323) and the down matrix.  The one place where this packing is written."""
+        return {"w_gate_up": weights.get_rows([prefix + "gate_proj.weight", prefix + "up_proj.weight"], MATRIX),
+                "w_down": weights.get(prefix + "down_proj.weight", MATRIX)}
+
     def __init__(self, spec, weights, prefix: str, runtime):
         self.spec, self.runtime = spec, runtime
-        # gate rows, then up rows (scripts/jiuge.py:311-323)
-        self.w_gate_up = torch.cat([weights.get(prefix + "gate_proj.weight", MATRIX),
-                                    weights.get(prefix + "up_proj.weight", MATRIX)], dim=0).contiguous()
-        self.w_down = weights.get(prefix + "down_proj.weight", MATRIX)
+        packed = self.pack(spec, weights, prefix)
+        self.w_gate_up, self.w_down = packed["w_gate_up"], packed["w_down"]
 
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))

@@ -15,12 +15,13 @@ them (scripts/jiuge.py:145-146).
 """
 from __future__ import annotations
 
+import warnings
 from dataclasses import dataclass
-from typing import Dict, Iterable, Mapping, Optional, Tuple
+from typing import Dict, Iterable, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
-from .safetensors_io import TensorInfo, index_directory, read_tensor
+from .safetensors_io import SafetensorsError, TensorInfo, index_directory, read_tensor
 
 MATRIX = "matrix"     # operand of a matrix product: compute dtype
 VECTOR = "vector"     # norm weights, biases: float32
@@ -54,14 +55,27 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+class UnusedTensorsWarning(UserWarning):
+    """The checkpoint holds tensors that the model does not use."""
+
+
 def check_manifest(manifest: Mapping[str, TensorDecl], found: Mapping[str, Tuple[int, ...]],
-                   where: str = "") -> None:
+                   where: str = "", strict: bool = False) -> None:
+    """Compare what the model's parts declare with what the checkpoint holds.  Missing tensors and wrong shapes
+    raise ONE ``WeightError`` that lists them all.  Tensors that no part declared are left alone with an
+    ``UnusedTensorsWarning`` that names them, as the reference reads every key of a checkpoint and uses what it
+    needs (scripts/jiuge.py:400-407; checkpoints carry such extras, e.g. ``rotary_emb.inv_freq``); with
+    ``strict=True`` they are part of the error."""
     missing = [n for n, d in manifest.items() if n not in found and not d.optional]
-    unexpected = [n for n in found if n not in manifest]
+    unexpected = sorted(n for n in found if n not in manifest)
     wrong = [(n, manifest[n].shape, tuple(found[n])) for n in manifest
              if n in found and tuple(found[n]) != tuple(manifest[n].shape)]
-    if missing or unexpected or wrong:
-        raise WeightError(sorted(missing), sorted(unexpected), sorted(wrong), where)
+    if missing or wrong or (strict and unexpected):
+        raise WeightError(sorted(missing), unexpected, sorted(wrong), where)
+    if unexpected:
+        shown = ", ".join(unexpected[:8]) + (", ..." if len(unexpected) > 8 else "")
+        warnings.warn(f"checkpoint {where} holds {len(unexpected)} tensors that the model does not use: {shown}".replace("  ", " "),
+                      UnusedTensorsWarning, stacklevel=2)
 
 
 def stored_dtype(dtype: torch.dtype) -> torch.dtype:
@@ -95,20 +109,67 @@ class WeightSource:
         self.compute_dtype = compute_dtype
         self.device = torch.device(device)
 
+    def plan(self, manifest: Mapping[str, TensorDecl]) -> None:
+        """Told once, before the parts are built, which tensors will be asked for and in which role."""
+
+    def close(self) -> None:
+        """Told once the parts are built: nothing more will be asked for."""
+
     def has(self, name: str) -> bool:
         raise NotImplementedError
 
     def get(self, name: str, role: str = MATRIX) -> torch.Tensor:
         raise NotImplementedError
 
+    def get_rows(self, names: Sequence[str], role: str = MATRIX) -> torch.Tensor:
+        """The named tensors one below the other (along their first dimension) as ONE tensor: how a part asks for
+        a fused matrix ([q | k | v], [gate | up]).  A source that can place the pieces directly overrides this."""
+        if len(names) == 1:
+            return self.get(names[0], role)
+        return torch.cat([self.get(n, role) for n in names], dim=0).contiguous()
+
+
+def _target_dtype(stored: torch.dtype, role: str, compute: torch.dtype) -> torch.dtype:
+    """The type a tensor stored as ``stored`` is handed out in (what ``_to_role`` produces)."""
+    if role == TABLE:
+        return torch.int32
+    if role == VECTOR:
+        return torch.float32
+    if role == MATRIX:
+        return compute
+    keep = stored_dtype(stored)
+    return torch.float32 if (compute == torch.float32 and keep == torch.bfloat16) else keep
+
+
+class Float16RoundedWarning(UserWarning):
+    """A float16 checkpoint runs in the bfloat16 engine: its matrices lose three bits of mantissa."""
+
 
 class FileWeights(WeightSource):
-    """Tensors of the ``*.safetensors`` files of a model folder."""
+    """Tensors of the ``*.safetensors`` files of a model folder.
+
+    On a CUDA device all tensors live in ONE device allocation (an arena sized from the manifest in ``plan``): a fused
+    matrix is one slice of it and each checkpoint tensor is copied straight to its rows, so nothing is concatenated
+    on the device and no tensor has an allocation of its own.  Bytes travel through two pinned staging buffers of
+    fixed size that take turns: the file is read into one while the other's asynchronous copy is in flight.  (The
+    reference allocates and copies tensor by tensor, blocking, under a global lock: src/tensor/tensor.cpp:142-167.)
+    """
+
+    STAGING_BYTES = 32 << 20
+    ALIGN = 256
 
     def __init__(self, model_dir: str, compute_dtype: torch.dtype, device):
         super().__init__(compute_dtype, device)
         self.model_dir = model_dir
         self.index: Dict[str, TensorInfo] = index_directory(model_dir)
+        self._arena: Optional[torch.Tensor] = None
+        self._arena_used = 0
+        self._staging: List[torch.Tensor] = []
+        self._events: List[Optional[object]] = [None, None]
+        self._turn = 0
+        self._warned_f16 = False
+        self.arena_bytes = 0          # size of the arena; outside_arena counts tensors that did not fit it
+        self.outside_arena = 0
 
     def shapes(self) -> Dict[str, Tuple[int, ...]]:
         return {n: i.shape for n, i in self.index.items()}
@@ -116,13 +177,106 @@ class FileWeights(WeightSource):
     def has(self, name: str) -> bool:
         return name in self.index
 
+    # ---- the arena ---------------------------------------------------------------------------------------
+    def plan(self, manifest: Mapping[str, TensorDecl]) -> None:
+        if self.device.type != "cuda" or self._arena is not None:
+            return
+        total = 0
+        for name, decl in manifest.items():
+            info = self.index.get(name)
+            if info is not None:
+                size = _numel(info.shape) * _itemsize(_target_dtype(info.dtype, decl.role, self.compute_dtype))
+                total += -(-size // self.ALIGN) * self.ALIGN + self.ALIGN      # a fused matrix starts aligned once
+        self._arena = torch.empty(max(total, self.ALIGN), dtype=torch.uint8, device=self.device)
+        self.arena_bytes = self._arena.numel()
+
+    def _alloc(self, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        size = _numel(shape) * _itemsize(dtype)
+        begin = -(-self._arena_used // self.ALIGN) * self.ALIGN
+        if self._arena is None or begin + size > self._arena.numel():
+            self.outside_arena += 1
+            return torch.empty(shape, dtype=dtype, device=self.device)
+        self._arena_used = begin + size
+        return self._arena[begin:begin + size].view(dtype).view(shape)
+
+    def close(self) -> None:
+        """Wait for the copies in flight and let the staging buffers go."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        self._staging, self._events = [], [None, None]
+
+    # ---- bytes: file -> pinned staging -> device -----------------------------------------------------------
+    def _stream(self, info: TensorInfo, dst: torch.Tensor) -> None:
+        """The tensor's stored bytes into ``dst`` (contiguous, of the stored type and shape)."""
+        if not info.nbytes:
+            return
+        if self.device.type != "cuda":
+            dst.copy_(read_tensor(info))
+            return
+        if not self._staging:
+            self._staging = [torch.empty(self.STAGING_BYTES, dtype=torch.uint8, pin_memory=True) for _ in range(2)]
+        raw = dst.view(-1).view(torch.uint8)
+        with open(info.path, "rb") as f:
+            f.seek(info.begin)
+            done = 0
+            while done < info.nbytes:
+                n = min(self.STAGING_BYTES, info.nbytes - done)
+                turn, self._turn = self._turn, self._turn ^ 1
+                if self._events[turn] is not None:
+                    self._events[turn].synchronize()          # its last copy has left the buffer
+                buf = self._staging[turn]
+                got = f.readinto(memoryview(buf.numpy())[:n])
+                if got != n:
+                    raise SafetensorsError(f"{info.path}: short read of {info.name} ({done + got} of {info.nbytes} bytes)")
+                raw[done:done + n].copy_(buf[:n], non_blocking=True)
+                if self._events[turn] is None:
+                    self._events[turn] = torch.cuda.Event()
+                self._events[turn].record()
+                done += n
+
+    def _load_into(self, info: TensorInfo, dst: torch.Tensor, role: str) -> None:
+        if info.dtype == dst.dtype:
+            self._stream(info, dst)
+            return
+        if info.dtype == torch.float16 and dst.dtype == torch.bfloat16 and not self._warned_f16:
+            self._warned_f16 = True
+            warnings.warn(f"checkpoint {self.model_dir} stores {info.name} (and maybe more) in float16; the bfloat16 engine "
+                          "rounds such matrices to bfloat16 (8 bits of mantissa instead of 11), where the reference keeps "
+                          "float16; dtype float32 runs them exactly", Float16RoundedWarning, stacklevel=4)
+        tmp = torch.empty(info.shape, dtype=info.dtype, device=self.device)
+        self._stream(info, tmp)
+        dst.copy_(tmp)          # converts on the device; the order of the stream keeps tmp alive until then
+
     def get(self, name: str, role: str = MATRIX) -> torch.Tensor:
-        info = self.index[name]
-        host = read_tensor(info, pin=self.device.type == "cuda")
-        if host.dtype == torch.float16:       # 16-bit: bfloat16 in the bfloat16 engine, widened exactly in float32
-            host = host.float() if (role == VECTOR or self.compute_dtype == torch.float32) else host.to(torch.bfloat16)
-        dev = host.to(self.device, non_blocking=False)
-        return _to_role(dev, role, self.compute_dtype).contiguous()
+        return self.get_rows([name], role)
+
+    def get_rows(self, names: Sequence[str], role: str = MATRIX) -> torch.Tensor:
+        infos = [self.index[n] for n in names]
+        rest = infos[0].shape[1:]
+        if any(i.shape[1:] != rest or not i.shape for i in infos[1:]) or (len(infos) > 1 and not infos[0].shape):
+            raise ValueError(f"tensors {list(names)} cannot be stacked: shapes {[i.shape for i in infos]}")
+        dtype = _target_dtype(infos[0].dtype, role, self.compute_dtype)
+        if len(infos) == 1:
+            out = self._alloc(infos[0].shape, dtype)
+            self._load_into(infos[0], out, role)
+            return out
+        out = self._alloc((sum(i.shape[0] for i in infos),) + tuple(rest), dtype)
+        row = 0
+        for info in infos:
+            self._load_into(info, out[row:row + info.shape[0]], role)
+            row += info.shape[0]
+        return out
+
+
+def _numel(shape) -> int:
+    n = 1
+    for s in shape:
+        n *= int(s)
+    return n
+
+
+def _itemsize(dtype: torch.dtype) -> int:
+    return torch.empty((), dtype=dtype).element_size()
 
 
 class DictWeights(WeightSource):

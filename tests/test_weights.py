@@ -145,3 +145,46 @@ def test_random_mode_writes_a_loadable_folder(tmp_path):
 def test_tied_folder_has_no_output_matrix(tmp_path):
     d = write_model_folder(MiniCPMConfig.from_dict(TINY_A), str(tmp_path / "a"), seed=0)
     assert "lm_head.weight" not in index_directory(d)
+
+
+def test_unused_tensors_warn_and_fail_only_when_strict():
+    """A checkpoint may hold more than the model reads (the reference reads every key and uses what it needs,
+    scripts/jiuge.py:400-407): that is a warning naming the tensors, an error only for a strict load."""
+    from infinicore_infer_b200.weights import UnusedTensorsWarning
+    spec = MiniCPMConfig.from_dict(TINY_A).model_spec()
+    manifest = model_manifest(spec)
+    shapes = {n: tuple(t.shape) for n, t in random_tensors(manifest, seed=0).items()}
+    shapes["model.layers.0.self_attn.rotary_emb.inv_freq"] = (8,)
+    with pytest.warns(UnusedTensorsWarning, match="rotary_emb.inv_freq"):
+        check_manifest(manifest, shapes)
+    with pytest.raises(WeightError) as e:
+        check_manifest(manifest, shapes, strict=True)
+    assert e.value.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"] and not e.value.missing
+
+
+def test_fused_rows_come_out_as_one_tensor(tmp_path):
+    """``get_rows`` hands a part its fused matrix: the named tensors one below the other, in the role's type."""
+    import warnings
+    from infinicore_infer_b200.weights import write_file
+    from infinicore_infer_b200.weights.loader import Float16RoundedWarning
+    a, b, c = torch.randn(4, 6), torch.randn(2, 6), torch.randn(3, 6)
+    d = tmp_path / "m"
+    d.mkdir()
+    write_file(str(d / "model.safetensors"), {"a": a.to(torch.bfloat16), "b": b.to(torch.float16), "c": c,
+                                              "v1": torch.randn(5).to(torch.bfloat16), "v2": torch.randn(3)})
+    want = torch.cat([a.to(torch.bfloat16).float(), b.to(torch.float16).float(), c])
+    f32 = FileWeights(str(d), torch.float32, "cpu")
+    assert torch.equal(f32.get_rows(["a", "b", "c"], MATRIX), want)            # widened exactly
+    bf = FileWeights(str(d), torch.bfloat16, "cpu")
+    with pytest.warns(Float16RoundedWarning, match="float16"):
+        got = bf.get_rows(["a", "b", "c"], MATRIX)
+    assert got.dtype == torch.bfloat16 and torch.equal(got, want.to(torch.bfloat16))
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")                                          # said once per source
+        bf.get("b", MATRIX)
+    v = bf.get_rows(["v1", "v2"], VECTOR)
+    assert v.dtype == torch.float32 and v.shape == (8,)
+    with pytest.raises(ValueError, match="cannot be stacked"):
+        bf.get_rows(["a", "v1"], MATRIX)
+    dw = DictWeights({"a": a, "b": b}, torch.float32, "cpu")
+    assert torch.equal(dw.get_rows(["a", "b"]), torch.cat([a, b]))
