@@ -2,6 +2,7 @@
 from .specs import (AttentionSpec, BlockSpec, ConfigError, ModelSpec, RMSNormSpec, RopeSpec,
                     RunEntry, SwiGLUSpec, default_order)
 from .minicpm import MiniCPMConfig
+from .presets import PRESETS, Preset
 from .registry import (architecture_names, config_class_for, read_config,
                        register_architecture)
 
@@ -12,5 +13,5 @@ for _name in ("minicpm", "fm9g", "llama", "MiniCPMForCausalLM", "LlamaForCausalL
 __all__ = [
     "AttentionSpec", "BlockSpec", "ConfigError", "ModelSpec", "RMSNormSpec", "RopeSpec",
     "RunEntry", "SwiGLUSpec", "default_order", "MiniCPMConfig", "architecture_names",
-    "config_class_for", "read_config", "register_architecture",
+    "config_class_for", "read_config", "register_architecture", "PRESETS", "Preset",
 ]

@@ -441,6 +441,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 unsigned char *dst = reinterpret_cast<unsigned char *>(s.p[half]) + row * 128 + ((c ^ (row & 7)) << 4);
                 *reinterpret_cast<uint4 *>(dst) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
             }
+            // The tile's value rows beyond the last key that any row of this tile sees carry weight 0 in P V, but
+            // 0 x NaN is NaN: slots of the request's last page that lie beyond its end hold whatever an earlier
+            // holder of the page left there.  Those rows become zeros before the product reads them (only the last
+            // tile of keys has any; the first half's threads take one key row each).
+            if (i == n_kv - 1 && half == 0 && kv_first + i * AT_BN + AT_BN - 1 > p_last) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&s.v_full[i & 1], (i >> 1) & 1))) { alive = false; break; }
+                if (kv_first + i * AT_BN + row > p_last) {
+#pragma unroll
+                    for (int u = 0; u < SUB; ++u) {
+                        uint4 *vrow = reinterpret_cast<uint4 *>(s.v[i & 1][u] + row * 64);      // 128 bytes; the swizzle stays inside
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+            }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             tc_fence_before();
             __syncwarp();

@@ -362,8 +362,9 @@ class Engine:
         graph, out, launches = rec
         graph.replay()
         self.kernel_launches += launches
+        # `out` is the captured graph's own buffer, which the next replay overwrites: the caller gets a copy
         if all(len(e.want) == 1 for e in entries):
-            return out[:B]
+            return out[:B].clone()
         rows = []
         for i, e in enumerate(entries):
             rows.extend([i] * len(e.want))

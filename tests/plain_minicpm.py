@@ -108,12 +108,14 @@ def plain_attention_layer(h, w: Dict[str, torch.Tensor], prefix: str, positions,
 
 def plain_forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int],
                   dtype: torch.dtype = torch.float64, windows: Optional[Sequence[Optional[int]]] = None,
-                  order: Optional[Sequence[tuple]] = None) -> torch.Tensor:
+                  order: Optional[Sequence[tuple]] = None, rows: Optional[Sequence[int]] = None) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence from position 0.  The step of the reference,
     src/models/jiuge/jiuge.cpp:114-298, for a single request with req_pos = 0.
 
     ``windows[i]``: attention window of layer i (None: full).  ``order``: run entries
     ``(layer, cache, writes_cache)``; the default runs every layer once with its own cache.
+    ``rows``: compute the logits of these positions only (the final norm and the output product look at single
+    rows, src/models/jiuge/jiuge.cpp:269-278); the result is then [len(rows), vocab].
     """
     w = {k: v.to(dtype) for k, v in weights.items()}
     L, d, nh = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["num_attention_heads"]
@@ -141,6 +143,8 @@ def plain_forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[
         h = plain_rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps)     # jiuge.cpp:246
         x = x + scale_res * plain_swiglu_ffn(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                                              w[p + "mlp.down_proj.weight"])      # jiuge.cpp:247-249, jiuge.py:348
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long)]
     h = plain_rmsnorm(x, w["model.norm.weight"], eps) * scale_logit             # jiuge.cpp:262, jiuge.py:198-201
     out = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]   # jiuge.py:182-191
     return h @ out.T                                                             # jiuge.cpp:264

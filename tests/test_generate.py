@@ -70,7 +70,7 @@ def test_greedy_generation_through_the_entry_point(tiny_models, models, name, dt
         if dtype == "float32":
             assert got == plain_generate(cfg, w, prompt, 8)[0], (name, n)
         else:       # bfloat16 may pick the other of two logits closer than twice its error bound
-            assert assert_greedy(cfg, w, prompt, got, margin=2 * 2.5e-2 * scale) >= 4
+            assert assert_greedy(cfg, w, prompt, got, margin=2 * 2.5e-2 * scale) >= 6
     assert not model.engine.cache.lengths               # every cache handle was dropped
 
 
@@ -122,15 +122,26 @@ def test_sampling_is_reproducible_and_depends_on_the_seed(tiny_models, models):
     assert c[0] != b[0] and len(set(b[0])) > 3
 
 
-def test_generation_under_page_pressure_preempts_and_still_matches(tiny_models):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generation_under_page_pressure_preempts_and_still_matches(tiny_models, dtype):
+    """A pool too small for three growing requests: the youngest is preempted and later recomputed.  float32: the
+    tokens are the plain implementation's.  bfloat16 (the native runner, captured decode steps): every token is the
+    plain choice for the sequence so far or within the error bound of it (a recomputed request meets its old positions
+    through the prefill kernels instead of the decode kernels, so tokens need not equal those of an undisturbed run)."""
     from infinicore_infer_b200.jiuge import JiugeForCauslLM
     folder, cfg, w = tiny_models["A"]
-    model = JiugeForCauslLM(folder, dtype="float32", max_batch=4, cache_tokens=96, chunk_size=16)
+    model = JiugeForCauslLM(folder, dtype=dtype, max_batch=4, cache_tokens=96, chunk_size=16)
     prompts = [random_tokens(900 + i, n, cfg["vocab_size"]) for i, n in enumerate((20, 25, 30))]
     got = model.generator.generate(prompts, max_new_tokens=24, eos_token_ids=())
     assert model.generator.scheduler.counters["preemptions"] >= 1
-    for p, g in zip(prompts, got):
-        assert g == plain_generate(cfg, w, p, 24)[0]
+    if dtype == "float32":
+        for p, g in zip(prompts, got):
+            assert g == plain_generate(cfg, w, p, 24)[0]
+    else:
+        assert model.engine.runner is not None
+        for p, g in zip(prompts, got):
+            scale = float(plain_forward(cfg, w, p).abs().max())
+            assert len(g) == 24 and assert_greedy(cfg, w, p, g, margin=2 * 2.5e-2 * scale) >= 18
     assert all(gr.pool.in_use == 0 for gr in model.engine.cache.groups)
 
 
@@ -193,3 +204,38 @@ def test_command_line(tiny_models):
                           capture_output=True, text=True, cwd=ROOT, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert "Time per step" in proc.stdout and "Model destroyed" in proc.stdout
+
+
+def test_command_line_runs_the_tiny_b_workload_through_the_scheduler(tmp_path):
+    """``--random tiny-B`` with four prompts of 1/7/23/40 tokens, portions of 9 beside decoded tokens, pages of 8,
+    temperature 0.8 with a fixed seed: the printed tokens are the plain implementation's."""
+    import re
+    from infinicore_infer_b200.config import PRESETS, MiniCPMConfig
+    from infinicore_infer_b200.weights import index_directory, read_tensor, write_model_folder
+    preset = PRESETS["tiny-B"]
+    proc = subprocess.run([sys.executable, "-m", "infinicore_infer_b200.jiuge", "--nvidia", "--random", "tiny-B", "--seed", "1",
+                           "--prompt-lens", "1,7,23,40", "--chunk-size", "9", "--page-size", "8", "--num-pages", "40",
+                           "--max-batch", "4", "--max-tokens-per-step", "16", "--temperature", "0.8", "--topk", "0",
+                           "--sample-seed", "1234", "--max-steps", "10", "--dtype", "float32"],
+                          capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    got = {int(m.group(1)): [int(t) for t in m.group(2).split()] for m in re.finditer(r"request (\d+): ([\d ]*)", proc.stdout)}
+    assert sorted(got) == [0, 1, 2, 3]
+    steps = int(re.search(r"(\d+) steps", proc.stdout).group(1))
+    assert steps > 10 + 4                                # the prompts really were cut into portions
+    cfg = MiniCPMConfig.from_dict(preset.config)
+    write_model_folder(cfg, str(tmp_path), seed=1, std=preset.std, norm_std=preset.norm_std)
+    w = {n: read_tensor(i).float() for n, i in index_directory(str(tmp_path)).items()}
+    eos = set(cfg.eos_token_id)
+    for k, n in enumerate((1, 7, 23, 40)):
+        prompt = torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(1 + k)).tolist()
+        want, _ = plain_generate(cfg.to_dict(), w, prompt, 10, temperature=0.8, seed=1234)
+        if eos & set(want):
+            want = want[:min(want.index(e) for e in eos if e in want) + 1]
+        assert got[k] == want, k
+
+
+def test_command_line_refuses_a_folder_together_with_a_random_model(tiny_models):
+    from infinicore_infer_b200.jiuge import test as cli
+    assert cli(["--nvidia", tiny_models["A"][0], "--random", "tiny-A"]) == 1
+    assert cli(["--nvidia"]) == 1

@@ -99,11 +99,11 @@ def test_gemm_f32_is_a_true_float32_product(K, M, N, K_):
         assert torch.equal(one[0], out[M - 1])
 
 
-def _scatter_pages(k, v, tables, page, num_pages, dtype):
+def _scatter_pages(k, v, tables, page, num_pages, dtype, junk=7.0):
     """Dense per-request keys/values [len, nkvh, dh] -> pages [num_pages, nkvh, page, dh]."""
     nkvh, dh = k[0].shape[1:]
-    kp = torch.full((num_pages, nkvh, page, dh), 7.0).to(dtype)       # junk where nothing was written
-    vp = torch.full((num_pages, nkvh, page, dh), -7.0).to(dtype)
+    kp = torch.full((num_pages, nkvh, page, dh), junk).to(dtype)       # junk where nothing was written
+    vp = torch.full((num_pages, nkvh, page, dh), -junk).to(dtype)
     for r, (kr, vr) in enumerate(zip(k, v)):
         for j in range(kr.shape[0]):
             p = tables[r][j // page]
@@ -359,7 +359,7 @@ def test_rope_and_cache_write(K, dtype, nh, nkvh, dh, page, interleaved):
     assert float(kp[0].abs().max()) == 0.0              # the null page was not written
 
 
-def _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, plant=None, seed=0, impl="rows", splits=1):
+def _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, plant=None, seed=0, impl="rows", splits=1, junk=7.0):
     """lens: cached length of each request; queries: per request the positions that are rows.
     impl: "rows" (one warp per row and head), "decode" (split keys), "prefill" (tensor cores; the
     positions of a request must be consecutive)."""
@@ -378,7 +378,7 @@ def _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, plant=N
     perm = (torch.randperm(R * max_blocks, generator=g) + 1).view(R, max_blocks)
     tables = perm.tolist()
     num_pages = R * max_blocks + 1
-    kp, vp = _scatter_pages(k, v, tables, page, num_pages, dtype)
+    kp, vp = _scatter_pages(k, v, tables, page, num_pages, dtype, junk)
     positions = torch.tensor([p for r in range(R) for p in queries[r]], dtype=torch.int32)
     row_req = torch.tensor([r for r in range(R) for _ in queries[r]], dtype=torch.int32)
     q = torch.stack([qf[r][p] for r in range(R) for p in queries[r]]).to(dtype)
@@ -496,6 +496,27 @@ def test_attention_finds_one_far_key_among_hundreds(K, impl, dtype, window):
         got, want, v = _attention_case(K, dtype, nh, nkvh, dh, page, window, lens, queries, plant, seed=5, **kw)
         _close(got, want, dtype, scale=2.0)
         assert not torch.allclose(got[i699, 1].float().cpu(), v[0][far - 1, 1 // group], atol=0.2)
+
+
+@pytest.mark.parametrize("junk", [float("nan"), float("inf")])
+@pytest.mark.parametrize("impl,dtype,nh,nkvh,dh,page", [
+    ("rows", torch.float32, 4, 2, 48, 8), ("rows", torch.bfloat16, 4, 4, 16, 16), ("decode", torch.bfloat16, 3, 3, 32, 8),
+    ("decode", torch.bfloat16, 6, 2, 64, 16), ("decode", torch.bfloat16, 8, 2, 128, 16), ("prefill", torch.bfloat16, 4, 2, 64, 16),
+    ("prefill", torch.bfloat16, 2, 1, 80, 32), ("tcgen05", torch.bfloat16, 4, 2, 64, 16), ("tcgen05", torch.bfloat16, 4, 2, 128, 64),
+    ("tcgen05", torch.bfloat16, 2, 2, 64, 128)])
+def test_attention_ignores_what_lies_beyond_a_request_s_length(K, impl, dtype, nh, nkvh, dh, page, junk):
+    """The slots of a held page beyond the request's last position, and pages that were never written, may hold
+    anything: what another request left there (a request whose activations overflowed leaves NaN or Inf) or what
+    the allocator handed out.  No kernel may let it reach a result, not even multiplied by a weight of zero."""
+    lens = [150, 333, 70, 41]
+    if impl in ("prefill", "tcgen05"):
+        queries = [list(range(0, 150)), list(range(203, 333)), list(range(6, 70)), list(range(31, 41))]
+    else:
+        queries = [[149], [331, 332], [69], list(range(36, 41))]
+    kw = dict(impl=impl, splits=3) if impl == "decode" else dict(impl=impl)
+    got, want, _ = _attention_case(K, dtype, nh, nkvh, dh, page, None, lens, queries, seed=dh + page, junk=junk, **kw)
+    assert torch.isfinite(got.float()).all()
+    _close(got, want, dtype, scale=2.0)
 
 
 @pytest.mark.parametrize("V", [5, 301, 122753])

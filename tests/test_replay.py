@@ -24,9 +24,9 @@ TOL = {"float32": 3e-5, "bfloat16": 2.5e-2}
 LENGTHS = {"A": [5, 47, 130], "B": [1, 40, 97], "C": [33, 64, 100], "D": [9, 140, 300]}
 
 
-def make_engine(folder, dtype, cache_tokens, **kw):
+def make_engine(folder, dtype, cache_tokens, page_size=16, **kw):
     from infinicore_infer_b200.engine import Engine
-    return Engine.from_folder(folder, dtype=DTYPES[dtype], cache_tokens=cache_tokens, page_size=16,
+    return Engine.from_folder(folder, dtype=DTYPES[dtype], cache_tokens=cache_tokens, page_size=page_size,
                               max_requests=8, max_step_tokens=1024, **kw)
 
 
@@ -174,6 +174,78 @@ def test_mixed_requests_in_a_pool_so_small_that_pages_are_used_again(tiny_models
         check(got, r, wants[r], TOL[dtype], f"{name} {dtype} mixed")
     g = eng.cache.groups[0]
     assert g.pool.high_water == g.pool.capacity == peak // 16 and g.pool.in_use == 0
+
+
+# Pages of other sizes than 16: tiny-B at its own 8; tiny-D (heads of 64: the tcgen05 attention builds another TMA box per
+# page size, and 128 keys are one page, two, or sixteen) at 8, 64 and 128; tiny-C (head size 48, the mma.sync kernels) at 4.
+PAGE_CASES = [("B", 8), ("D", 8), ("D", 64), ("D", 128), ("C", 4), ("A", 32)]
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+@pytest.mark.parametrize("name,page", PAGE_CASES)
+def test_every_way_of_cutting_at_other_page_sizes(tiny_models, name, page, dtype):
+    eng = make_engine(tiny_models[name][0], dtype, 1024, page_size=page)
+    for i, n in enumerate(LENGTHS[name][1:]):
+        toks, want = expected(tiny_models, name, 101 + i, n)
+        for what, steps in (("whole", whole("r", toks)), ("tail", tail_decode("r", toks)), ("portions", portions("r", toks))):
+            check(run(eng, steps), "r", want, TOL[dtype], f"{name} page {page} {dtype} {what} n={n}")
+    # mixed, in a pool of exactly the pages the live requests need at the worst moment
+    lens = {"a": 70, "b": 33, "c": 90, "d": 48, "e": 61, "f": 20}
+    reqs, wants = {}, {}
+    for i, (r, n) in enumerate(lens.items()):
+        reqs[r], wants[r] = expected(tiny_models, name, 200 + i, n)
+    plan = [{"a": 40}, {"a": 2, "b": 30}, {"a": 1, "b": 1, "c": 50}, {"a": 1, "b": 1, "c": 38, "d": 9},
+            {"a": 26, "b": 1, "c": 1, "d": 2}, {"c": 1, "d": 37, "e": 13}, {"e": 2, "f": 3}, {"e": 1, "f": 1}, {"e": 45, "f": 16}]
+    steps = mixed(reqs, plan)
+    peak = peak_tokens(steps, round_to=page)
+    eng = make_engine(tiny_models[name][0], dtype, peak, page_size=page)
+    got = run(eng, steps)
+    for r in reqs:
+        check(got, r, wants[r], TOL[dtype], f"{name} page {page} {dtype} mixed")
+    g = eng.cache.groups[0]
+    assert g.pool.high_water == g.pool.capacity == peak // page and g.pool.in_use == 0
+    eng.check()
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_an_entry_may_want_nothing_in_a_decode_step(tiny_models, engines, dtype):
+    """A decode step (single tokens only, so it runs as a captured graph) in which one request asks for no logits
+    and another for its one row: the rows that come back are the wanted ones, in order."""
+    name = "A"
+    ta, wa = expected(tiny_models, name, 410, 20)
+    tb, wb = expected(tiny_models, name, 411, 16)
+    tc, wc = expected(tiny_models, name, 412, 12)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": ta[:10], "want": []}, {"id": "b", "tokens": tb[:10], "want": [9]},
+                                     {"id": "c", "tokens": tc[:10], "want": []}], "end": []}]
+    for s in range(1, 3):
+        steps.append({"step": s, "entries": [{"id": "a", "tokens": [ta[9 + s]], "want": [0] if s == 2 else []},
+                                             {"id": "b", "tokens": [tb[9 + s]], "want": []},
+                                             {"id": "c", "tokens": [tc[9 + s]], "want": [0]}], "end": []})
+    steps.append({"step": 3, "entries": [{"id": "a", "tokens": [ta[12]], "want": []}, {"id": "b", "tokens": [tb[12]], "want": []}],
+                  "end": ["a", "b", "c"]})
+    from infinicore_infer_b200.trace import replay
+    results = replay(engines(name, dtype), steps)
+    assert sorted(results) == [0, 1, 2]                     # step 3 wants nothing: no rows, no file
+    got = by_position(steps, results)
+    assert sorted(got) == [("a", 11), ("b", 9), ("c", 10), ("c", 11)]
+    tol = TOL[dtype]
+    for (r, p), row in got.items():
+        want = {"a": wa, "b": wb, "c": wc}[r]
+        assert np.abs(row - want[p]).max() <= tol * np.abs(want).max(), (r, p)
+
+
+def test_logits_of_a_captured_step_are_the_caller_s_own(tiny_models):
+    """``Engine.step`` hands back rows that the next captured decode step must not change."""
+    from infinicore_infer_b200.engine import StepEntry
+    folder, cfg, _ = tiny_models["A"]
+    eng = make_engine(folder, "bfloat16", 256)
+    toks = random_tokens(3, 12, cfg["vocab_size"])
+    eng.step([StepEntry("a", toks[:8], [7])])
+    first = eng.step([StepEntry("a", [toks[8]], [0])])
+    keep = first.clone()
+    eng.step([StepEntry("a", [toks[9]], [0])])
+    eng.step([StepEntry("a", [toks[10]], [0])])
+    assert torch.equal(first, keep)
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
