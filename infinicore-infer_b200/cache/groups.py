@@ -21,19 +21,75 @@ from .pages import OutOfPages, PagePool
 NO_PAGE = 0     # block-table entry of a block that holds nothing (the null page)
 
 
+class CacheNeed:
+    """What a mixer asks of the cache manager, as an object that knows how to provide it.  The manager and the
+    scheduler call these methods and look at nothing else, so another kind of need (a class with the same methods,
+    defined beside its mixer) is an addition, not a change:
+
+    ``group_key()``              needs with equal keys share one group (a pool and block tables of their own); None: this
+                                 need takes no pages and forms no group;
+    ``make_group(...)``          the group's bookkeeping: an object with ``pages_needed / reserve / give_back / trim /
+                                 truncate / release / row`` and a ``pool`` (see ``CacheGroup``);
+    ``make_storage(...)``        device memory for the caches of a group (or for one cache without a group);
+    ``make_view(...)``           what the mixer of one cache is handed at every step;
+    ``most_pages_alone(...)``    pages that a request of ``total`` tokens holds at most when it runs alone with portions of
+                                 ``chunk`` tokens (the scheduler's "can this request ever fit").
+    """
+
+    def group_key(self):
+        return None
+
+    def most_pages_alone(self, total: int, chunk: int, page_size: int) -> int:
+        return 0
+
+
 @dataclass(frozen=True)
-class PagedKV:
+class PagedKV(CacheNeed):
     """Keys and values of ``num_kv_heads`` heads of ``head_dim`` for every cached position."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: all keys are kept
 
+    def group_key(self):
+        return self
+
+    def make_group(self, cache_ids, num_pages: int, page_size: int, max_blocks: int) -> "CacheGroup":
+        return CacheGroup(self, cache_ids, num_pages, page_size, max_blocks=max_blocks)
+
+    def make_storage(self, count: int, num_pages: int, page_size: int, num_slots: int, dtype, device):
+        import torch
+        if device is None:
+            return None
+        shape = (count, num_pages, self.num_kv_heads, page_size, self.head_dim)
+        # zeros: what lies beyond a request's last position in a held page must be finite for every kernel
+        return torch.zeros(shape, dtype=dtype, device=device), torch.zeros(shape, dtype=dtype, device=device)
+
+    def make_view(self, storage, index: int, group_index: int, page_size: int):
+        from .manager import KVView
+        if storage is None:
+            return KVView(group_index, None, None, page_size)
+        return KVView(group_index, storage[0][index], storage[1][index], page_size)
+
+    def most_pages_alone(self, total: int, chunk: int, page_size: int) -> int:
+        span = total if self.window is None else min(total, self.window + chunk + page_size)
+        return (span + page_size - 1) // page_size
+
 
 @dataclass(frozen=True)
-class StateSlot:
+class StateSlot(CacheNeed):
     """Per-request state of fixed shape, e.g. a recurrent mixer's."""
     shape: Tuple[int, ...]
     dtype: str = "float32"
+
+    def make_storage(self, count: int, num_pages: int, page_size: int, num_slots: int, dtype, device):
+        import torch
+        if device is None:
+            return None
+        return torch.zeros((num_slots,) + tuple(self.shape), dtype=getattr(torch, self.dtype), device=device)
+
+    def make_view(self, storage, index: int, group_index: int, page_size: int):
+        from .manager import StateView
+        return StateView(storage)
 
 
 class CacheGroup:

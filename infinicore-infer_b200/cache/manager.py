@@ -13,7 +13,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
-from .groups import NO_PAGE, CacheGroup, PagedKV, StateSlot
+from .groups import NO_PAGE, CacheGroup, CacheNeed, PagedKV, StateSlot
 from .pages import OutOfPages
 from .slots import OutOfSlots, SlotAllocator
 
@@ -54,31 +54,25 @@ class CacheManager:
         self.lengths: Dict[object, int] = {}
         self._state_tensors: List[torch.Tensor] = []
 
-        by_need: Dict[PagedKV, List[int]] = {}
+        # Needs with equal group keys share a group; a need without a key (per-request state) gets storage of its own.
+        # What each kind of need provides is the need's own business (``CacheNeed`` in groups.py).
+        by_key: Dict[object, List[int]] = {}
         for c, need in enumerate(needs):
-            if isinstance(need, PagedKV):
-                by_need.setdefault(need, []).append(c)
-        for gi, (need, ids) in enumerate(by_need.items()):
+            if need is not None and need.group_key() is not None:
+                by_key.setdefault(need.group_key(), []).append(c)
+        for gi, (key, ids) in enumerate(by_key.items()):
+            need = needs[ids[0]]
             n = (pages_per_group or {}).get(gi, num_pages)
-            group = CacheGroup(need, ids, n + 1, page_size, max_blocks=self.max_blocks)
-            self.groups.append(group)
-            if device is not None:
-                shape = (len(ids), n + 1, need.num_kv_heads, page_size, need.head_dim)
-                k = torch.zeros(shape, dtype=dtype, device=device)
-                v = torch.zeros(shape, dtype=dtype, device=device)
-                for i, c in enumerate(ids):
-                    self.views[c] = KVView(gi, k[i], v[i], page_size)
-            else:
-                for c in ids:
-                    self.views[c] = KVView(gi, None, None, page_size)
+            self.groups.append(need.make_group(ids, n + 1, page_size, self.max_blocks))
+            storage = need.make_storage(len(ids), n + 1, page_size, self.slots.num_slots, dtype, device)
+            for i, c in enumerate(ids):
+                self.views[c] = need.make_view(storage, i, gi, page_size)
         for c, need in enumerate(needs):
-            if isinstance(need, StateSlot):
-                st = None
-                if device is not None:
-                    st = torch.zeros((self.slots.num_slots,) + tuple(need.shape),
-                                     dtype=getattr(torch, need.dtype), device=device)
-                    self._state_tensors.append(st)
-                self.views[c] = StateView(st)
+            if need is not None and need.group_key() is None:
+                storage = need.make_storage(1, 0, page_size, self.slots.num_slots, dtype, device)
+                if storage is not None and hasattr(storage, "zero_"):
+                    self._state_tensors.append(storage)
+                self.views[c] = need.make_view(storage, 0, -1, page_size)
 
     # ---- requests ------------------------------------------------------------------------
     def admit(self, req) -> int:

@@ -19,16 +19,18 @@ class OutOfPages(RuntimeError):
 
 
 class PagePool:
+    """The free list of one cache group.  The bookkeeping itself (which pages are free, in which order they go out,
+    which are held) is ``jk::PagePool`` of csrc/host_rules.h, the same class that the C interface's pool is; this
+    wrapper gives it Python's errors and names."""
+
     def __init__(self, num_pages: int, reserved: int = 1, name: str = ""):
         if num_pages <= reserved:
             raise ValueError(f"a pool of {num_pages} pages with {reserved} reserved holds nothing")
+        from ..kernels.host import NativePagePool
         self.num_pages = num_pages
         self.reserved = reserved
         self.name = name
-        # stack: pop from the end; lowest page first at the start
-        self._free: List[int] = list(range(num_pages - 1, reserved - 1, -1))
-        self._held = [False] * num_pages
-        self.high_water = 0
+        self._pool = NativePagePool(num_pages, reserved)
 
     @property
     def capacity(self) -> int:
@@ -36,35 +38,35 @@ class PagePool:
 
     @property
     def available(self) -> int:
-        return len(self._free)
+        return self._pool.available()
 
     @property
     def in_use(self) -> int:
-        return self.capacity - len(self._free)
+        return self.capacity - self._pool.available()
+
+    @property
+    def high_water(self) -> int:
+        return self._pool.high_water()
 
     def alloc(self, n: int) -> List[int]:
         if n < 0:
             raise ValueError("negative page count")
-        if n > len(self._free):
-            raise OutOfPages(n, len(self._free), self.name)
-        out = [self._free.pop() for _ in range(n)]
-        for p in out:
-            self._held[p] = True
-        self.high_water = max(self.high_water, self.in_use)
+        out = self._pool.alloc(n)
+        if out is None:
+            raise OutOfPages(n, self._pool.available(), self.name)
         return out
 
     def free(self, pages: Iterable[int]) -> None:
         pages = list(pages)
-        for p in pages:
-            if not (self.reserved <= p < self.num_pages):
-                raise ValueError(f"page {p} is not one of this pool's")
-            if not self._held[p]:
-                raise ValueError(f"page {p} freed twice (or never handed out)")
-        if len(set(pages)) != len(pages):
+        rc = self._pool.free(pages)
+        if rc == 1:
+            bad = next(p for p in pages if not (self.reserved <= p < self.num_pages))
+            raise ValueError(f"page {bad} is not one of this pool's")
+        if rc == 2:
+            bad = next(p for p in pages if not self._pool.is_held(p))
+            raise ValueError(f"page {bad} freed twice (or never handed out)")
+        if rc == 3:
             raise ValueError("a page appears twice in one free")
-        for p in pages:
-            self._held[p] = False
-            self._free.append(p)
 
     def held_pages(self) -> List[int]:
-        return [p for p in range(self.reserved, self.num_pages) if self._held[p]]
+        return [p for p in range(self.reserved, self.num_pages) if self._pool.is_held(p)]

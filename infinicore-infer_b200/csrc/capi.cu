@@ -1,8 +1,11 @@
-// The C interface of model_api.h on top of the native runner: weights and cache pages on the device,
-// a page pool with per-request page lists, the packing of a batch's metadata, and sampling.
+// The C interface of model_api.h on top of the native step: weights and cache pages on the device, one page list per
+// cache handle, and sampling.
 //
-// It is the same step as the Python engine's: jk_runner_forward runs the kernels, this file only decides
-// which pages a request holds and describes the batch.  (The reference's counterpart is
+// It is the same step as the Python engine's, made of the same pieces: the model is the launch records that the
+// emitters of runner.cu write (the ones the Python parts call), jk_runner_run replays them, and the page pool, the
+// layout and packing of a batch's metadata, the attention's work lists, the rotary tables and the uniform numbers are
+// the functions of host_rules.h that the Python engine calls too.  This file only decides which pages a request holds
+// and arranges the records in this architecture's block.  (The reference's counterpart is
 // src/models/jiuge/jiuge.cpp:27-117 for the device resources and :300-350 for the two batch calls; its
 // caches are contiguous per request, src/cache_manager/kvcache.cpp, these are paged.)
 #include <dlfcn.h>
@@ -21,31 +24,7 @@ extern "C" const char *jk_runner_last_error();
 extern "C" int jk_runner_launches();
 
 namespace {
-
-constexpr int TILE_ROWS = 128;      // rows of a query tile of the prefill attention kernels
-constexpr int SHORT_ROWS = 8;       // a request with at most this many rows goes to the decode kernel
 constexpr long long WORKSPACE_BYTES = 32ll << 20;
-
-int align4(int n) { return (n + 3) & ~3; }
-
-// Where each array of a step's metadata lies in the one buffer that is copied per step.
-struct MetaLayout {
-    int tokens, positions, row_req, req_start, req_pos, want_rows, short_rows, tiles, block_table, total;
-    MetaLayout(int T, int B, int max_blocks) {
-        int o = 0;
-        tokens = o; o += align4(T);
-        positions = o; o += align4(T);
-        row_req = o; o += align4(T);
-        req_start = o; o += align4(B + 1);
-        req_pos = o; o += align4(B);
-        want_rows = o; o += align4(T);
-        short_rows = o; o += align4(T);
-        tiles = o; o += align4(2 * (T / TILE_ROWS + B));
-        block_table = o; o += align4(B * max_blocks);
-        total = o;
-    }
-};
-
 }  // namespace
 
 struct JkKVCache {
@@ -55,19 +34,18 @@ struct JkKVCache {
 struct JkModel {
     JkModelMeta meta{};
     int device = 0, page_size = 64, max_step_tokens = 2048, max_blocks = 0, max_requests = 0;
-    long long num_pages = 0;
-    RunnerModel rm{};
-    std::vector<RunnerLayer> layers;
-    RunnerScratch scratch{};
+    RunnerEnv env{};
+    std::vector<RunnerOp> ops;                   // the model as launch records: embedding, the layers, final norm, output product
+    RunnerBuffers buffers{};
+    std::vector<void *> k_pages, v_pages;        // per layer
+    const float *cos_table = nullptr, *sin_table = nullptr;
     std::vector<void *> device_allocs;
-    mutable std::vector<int> free_pages;         // page 0 is never handed out: padding rows write there
+    jk::PagePool *pool = nullptr;                // page 0 is never handed out: padding rows write there
     cudaStream_t stream = nullptr;
     int *meta_host = nullptr, *meta_dev = nullptr;
-    int meta_words = 0;
+    int meta_words = 0, extra_words = 0;
     float *logits = nullptr;
     long long logits_rows = 0;
-    float *decode_scratch = nullptr;
-    long long decode_floats = 0;
     int *out_dev = nullptr;                      // ids of the largest logits, then drawn ids: 2 * max_requests
     float *sample_dev = nullptr;                 // sampling parameters of a batch: 4 * max_requests
     size_t page_bytes = 0;                       // one page of one layer's keys (or values)
@@ -120,23 +98,15 @@ int upload_norm(JkModel *m, const float **dst, const void *src, int dtype, int n
     return JK_OK;
 }
 
-// Angle of pair j at position p: p / theta^(j / half), computed in double and rounded once.
 int upload_rotary_tables(JkModel *m) {
     const int half = m->meta.dh / 2, P = m->meta.dctx;
     std::vector<float> c((size_t)P * half), s((size_t)P * half);
-    std::vector<double> inv(half);
-    for (int j = 0; j < half; ++j) inv[j] = std::pow((double)m->meta.theta, -((double)j / half));
-    for (int p = 0; p < P; ++p)
-        for (int j = 0; j < half; ++j) {
-            const double a = (double)p * inv[j];
-            c[(size_t)p * half + j] = (float)std::cos(a);
-            s[(size_t)p * half + j] = (float)std::sin(a);
-        }
+    jk::rotary_tables((double)m->meta.theta, half, P, 1.0, c.data(), s.data());
     const void *pc = nullptr, *ps = nullptr;
     if (int rc = upload(m, &pc, c.data(), c.size() * sizeof(float), "the cosine table")) return rc;
     if (int rc = upload(m, &ps, s.data(), s.size() * sizeof(float), "the sine table")) return rc;
-    m->rm.cos_table = (const float *)pc;
-    m->rm.sin_table = (const float *)ps;
+    m->cos_table = (const float *)pc;
+    m->sin_table = (const float *)ps;
     return JK_OK;
 }
 
@@ -168,6 +138,10 @@ int bind_from_directory(JkModel *m, const char *dir, bool need_gemm_tcgen05, boo
     };
     f.embed = (EmbedFn)sym(ew, "jk_embed");
     f.add_rmsnorm = (AddRmsnormFn)sym(ew, "jk_add_rmsnorm");
+    f.residual_add = (ResidualAddFn)sym(ew, "jk_residual_add");
+    f.gemm_f32 = (GemmF32Fn)sym(ew, "jk_gemm_f32");
+    f.attention_rows = (AttentionRowsFn)sym(at, "jk_attention_rows");
+    f.attention_prefill_supports = (Supports1Fn)sym(at, "jk_attention_prefill_supports");
     f.swiglu = (SwigluFn)sym(ew, "jk_swiglu");
     f.rope_kv = (RopeKvFn)sym(ew, "jk_rope_kv");
     f.linear_small = (LinearSmallFn)sym(ls, "jk_linear_small");
@@ -195,63 +169,41 @@ int bind_from_directory(JkModel *m, const char *dir, bool need_gemm_tcgen05, boo
     return jk_runner_bind(&f);
 }
 
-bool takes_tcgen05(const RunnerModel &m, int rows, int n, int k) {
-    return runner_takes_tcgen05(m.sms, m.tcgen05_min_rows, m.tcgen05_min_tiles, m.tcgen05_min_fill_pct, rows, n, k);
-}
-
-// The gemm_tcgen05 module is loaded if a step can reach one of its kernels: the tiled one under the runner's
-// routing, or the few-rows one (a block for every SM).
-bool needs_gemm_tcgen05(const RunnerModel &rm, int max_step_tokens) {
-    const int nq = (rm.heads + 2 * rm.kv_heads) * rm.head_dim;
-    const int products[5][3] = {{nq, rm.hidden, RUNNER_F32}, {rm.hidden, rm.heads * rm.head_dim, RUNNER_RESIDUAL},
-                                {rm.intermediate, rm.hidden, RUNNER_SWIGLU}, {rm.hidden, rm.intermediate, RUNNER_RESIDUAL},
-                                {rm.vocab, rm.hidden, RUNNER_F32}};
-    const long long need = rm.skinny_min_blocks > 0 ? rm.skinny_min_blocks : rm.sms;
-    for (auto &p : products) {
-        if (takes_tcgen05(rm, max_step_tokens, p[2] == RUNNER_SWIGLU ? 2 * p[0] : p[0], p[1])) return true;
-        if (p[1] % 8 == 0 && runner_skinny_blocks(rm.sms, p[0], p[1], p[2]) >= need) return true;
+// The model as launch records, in the arrangement of this architecture's block (src/models/jiuge/jiuge.cpp:195-258):
+// norm, attention, norm, feed-forward, each branch added into the stream; the records of each part come from the
+// emitters that the Python parts use too.  Pointers that are not known yet (weights, pages) may be null: the same
+// function sizes the kernel modules before anything is on the device.
+void build_records(JkModel *m, const std::vector<const void *> &w_qkv, const std::vector<const float *> &b_qkv,
+                   const std::vector<const void *> &w_o, const std::vector<const void *> &w_gate_up,
+                   const std::vector<const void *> &w_down, const std::vector<const float *> &norm1,
+                   const std::vector<const float *> &norm2, const void *embedding, const void *lm_head, const float *final_norm) {
+    const JkModelMeta &a = m->meta;
+    const float softmax_scale = 1.f / std::sqrt((float)a.dh);
+    m->ops.clear();
+    m->ops.resize((size_t)a.nlayer * 7 + 3);
+    RunnerOp *at = m->ops.data();
+    at += jk_emit_embedding(at, embedding, JK_BF16, a.d, a.embed_scale);
+    for (int l = 0; l < a.nlayer; ++l) {
+        at += jk_emit_rmsnorm(at, norm1[l], a.d, a.epsilon, 1.f, 0);
+        at += jk_emit_attention(at, w_qkv[l], b_qkv[l], w_o[l], a.d, a.nh, a.nkvh, a.dh, 0, softmax_scale, a.residual_scale,
+                                m->cos_table, m->sin_table, 0, a.dctx, m->k_pages.empty() ? nullptr : m->k_pages[l],
+                                m->v_pages.empty() ? nullptr : m->v_pages[l], m->pool ? m->pool->num_pages() : 0, 0, 1, 0, 1);
+        at += jk_emit_rmsnorm(at, norm2[l], a.d, a.epsilon, 1.f, 0);
+        at += jk_emit_swiglu(at, w_gate_up[l], w_down[l], a.d, a.di, a.residual_scale);
     }
-    return false;
+    at += jk_emit_rmsnorm(at, final_norm, a.d, a.epsilon, a.logit_scale, 1);
+    at += jk_emit_output(at, lm_head, a.dvoc, a.d);
+    m->ops.resize((size_t)(at - m->ops.data()));
 }
 
-bool tcgen05_attention_takes(int dh, int page) {
-    return (dh == 64 || dh == 128) && (page == 8 || page == 16 || page == 32 || page == 64 || page == 128);
-}
-
-// How many ways the decode kernels cut each row's key range (the same rule as kernels.attention_decode_splits of
-// the Python side).  Head sizes 64 and 128, the tensor-core kernel: as many cuts as make the blocks fill the SMs once
-// (two blocks an SM, rounded) as long as a block keeps 256 keys, then up to two rounds of blocks as long as it keeps 1024.  Other
-// head sizes: full waves of blocks (three an SM) against a block's fixed cost of about 128 keys' worth of time.
-int decode_splits(int nrows, int nkvh, int group, int max_positions, int sms, int dh) {
-    const int keys = std::max(1, max_positions / 2);
-    if (dh == 64 || dh == 128) {
-        const long long blocks = std::max(1, nrows * nkvh * ((group + 15) / 16));
-        const long long slots = 2LL * sms;
-        long long s = std::max(1LL, std::min({(2 * slots + blocks) / (2 * blocks), (long long)keys / 256, 32LL}));      // slots / blocks, rounded
-        while (blocks * (s + 1) <= 2 * slots && keys / (s + 1) >= 1024 && s < 32) ++s;
-        return (int)s;
-    }
-    const long long blocks = std::max(1, nrows * nkvh * (group > 4 ? (group + 3) / 4 : 1));
-    const long long slots = (long long)sms * 3;
-    int best = 1;
-    double best_cost = -1;
-    for (int s = 1; s <= 32; ++s) {
-        if (s > 1 && (double)keys / s < 64) break;
-        const long long waves = (blocks * s + slots - 1) / slots;
-        const double cost = waves * (128 + (double)keys / s);
-        if (best_cost < 0 || cost < best_cost * 0.97) best = s, best_cost = cost;
-    }
-    return best;
-}
-
-float uniform_for(uint64_t seed, uint64_t index) {      // the splitmix64 finaliser, top 24 bits
-    uint64_t z = seed * 0x9E3779B97F4A7C15ull + (index + 1) * 0xBF58476D1CE4E5B9ull;
-    z ^= z >> 30;
-    z *= 0xBF58476D1CE4E5B9ull;
-    z ^= z >> 27;
-    z *= 0x94D049BB133111EBull;
-    z ^= z >> 31;
-    return (float)(z >> 40) / (float)(1 << 24);
+void set_environment(JkModel *m, int sms) {
+    RunnerEnv &e = m->env;
+    e.dtype = JK_BF16;
+    e.page_size = m->page_size;
+    e.max_blocks = m->max_blocks;
+    e.fused_norms = getenv("JK_NO_FUSED_NORM") == nullptr || getenv("JK_NO_FUSED_NORM")[0] != '1';
+    e.routing = jk::Routing{};        // the measured thresholds are the defaults of host_rules.h
+    e.routing.sms = sms;
 }
 
 int create(JkModel *m, const JkModelMeta *meta, const JkModelWeights *w, const JkModelOptions *opt) {
@@ -261,9 +213,8 @@ int create(JkModel *m, const JkModelMeta *meta, const JkModelWeights *w, const J
     JK_REQUIRE(L > 0 && d > 0 && nh > 0 && nkvh > 0 && dh > 0 && di > 0 && V > 0 && meta->dctx > 0,
                "create model: a size is not positive");
     JK_REQUIRE(nh % nkvh == 0, "create model: %d heads do not divide into %d key/value heads", nh, nkvh);
-    JK_REQUIRE(d % 32 == 0 && di % 32 == 0 && (nh * dh) % 32 == 0 && dh % 16 == 0 && dh <= 256,
-               "create model: width %d, feed-forward width %d and head size %d must be multiples of 32, 32 and 16 "
-               "(head size at most 256) for the kernels of this interface", d, di, dh);
+    JK_REQUIRE(d % 8 == 0 && di % 8 == 0 && (nh * dh) % 8 == 0 && dh % 2 == 0,
+               "create model: width %d, feed-forward width %d and head size %d must be multiples of 8, 8 and 2", d, di, dh);
     JK_REQUIRE(w->norm_dtype == JK_F32 || w->norm_dtype == JK_BF16, "create model: norm_dtype %d", w->norm_dtype);
     m->device = opt ? opt->device : 0;
     m->page_size = opt && opt->page_size ? opt->page_size : 64;
@@ -276,44 +227,33 @@ int create(JkModel *m, const JkModelMeta *meta, const JkModelWeights *w, const J
     JK_REQUIRE(prop.major == 10, "create model: the kernels are built for sm_100a, device %d is sm_%d%d", m->device, prop.major,
                prop.minor);
     CUDA_TRY(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking), "create model: stream");
-
-    RunnerModel &rm = m->rm;
-    rm.layers = L; rm.hidden = d; rm.heads = nh; rm.kv_heads = nkvh; rm.head_dim = dh; rm.intermediate = di; rm.vocab = V;
-    rm.page_size = m->page_size;
     m->max_blocks = (meta->dctx + m->page_size - 1) / m->page_size;
-    rm.max_blocks = m->max_blocks;
-    m->num_pages = (cache_tokens + m->page_size - 1) / m->page_size;
-    rm.num_pages = (int)m->num_pages + 1;
-    rm.window = 0;
-    rm.sms = prop.multiProcessorCount;
-    rm.tcgen05_min_rows = 129;       // the routing's measured thresholds: see runner_takes_tcgen05
-    rm.tcgen05_min_tiles = 200;
-    rm.tcgen05_min_fill_pct = 80;
-    rm.attention_tcgen05 = tcgen05_attention_takes(dh, m->page_size);
-    rm.fused_norms = getenv("JK_NO_FUSED_NORM") == nullptr || getenv("JK_NO_FUSED_NORM")[0] != '1';
-    rm.embed_dtype = JK_BF16;
-    rm.embed_scale = meta->embed_scale; rm.residual_scale = meta->residual_scale; rm.logit_scale = meta->logit_scale;
-    rm.softmax_scale = 1.f / std::sqrt((float)dh);
-    rm.final_eps = meta->epsilon;
+    const long long num_pages = (cache_tokens + m->page_size - 1) / m->page_size;
+    m->pool = new jk::PagePool((int)num_pages + 1, 1);
+    set_environment(m, prop.multiProcessorCount);
 
-    // the kernels
-    const int nq = (nh + 2 * nkvh) * dh;
-    const bool need_gemm = needs_gemm_tcgen05(rm, m->max_step_tokens);
+    // the kernels: which modules the records can reach is asked of the runner itself, on records without pointers
+    const std::vector<const void *> none((size_t)L, nullptr);
+    const std::vector<const float *> nonef((size_t)L, nullptr);
+    build_records(m, none, nonef, none, none, none, nonef, nonef, nullptr, nullptr, nullptr);
+    const bool need_gemm = jk_runner_needs_gemm_tcgen05(&m->env, m->ops.data(), (int)m->ops.size(), m->max_step_tokens) != 0;
+    const bool need_attention = jk::attention_tcgen05_takes(dh, m->page_size);
     if (opt && opt->kernel_dir) {
-        if (int rc = bind_from_directory(m, opt->kernel_dir, need_gemm, rm.attention_tcgen05 != 0)) return rc;
+        if (int rc = bind_from_directory(m, opt->kernel_dir, need_gemm, need_attention)) return rc;
     }
     const RunnerFns *fns = jk_runner_fns();
     JK_REQUIRE(fns != nullptr, "create model: no kernels are bound; give kernel_dir or call jk_runner_bind first");
     JK_REQUIRE(fns->argmax && fns->sample, "create model: the bound kernels lack the sampling entry points");
     JK_REQUIRE(!need_gemm || fns->gemm_tcgen05, "create model: steps of %d tokens need the tcgen05 product, which is not bound",
                m->max_step_tokens);
-    JK_REQUIRE(!rm.attention_tcgen05 || fns->attention_tcgen05, "create model: the tcgen05 attention kernel is not bound");
 
     // weights
-    if (int rc = upload(m, &rm.embedding, w->input_embd, (size_t)V * d * 2, "input_embd")) return rc;
-    if (w->output_embd == w->input_embd || w->output_embd == nullptr) rm.lm_head = rm.embedding;
-    else if (int rc = upload(m, &rm.lm_head, w->output_embd, (size_t)V * d * 2, "output_embd")) return rc;
-    if (int rc = upload_norm(m, &rm.final_norm, w->output_norm, w->norm_dtype, d, "output_norm")) return rc;
+    const void *embedding = nullptr, *lm_head = nullptr;
+    const float *final_norm = nullptr;
+    if (int rc = upload(m, &embedding, w->input_embd, (size_t)V * d * 2, "input_embd")) return rc;
+    if (w->output_embd == w->input_embd || w->output_embd == nullptr) lm_head = embedding;
+    else if (int rc = upload(m, &lm_head, w->output_embd, (size_t)V * d * 2, "output_embd")) return rc;
+    if (int rc = upload_norm(m, &final_norm, w->output_norm, w->norm_dtype, d, "output_norm")) return rc;
     if (meta->theta > 0.f)
         if (int rc = upload_rotary_tables(m)) return rc;
     JK_REQUIRE(w->attn_norm && w->attn_qkv && w->attn_o && w->ffn_norm && w->ffn_gate_up && w->ffn_down,
@@ -321,50 +261,56 @@ int create(JkModel *m, const JkModelMeta *meta, const JkModelWeights *w, const J
     void *status = nullptr;
     if (int rc = device_alloc(m, &status, sizeof(int), "status word")) return rc;
     CUDA_TRY(cudaMemset(status, 0, sizeof(int)), "status word");
-    rm.status = (int *)status;
+    m->env.status = (int *)status;
 
+    const int nq = (nh + 2 * nkvh) * dh;
     m->page_bytes = (size_t)nkvh * m->page_size * dh * 2;
-    m->layers.resize(L);
+    std::vector<const void *> w_qkv((size_t)L), w_o((size_t)L), w_gate_up((size_t)L), w_down((size_t)L);
+    std::vector<const float *> b_qkv((size_t)L, nullptr), norm1((size_t)L), norm2((size_t)L);
+    m->k_pages.resize((size_t)L); m->v_pages.resize((size_t)L);
     for (int l = 0; l < L; ++l) {
-        RunnerLayer &y = m->layers[l];
-        if (int rc = upload(m, &y.w_qkv, w->attn_qkv[l], (size_t)nq * d * 2, "attn_qkv")) return rc;
-        if (int rc = upload(m, &y.w_o, w->attn_o[l], (size_t)d * nh * dh * 2, "attn_o")) return rc;
-        if (int rc = upload(m, &y.w_gate_up, w->ffn_gate_up[l], (size_t)2 * di * d * 2, "ffn_gate_up")) return rc;
-        if (int rc = upload(m, &y.w_down, w->ffn_down[l], (size_t)d * di * 2, "ffn_down")) return rc;
-        if (int rc = upload_norm(m, &y.norm1, w->attn_norm[l], w->norm_dtype, d, "attn_norm")) return rc;
-        if (int rc = upload_norm(m, &y.norm2, w->ffn_norm[l], w->norm_dtype, d, "ffn_norm")) return rc;
-        y.eps1 = y.eps2 = meta->epsilon;
-        const size_t bytes = m->page_bytes * (size_t)rm.num_pages;
-        if (int rc = device_alloc(m, &y.k_pages, bytes, "key pages")) return rc;
-        if (int rc = device_alloc(m, &y.v_pages, bytes, "value pages")) return rc;
-        // Every page starts as zeros.  Page 0 is read by padding rows; of the others a kernel that loads whole pages
-        // (the tcgen05 attention, by TMA) also reads the slots beyond a request's last position, with weight 0 in
-        // the P V product: what lies there must be finite, and memory that cudaMalloc hands back need not be.
-        CUDA_TRY(cudaMemset(y.k_pages, 0, bytes), "key pages");
-        CUDA_TRY(cudaMemset(y.v_pages, 0, bytes), "value pages");
+        if (int rc = upload(m, &w_qkv[l], w->attn_qkv[l], (size_t)nq * d * 2, "attn_qkv")) return rc;
+        if (int rc = upload(m, &w_o[l], w->attn_o[l], (size_t)d * nh * dh * 2, "attn_o")) return rc;
+        if (int rc = upload(m, &w_gate_up[l], w->ffn_gate_up[l], (size_t)2 * di * d * 2, "ffn_gate_up")) return rc;
+        if (int rc = upload(m, &w_down[l], w->ffn_down[l], (size_t)d * di * 2, "ffn_down")) return rc;
+        if (int rc = upload_norm(m, &norm1[l], w->attn_norm[l], w->norm_dtype, d, "attn_norm")) return rc;
+        if (int rc = upload_norm(m, &norm2[l], w->ffn_norm[l], w->norm_dtype, d, "ffn_norm")) return rc;
+        if (w->attn_qkv_b != nullptr && w->attn_qkv_b[l] != nullptr) {
+            const void *b = nullptr;
+            if (int rc = upload(m, &b, w->attn_qkv_b[l], sizeof(float) * nq, "attn_qkv_b")) return rc;
+            b_qkv[l] = (const float *)b;
+        }
+        const size_t bytes = m->page_bytes * (size_t)m->pool->num_pages();
+        if (int rc = device_alloc(m, &m->k_pages[l], bytes, "key pages")) return rc;
+        if (int rc = device_alloc(m, &m->v_pages[l], bytes, "value pages")) return rc;
+        // Every page starts as zeros.  Page 0 is read by padding rows; what cudaMalloc hands back need not be finite, and
+        // no kernel should ever meet such bytes, not even with weight 0.
+        CUDA_TRY(cudaMemset(m->k_pages[l], 0, bytes), "key pages");
+        CUDA_TRY(cudaMemset(m->v_pages[l], 0, bytes), "value pages");
     }
-    m->free_pages.reserve(m->num_pages);
-    for (long long p = m->num_pages; p >= 1; --p) m->free_pages.push_back((int)p);      // low pages go out first
+    build_records(m, w_qkv, b_qkv, w_o, w_gate_up, w_down, norm1, norm2, embedding, lm_head, final_norm);
 
-    // buffers of a step
-    const size_t T = m->max_step_tokens;
-    RunnerScratch &s = m->scratch;
-    void *p = nullptr;
-    if (int rc = device_alloc(m, &p, T * d * 4, "x")) return rc; s.x = (float *)p;
-    if (int rc = device_alloc(m, &s.h, T * d * 2, "h")) return rc;
-    if (int rc = device_alloc(m, &p, T * nq * 4, "qkv")) return rc; s.qkv = (float *)p;
-    if (int rc = device_alloc(m, &s.q, T * nh * dh * 2, "q")) return rc;
-    if (int rc = device_alloc(m, &s.o, T * nh * dh * 2, "o")) return rc;
-    if (int rc = device_alloc(m, &p, T * d * 4, "delta")) return rc; s.delta = (float *)p;
-    if (int rc = device_alloc(m, &p, T * 2 * di * 4, "gate_up")) return rc; s.gate_up = (float *)p;
-    if (int rc = device_alloc(m, &s.act, T * di * 2, "act")) return rc;
-    if (int rc = device_alloc(m, &s.hw, T * d * 2, "hw")) return rc;
-    if (int rc = device_alloc(m, &s.workspace, WORKSPACE_BYTES, "workspace")) return rc;
-    s.workspace_bytes = WORKSPACE_BYTES;
-    if (int rc = device_alloc(m, &p, sizeof(unsigned long long) * 2 * L * 16, "sums of squares")) return rc;
-    s.sumsq = (unsigned long long *)p;
+    // buffers of a step: as many bytes per slot as the records ask for, sized once (captured or not, nothing moves later)
     m->max_requests = m->max_step_tokens;
-    m->meta_words = MetaLayout(m->max_step_tokens, m->max_requests, m->max_blocks).total;
+    long long bytes[RUNNER_SLOTS];
+    if (int rc = jk_runner_slot_bytes(&m->env, m->ops.data(), (int)m->ops.size(), m->max_step_tokens, m->max_step_tokens, bytes)) {
+        snprintf(jk_error_buffer(), 512, "%s", jk_runner_last_error());
+        return rc;
+    }
+    bytes[SLOT_LOGITS] = 0;       // the logits grow with the batches that ask for many rows (see run_batch)
+    for (int s = 0; s < RUNNER_SLOTS; ++s) {
+        m->buffers.bytes[s] = bytes[s];
+        if (bytes[s] > 0)
+            if (int rc = device_alloc(m, &m->buffers.slot[s], (size_t)bytes[s], "a step's buffer")) return rc;
+    }
+    if (int rc = device_alloc(m, &m->buffers.workspace, WORKSPACE_BYTES, "workspace")) return rc;
+    m->buffers.workspace_bytes = WORKSPACE_BYTES;
+    m->buffers.sumsq_rows = (int)m->ops.size();
+    void *p = nullptr;
+    if (int rc = device_alloc(m, &p, sizeof(unsigned long long) * 16 * m->ops.size(), "sums of squares")) return rc;
+    m->buffers.sumsq = (unsigned long long *)p;
+    m->extra_words = jk::attention_short_rows_capacity(m->max_step_tokens) + jk::attention_tiles_capacity(m->max_step_tokens, m->max_requests);
+    m->meta_words = jk::StepLayout(m->max_step_tokens, m->max_requests, 1, m->max_blocks, m->extra_words).total;
     CUDA_TRY(cudaMallocHost((void **)&m->meta_host, sizeof(int) * m->meta_words), "pinned metadata");
     if (int rc = device_alloc(m, &p, sizeof(int) * m->meta_words, "metadata")) return rc; m->meta_dev = (int *)p;
     if (int rc = device_alloc(m, &p, sizeof(int) * 2 * m->max_requests, "sampled ids")) return rc; m->out_dev = (int *)p;
@@ -400,14 +346,15 @@ int reserve_pages(JkModel *m, const uint32_t *req_lens, uint32_t nreq, const uin
         const long long want = (end + m->page_size - 1) / m->page_size;
         need += std::max(0ll, want - held);
     }
-    if (need > (long long)m->free_pages.size())
-        JK_FAIL(JK_UNSUPPORTED, "batch: %lld more cache pages are needed and %zu are free; drop a cache or make the pool larger",
-                need, m->free_pages.size());
+    if (need > (long long)m->pool->available())
+        JK_FAIL(JK_UNSUPPORTED, "batch: %lld more cache pages are needed and %d are free; drop a cache or make the pool larger",
+                need, m->pool->available());
     for (uint32_t i = 0; i < nreq; ++i) {
         const size_t want = ((size_t)req_pos[i] + req_lens[i] + m->page_size - 1) / m->page_size;
-        while (caches[i]->pages.size() < want) {
-            caches[i]->pages.push_back(m->free_pages.back());
-            m->free_pages.pop_back();
+        const size_t held = caches[i]->pages.size();
+        if (want > held) {
+            caches[i]->pages.resize(want);
+            m->pool->alloc((int)(want - held), caches[i]->pages.data() + held);
         }
     }
     return JK_OK;
@@ -423,68 +370,52 @@ int run_batch(JkModel *m, const uint32_t *tokens, uint32_t ntok, const uint32_t 
     long long sum = 0;
     for (uint32_t i = 0; i < nreq; ++i) sum += req_lens[i];
     JK_REQUIRE(sum == ntok, "batch: the requests' lengths add up to %lld, ntok is %u", sum, ntok);
+    for (uint32_t t = 0; t < ntok; ++t)
+        JK_REQUIRE(tokens[t] < (uint32_t)m->meta.dvoc, "batch: token %u is outside the vocabulary of %d", tokens[t], m->meta.dvoc);
     CUDA_TRY(cudaSetDevice(m->device), "batch: cudaSetDevice");
     if (int rc = reserve_pages(m, req_lens, nreq, req_pos, caches)) return rc;
     // the pinned buffer is free again: every call ends with a synchronisation of the stream
     const int T = (int)ntok, B = (int)nreq, mb = m->max_blocks;
-    const MetaLayout lay(T, B, mb);
+    const int extra = jk::attention_short_rows_capacity(T) + jk::attention_tiles_capacity(T, B);
+    const jk::StepLayout lay(T, B, 1, mb, extra);
     int *h = m->meta_host;
     memset(h, 0, sizeof(int) * lay.total);
-    int row = 0, n_short = 0, n_want = 0, max_end = 0;
-    struct Tile { int keys, req, row; };
-    std::vector<Tile> tiles;
+    std::vector<int> want, lens(B), starts(B), table((size_t)B * mb, 0);
+    int row = 0, longest = 0;
     for (int i = 0; i < B; ++i) {
-        const int n = (int)req_lens[i], s = (int)req_pos[i];
-        h[lay.req_start + i] = row;
-        h[lay.req_pos + i] = s;
-        for (int t = 0; t < n; ++t) {
-            JK_REQUIRE(tokens[row + t] < (uint32_t)m->meta.dvoc, "batch: token %u is outside the vocabulary of %d", tokens[row + t],
-                       m->meta.dvoc);
-            h[lay.tokens + row + t] = (int)tokens[row + t];
-            h[lay.positions + row + t] = s + t;
-            h[lay.row_req + row + t] = i;
-            if (all_rows) h[lay.want_rows + n_want++] = row + t;
-        }
-        if (!all_rows) h[lay.want_rows + n_want++] = row + n - 1;
-        if (n <= SHORT_ROWS)
-            for (int t = 0; t < n; ++t) h[lay.short_rows + n_short++] = row + t;
-        else
-            for (int t0 = 0; t0 < n; t0 += TILE_ROWS) tiles.push_back({s + t0, i, row + t0});
+        lens[i] = (int)req_lens[i]; starts[i] = (int)req_pos[i];
+        if (all_rows) for (int t = 0; t < lens[i]; ++t) want.push_back(row + t);
+        else want.push_back(row + lens[i] - 1);
         const std::vector<int> &pages = caches[i]->pages;
-        for (size_t b = 0; b < pages.size() && (int)b < mb; ++b) h[lay.block_table + i * mb + (int)b] = pages[b];
-        max_end = std::max(max_end, s + n);
-        row += n;
+        for (size_t b = 0; b < pages.size() && (int)b < mb; ++b) table[(size_t)i * mb + b] = pages[b];
+        longest = std::max(longest, starts[i] + lens[i]);
+        row += lens[i];
     }
-    h[lay.req_start + B] = row;
-    // the attention kernels start tiles in the order of the list: those that see the most keys first
-    std::stable_sort(tiles.begin(), tiles.end(), [](const Tile &a, const Tile &b) { return a.keys > b.keys; });
-    for (size_t t = 0; t < tiles.size(); ++t) {
-        h[lay.tiles + 2 * (int)t] = tiles[t].req;
-        h[lay.tiles + 2 * (int)t + 1] = tiles[t].row;
-    }
+    const int *tables[1] = {table.data()};
+    jk::pack_step(h, lay, B, B, (const int *)tokens, lens.data(), starts.data(), nullptr, want.data(), (int)want.size(), 1, mb, tables);
+    int *short_rows = h + lay.extra, *tiles = short_rows + jk::attention_short_rows_capacity(T);
+    const jk::AttentionLists lists = jk::attention_work_lists(B, B, lens.data(), starts.data(), short_rows, tiles);
     CUDA_TRY(cudaMemcpyAsync(m->meta_dev, h, sizeof(int) * lay.total, cudaMemcpyHostToDevice, m->stream), "batch: metadata");
 
-    int splits = 1;
-    if (n_short) {
-        splits = decode_splits(n_short, m->meta.nkvh, m->meta.nh / m->meta.nkvh, m->meta.dctx, m->rm.sms, m->meta.dh);
-        const long long need = splits > 1 ? (long long)n_short * m->meta.nh * splits * (m->meta.dh + 2) : 0;
-        if (int rc = grow(m, (void **)&m->decode_scratch, &m->decode_floats, need, sizeof(float), "batch: attention scratch")) return rc;
-        m->scratch.decode_scratch = m->decode_scratch;
-    }
+    const int n_want = (int)want.size();
     long long logit_rows = m->logits_rows;
     if (int rc = grow(m, (void **)&m->logits, &logit_rows, n_want, sizeof(float) * m->meta.dvoc, "batch: logits")) return rc;
     m->logits_rows = logit_rows;
+    m->buffers.slot[SLOT_LOGITS] = m->logits;
+    m->buffers.bytes[SLOT_LOGITS] = (long long)sizeof(float) * m->meta.dvoc * m->logits_rows;
 
     RunnerStep st{};
-    st.ntok = T; st.nreq = B; st.n_want = n_want; st.n_tiles = (int)tiles.size(); st.n_short = n_short; st.splits = splits;
+    st.ntok = T; st.nreq = B; st.n_want = n_want;
+    st.context = jk::context_bucket(longest, m->meta.dctx);
     const int *dv = m->meta_dev;
     st.tokens = dv + lay.tokens; st.positions = dv + lay.positions; st.row_req = dv + lay.row_req;
     st.req_start = dv + lay.req_start; st.req_pos = dv + lay.req_pos; st.want_rows = dv + lay.want_rows;
-    st.short_rows = n_short == T ? nullptr : dv + lay.short_rows;
-    st.tiles = tiles.empty() ? nullptr : dv + lay.tiles;
-    st.block_table = dv + lay.block_table;
-    st.logits = m->logits;
-    const int rc = jk_runner_forward(&m->rm, m->layers.data(), &st, &m->scratch, m->stream);
+    st.block_tables[0] = dv + lay.tables[0];
+    st.lists[0] = lists.n_short == T ? nullptr : dv + lay.extra;       // every row is a short row: no list is needed
+    st.list_n[0] = lists.n_short;
+    st.lists[1] = lists.n_tiles ? dv + lay.extra + jk::attention_short_rows_capacity(T) : nullptr;
+    st.list_n[1] = lists.n_tiles;
+    const int rc = jk_runner_run(&m->env, m->ops.data(), 0, (int)m->ops.size(), &st, &m->buffers, 0, m->stream);
     m->last_launches = jk_runner_launches();
     return rc;
 }
@@ -492,9 +423,9 @@ int run_batch(JkModel *m, const uint32_t *tokens, uint32_t ntok, const uint32_t 
 // After the stream is idle: did a kernel give up a bounded wait?
 int check_status(JkModel *m) {
     int status = 0;
-    CUDA_TRY(cudaMemcpy(&status, m->rm.status, sizeof(int), cudaMemcpyDeviceToHost), "batch: status word");
+    CUDA_TRY(cudaMemcpy(&status, m->env.status, sizeof(int), cudaMemcpyDeviceToHost), "batch: status word");
     if (status != 0) {
-        cudaMemset(m->rm.status, 0, sizeof(int));
+        cudaMemset(m->env.status, 0, sizeof(int));
         if (status == 4)
             JK_FAIL(JK_CUDA_ERROR, "batch: a row's sum of squares is beyond the range of the fixed-point counters; the results "
                                    "of this batch are invalid (JK_NO_FUSED_NORM=1 keeps the norm kernels, which have no such limit)");
@@ -509,17 +440,22 @@ JK_EXPORT const char *jkLastError(void) { return jk_runner_last_error(); }
 
 JK_EXPORT int jkKernelModules(const JkModelMeta *meta, const JkModelOptions *opt, char *out, int size) {
     JK_REQUIRE(meta && out && size > 0, "kernel modules: an argument is missing");
-    RunnerModel rm{};
-    rm.hidden = meta->d; rm.heads = meta->nh; rm.kv_heads = meta->nkvh; rm.head_dim = meta->dh; rm.intermediate = meta->di;
-    rm.vocab = meta->dvoc;
-    rm.sms = 148; rm.tcgen05_min_rows = 129; rm.tcgen05_min_tiles = 200; rm.tcgen05_min_fill_pct = 80;
-    int device = 0;
+    JkModel probe;
+    probe.meta = *meta;
+    probe.page_size = opt && opt->page_size ? opt->page_size : 64;
+    probe.max_blocks = (meta->dctx + probe.page_size - 1) / probe.page_size;
+    int device = 0, sms = 148;
     cudaDeviceProp prop;
     if (cudaGetDevice(&device) == cudaSuccess && cudaGetDeviceProperties(&prop, opt ? opt->device : device) == cudaSuccess)
-        rm.sms = prop.multiProcessorCount;
+        sms = prop.multiProcessorCount;
+    set_environment(&probe, sms);
+    const std::vector<const void *> none((size_t)meta->nlayer, nullptr);
+    const std::vector<const float *> nonef((size_t)meta->nlayer, nullptr);
+    build_records(&probe, none, nonef, none, none, none, nonef, nonef, nullptr, nullptr, nullptr);
     std::string list = "elementwise,linear_small,attention,sampling,runner";
-    if (needs_gemm_tcgen05(rm, opt && opt->max_step_tokens ? opt->max_step_tokens : 2048)) list += ",gemm_tcgen05";
-    if (tcgen05_attention_takes(meta->dh, opt && opt->page_size ? opt->page_size : 64)) list += ",attention_tcgen05";
+    if (jk_runner_needs_gemm_tcgen05(&probe.env, probe.ops.data(), (int)probe.ops.size(), opt && opt->max_step_tokens ? opt->max_step_tokens : 2048))
+        list += ",gemm_tcgen05";
+    if (jk::attention_tcgen05_takes(meta->dh, probe.page_size)) list += ",attention_tcgen05";
     JK_REQUIRE((int)list.size() < size, "kernel modules: the list needs %zu bytes", list.size() + 1);
     snprintf(out, size, "%s", list.c_str());
     return JK_OK;
@@ -542,10 +478,10 @@ JK_EXPORT void jkDestroyModel(JkModel *m) {
     if (m->stream) cudaStreamSynchronize(m->stream);
     for (void *p : m->device_allocs) cudaFree(p);
     if (m->logits) cudaFree(m->logits);
-    if (m->decode_scratch) cudaFree(m->decode_scratch);
     if (m->meta_host) cudaFreeHost(m->meta_host);
     if (m->stream) cudaStreamDestroy(m->stream);
     // the kernel modules stay loaded: the runner's table still points into them
+    delete m->pool;
     delete m;
 }
 
@@ -556,7 +492,9 @@ JK_EXPORT JkKVCache *jkCreateKVCache(const JkModel *m) {
 
 JK_EXPORT void jkDropKVCache(const JkModel *m, JkKVCache *c) {
     if (m == nullptr || c == nullptr) return;
-    for (auto it = c->pages.rbegin(); it != c->pages.rend(); ++it) m->free_pages.push_back(*it);
+    // the page taken last goes back first, so that it is the last of these to be handed out again
+    std::vector<int> back(c->pages.rbegin(), c->pages.rend());
+    m->pool->free(back.data(), (int)back.size());
     delete c;
 }
 
@@ -569,24 +507,23 @@ JK_EXPORT JkKVCache *jkDuplicateKVCache(const JkModel *m, const JkKVCache *src, 
                  src->pages.size() * m->page_size);
         return nullptr;
     }
-    if (pages > m->free_pages.size()) {
-        snprintf(err, 512, "duplicate cache: %zu pages needed, %zu free", pages, m->free_pages.size());
+    if ((long long)pages > m->pool->available()) {
+        snprintf(err, 512, "duplicate cache: %zu pages needed, %d free", pages, m->pool->available());
         return nullptr;
     }
     cudaSetDevice(m->device);
     JkKVCache *c = new JkKVCache();
-    for (size_t b = 0; b < pages; ++b) {
-        c->pages.push_back(m->free_pages.back());
-        m->free_pages.pop_back();
-    }
+    c->pages.resize(pages);
+    m->pool->alloc((int)pages, c->pages.data());
     cudaError_t e = cudaSuccess;
-    for (const RunnerLayer &y : m->layers)
+    for (size_t l = 0; l < m->k_pages.size(); ++l)
         for (size_t b = 0; b < pages && e == cudaSuccess; ++b) {
             const size_t from = (size_t)src->pages[b] * m->page_bytes, to = (size_t)c->pages[b] * m->page_bytes;
-            e = cudaMemcpyAsync((char *)y.k_pages + to, (const char *)y.k_pages + from, m->page_bytes, cudaMemcpyDeviceToDevice, m->stream);
+            e = cudaMemcpyAsync((char *)m->k_pages[l] + to, (const char *)m->k_pages[l] + from, m->page_bytes, cudaMemcpyDeviceToDevice,
+                                m->stream);
             if (e == cudaSuccess)
-                e = cudaMemcpyAsync((char *)y.v_pages + to, (const char *)y.v_pages + from, m->page_bytes, cudaMemcpyDeviceToDevice,
-                                    m->stream);
+                e = cudaMemcpyAsync((char *)m->v_pages[l] + to, (const char *)m->v_pages[l] + from, m->page_bytes,
+                                    cudaMemcpyDeviceToDevice, m->stream);
         }
     if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
     if (e != cudaSuccess) {
@@ -631,7 +568,7 @@ JK_EXPORT int jkInferBatch(JkModel *m, const uint32_t *tokens, uint32_t ntok, co
             const int k = topk ? (int)topk[i] : 0;
             memcpy(&par[B + i], &k, 4);
             par[2 * B + i] = topp ? topp[i] : 1.f;
-            par[3 * B + i] = uniform_for(seeds ? seeds[i] : 0, (uint64_t)req_pos[i] + req_lens[i]);
+            par[3 * B + i] = jk::uniform_for(seeds ? seeds[i] : 0, (uint64_t)req_pos[i] + req_lens[i]);
         }
         // the copy reads pageable memory: it has finished with `par` when it returns
         CUDA_TRY(cudaMemcpyAsync(m->sample_dev, par.data(), sizeof(float) * par.size(), cudaMemcpyHostToDevice, m->stream),
@@ -648,5 +585,5 @@ JK_EXPORT int jkInferBatch(JkModel *m, const uint32_t *tokens, uint32_t ntok, co
     return check_status(m);
 }
 
-JK_EXPORT int64_t jkFreePages(const JkModel *m) { return m ? (int64_t)m->free_pages.size() : 0; }
+JK_EXPORT int64_t jkFreePages(const JkModel *m) { return m && m->pool ? (int64_t)m->pool->available() : 0; }
 JK_EXPORT int32_t jkLastLaunches(const JkModel *m) { return m ? m->last_launches : 0; }

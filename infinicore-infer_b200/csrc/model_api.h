@@ -44,6 +44,7 @@ typedef struct {
     const void *const *ffn_norm;      /* nlayer * [d] */
     const void *const *ffn_gate_up;   /* nlayer * bfloat16 [2 di, d]: gate rows, then up rows */
     const void *const *ffn_down;      /* nlayer * bfloat16 [d, di] */
+    const void *const *attn_qkv_b;    /* null, or nlayer * float32 [(nh + 2 nkvh) * dh]: the q, k and v biases (an entry may be null) */
 } JkModelWeights;
 
 typedef struct {

@@ -31,7 +31,7 @@ class _Weights(ctypes.Structure):
     _fields_ = [("norm_dtype", ctypes.c_int32), ("input_embd", ctypes.c_void_p), ("output_norm", ctypes.c_void_p),
                 ("output_embd", ctypes.c_void_p)] \
         + [(n, ctypes.POINTER(ctypes.c_void_p)) for n in ("attn_norm", "attn_qkv", "attn_o", "ffn_norm", "ffn_gate_up",
-                                                          "ffn_down")]
+                                                          "ffn_down", "attn_qkv_b")]
 
 
 class _Options(ctypes.Structure):
@@ -59,8 +59,6 @@ class NativeModel:
         spec = config.model_spec()
         blocks = [spec.layers[e.layer] for e in spec.order]
         a, f = blocks[0].mixer, blocks[0].feed_forward
-        if a.bias:
-            raise NativeModelError("the C interface takes attention without bias")
         L = len(blocks)
         self.lib = _build.load("runner")
         lib = self.lib
@@ -107,6 +105,8 @@ class NativeModel:
             output_embd=embd if tied else mat(source.get(spec.lm_head_name)),
             attn_norm=per_layer("norm1"), attn_qkv=per_layer("w_qkv"), attn_o=per_layer("w_o"),
             ffn_norm=per_layer("norm2"), ffn_gate_up=per_layer("w_gate_up"), ffn_down=per_layer("w_down"))
+        if a.bias:
+            w.attn_qkv_b = (ctypes.c_void_p * L)(*[mat(one["b_qkv"].float().contiguous()) for one in packed])
         meta = _Meta(nlayer=L, d=spec.hidden_size, nh=a.num_heads, nkvh=a.num_kv_heads, dh=a.head_dim,
                      di=f.intermediate_size, dctx=spec.max_positions, dvoc=spec.vocab_size, epsilon=blocks[0].mixer_norm.eps,
                      theta=a.position.theta if a.position is not None else 0.0, embed_scale=spec.embed_scale,

@@ -195,12 +195,8 @@ class Scheduler:
     def _can_ever_fit(self, r: Request) -> bool:
         """Could the request's next token ever be computed, alone in an empty cache?"""
         total = len(r.prompt) + len(r.generated)
-        ps = self.cache.page_size
-        for g in self.cache.groups:
-            span = total if g.need.window is None else min(total, g.need.window + self.chunk_size + ps)
-            if (span + ps - 1) // ps > g.pool.capacity:
-                return False
-        return True
+        return all(g.need.most_pages_alone(total, self.chunk_size, self.cache.page_size) <= g.pool.capacity
+                   for g in self.cache.groups)
 
     def _preempt_youngest(self) -> None:
         victim = max(self.running, key=lambda r: r.arrival)

@@ -23,7 +23,8 @@ import torch
 
 from ..cache import CacheManager, OutOfPages
 from ..config import read_config
-from ..parts import SHORT_ROWS, TILE_ROWS, Model, Runtime, StepContext, cache_needs, model_manifest
+from ..kernels import host as host_rules
+from ..parts import Model, ProgramRunner, Runtime, StepContext, cache_needs, model_manifest
 from ..weights import FileWeights, check_manifest
 
 
@@ -40,38 +41,13 @@ class StepError(ValueError):
     """A step that cannot run as given (bad token, context overflow, unknown place)."""
 
 
-def _align(n: int, a: int = 4) -> int:
-    return (n + a - 1) // a * a
-
-
-class _Layout:
-    """Offsets (in int32 elements) of a step's arrays inside the metadata buffer."""
-
-    def __init__(self, T: int, B: int, n_groups: int, max_blocks: int):
-        self.T, self.B = T, B
-        o = 0
-        self.tokens = o; o += _align(T)
-        self.positions = o; o += _align(T)
-        self.row_req = o; o += _align(T)
-        self.want_rows = o; o += _align(T)
-        self.req_start = o; o += _align(B + 1)
-        self.req_pos = o; o += _align(B)
-        self.slot_ids = o; o += _align(B)
-        self.short_rows = o; o += _align(T)
-        self.tiles = o; o += _align(2 * (T // TILE_ROWS + B))
-        self.tables = []
-        for _ in range(n_groups):
-            self.tables.append(o); o += _align(B * max_blocks)
-        self.total = o
-
-
 class Engine:
     """A model, its cache and the step function over them."""
 
     def __init__(self, spec, weights, dtype: torch.dtype = torch.bfloat16, device="cuda:0",
                  cache_tokens: int = 4096, page_size: int = 16, max_requests: int = 64,
                  max_step_tokens: int = 8192, use_graphs: bool = True, native_runner: bool = True,
-                 strict_weights: bool = False):
+                 strict_weights: bool = False, context_buckets: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
         self.spec = spec
@@ -89,22 +65,28 @@ class Engine:
         self.max_requests = max_requests
         self.max_step_tokens = max_step_tokens
         self.use_graphs = use_graphs and self.model.graph_safe
-        n_groups, mb = len(self.cache.groups), self.cache.max_blocks
-        cap = _Layout(max_step_tokens, max_requests, n_groups, mb).total
+        # The model as launch records (parts/program.py) and the buffers that a step replays them over.  With
+        # ``native_runner=False`` (or JK_NO_RUNNER=1) every record is a call of its own, so that no record shares work
+        # with its neighbours: the unfused way of running the same program.
+        self.program = self.model.plan(self.cache.views, page_size, self.cache.max_blocks)
+        one_by_one = not native_runner or os.environ.get("JK_NO_RUNNER") == "1"
+        self.runner = ProgramRunner(self.program, max_step_tokens, one_by_one=one_by_one)
+        # what the mixers ask every step to carry (work lists), after the arrays that every model needs
+        self._list_owners = list(self.program.list_owners)
+        self._layouts: Dict[tuple, tuple] = {}
+        cap = self._layout(max_step_tokens, max_requests)[0].total
         self._meta_dev = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self._meta_host = [torch.zeros(cap, dtype=torch.int32, pin_memory=True) for _ in range(3)]
         self._meta_events: List[Optional[torch.cuda.Event]] = [None] * 3
         self._meta_turn = 0
-        self._decode_templates: Dict[int, tuple] = {}
-        self._graphs: Dict[int, object] = {}
+        self._table_scratch = [np.zeros((max_requests, self.cache.max_blocks), dtype=np.int32) for _ in self.cache.groups]
+        self._graphs: Dict[tuple, object] = {}
+        # Captured decode steps are kept per (batch bucket, context bucket): how the decode attention cuts a row's keys
+        # follows the live requests' lengths, not the model's longest context.
+        self.context_buckets = context_buckets
         self.steps_run = 0
         self.tokens_run = 0
         self.kernel_launches = 0      # this package's kernels launched by steps (replayed graphs included)
-        # the standard stack is issued from native code (csrc/runner.cu); other models through the parts
-        self.runner = None
-        if native_runner and os.environ.get("JK_NO_RUNNER") != "1":
-            from .runner import NativeRunner
-            self.runner = NativeRunner.build(self)
 
     # ---- construction -------------------------------------------------------------------------
     @classmethod
@@ -156,11 +138,9 @@ class Engine:
         if decode:
             logits = self._run_decode_graph(entries, starts)
         else:
-            from .. import kernels
             ctx = self._upload(entries, starts, len(entries), sum(len(e.tokens) for e in entries))
-            before = kernels.launch_count
             logits = self._forward(ctx)
-            self.kernel_launches += kernels.launch_count - before
+            self.kernel_launches += self.runner.launches
         for r, n in new_len.items():
             self.cache.commit(r, n)
         self.steps_run += 1
@@ -168,12 +148,7 @@ class Engine:
         return logits
 
     def _forward(self, ctx: StepContext) -> torch.Tensor:
-        if self.runner is not None:
-            from .. import kernels
-            logits = self.runner.forward(ctx)
-            kernels.launch_count += self.runner.launches
-            return logits
-        return self.model.forward(ctx, self.cache.views)
+        return self.runner.forward(ctx, self.spec.vocab_size)
 
     # ---- checks that run before anything touches the device ------------------------------------
     def _validate(self, entries: Sequence[StepEntry]) -> None:
@@ -202,120 +177,94 @@ class Engine:
             raise StepError(f"{new} new requests but {self.cache.slots.available} request slots free")
 
     # ---- host -> device metadata ------------------------------------------------------------------
-    def _upload(self, entries, starts, B: int, T: int, pad_to: Optional[int] = None) -> StepContext:
-        """Fill the pinned buffer, copy it in one piece, return views of the device copy.
+    def _layout(self, T: int, B: int):
+        """The layout of a step of T rows and B requests, with the place of every work list in its extra words."""
+        key = (T, B)
+        made = self._layouts.get(key)
+        if made is None:
+            places, extra = [], 0
+            for owner in self._list_owners:
+                for name, words in owner.step_list_capacity(T, B).items():
+                    places.append((owner, name, extra, words))
+                    extra += (words + 3) // 4 * 4
+            lay = host_rules.StepLayout(T, B, len(self.cache.groups), self.cache.max_blocks, extra)
+            made = self._layouts[key] = (lay, places)
+        return made
 
-        ``pad_to``: batch size of a captured decode step; missing entries become rows that use
-        slot 0 and the null page at position 0.
-        """
-        nB = pad_to or B
-        nT = pad_to or T
-        lay = _Layout(nT, nB, len(self.cache.groups), self.cache.max_blocks)
+    def _pack(self, entries, starts, B: int, T: int, pad_to: Optional[int] = None):
+        """Fill a pinned buffer with the step's metadata (``jk::pack_step`` and the mixers' work lists) and copy it in
+        one piece.  ``pad_to``: batch size of a captured decode step; missing entries become rows that use slot 0
+        and the null page at position 0, and every row is a wanted row."""
+        nB, nT = pad_to or B, pad_to or T
+        lay, places = self._layout(nT, nB)
         turn = self._meta_turn
         self._meta_turn = (turn + 1) % len(self._meta_host)
         if self._meta_events[turn] is not None:
             self._meta_events[turn].synchronize()
         host = self._meta_host[turn].numpy()
-        host[:lay.total] = 0
-        row = 0
-        want_rows: List[int] = []
-        req_start = [0]
-        for i, (e, s) in enumerate(zip(entries, starts)):
+        tokens: List[int] = []
+        want: List[int] = []
+        lens = []
+        for e in entries:
             n = len(e.tokens)
-            host[lay.tokens + row: lay.tokens + row + n] = np.asarray(e.tokens, dtype=np.int32)
-            host[lay.positions + row: lay.positions + row + n] = np.arange(s, s + n, dtype=np.int32)
-            host[lay.row_req + row: lay.row_req + row + n] = i
-            want_rows.extend(row + w for w in e.want)
-            row += n
-            req_start.append(row)
-        for i in range(B, nB):           # padding rows of a captured step
-            host[lay.row_req + row] = i
-            row += 1
-            req_start.append(row)
-        short_rows: List[int] = []
-        tile_list: List[tuple] = []
-        for i in range(nB):
-            r0, r1 = req_start[i], req_start[i + 1]
-            if r1 - r0 <= SHORT_ROWS:
-                short_rows.extend(range(r0, r1))
-            else:
-                for t0 in range(r0, r1, TILE_ROWS):
-                    tile_list.append((starts[i] + (t0 - r0), i, t0))
-        # the attention kernels start tiles in the order of the list: those that see the most keys first
-        tile_list.sort(key=lambda t: -t[0])
-        tiles: List[int] = [v for t in tile_list for v in t[1:]]
-        host[lay.short_rows: lay.short_rows + len(short_rows)] = short_rows
-        host[lay.tiles: lay.tiles + len(tiles)] = tiles
-        n_want = len(want_rows)
-        if pad_to:                       # a captured step computes logits for every row
-            want_rows = list(range(nT))
-        host[lay.want_rows: lay.want_rows + len(want_rows)] = want_rows
-        host[lay.req_start: lay.req_start + nB + 1] = req_start
-        host[lay.req_pos: lay.req_pos + B] = starts
+            want.extend(len(tokens) + w for w in e.want)
+            tokens.extend(e.tokens)
+            lens.append(n)
+        n_want = len(want)
+        if pad_to:
+            want = list(range(nT))
         reqs = [e.req_id for e in entries]
         slots = self.cache.slot_ids(reqs)
-        host[lay.slot_ids: lay.slot_ids + B] = slots
-        mb = self.cache.max_blocks
-        for gi, off in enumerate(lay.tables):
-            self.cache.block_table_rows(gi, reqs, host[off: off + nB * mb].reshape(nB, mb))
-        self._copy_meta(turn, lay.total)
-        ctx = self._context(lay, len(want_rows))
-        ctx.host_req_start = req_start
-        ctx.host_req_pos = list(starts) + [0] * (nB - B)
-        ctx.host_slot_ids = list(slots) + [0] * (nB - B)
-        ctx.n_want = n_want if not pad_to else nT
-        ctx.n_short, ctx.n_tiles = len(short_rows), len(tiles) // 2
-        ctx.short_rows = None if ctx.n_short == nT else self._meta_dev[lay.short_rows: lay.short_rows + ctx.n_short]
-        ctx.tiles = self._meta_dev[lay.tiles: lay.tiles + len(tiles)]
-        return ctx
-
-    def _copy_meta(self, turn: int, words: int) -> None:
-        self._meta_dev[:words].copy_(self._meta_host[turn][:words], non_blocking=True)
+        tables = []
+        for gi in range(len(self.cache.groups)):
+            rows = self._table_scratch[gi][:B]
+            self.cache.block_table_rows(gi, reqs, rows)
+            tables.append(rows)
+        host_rules.pack_step(host, lay, B, tokens, lens, starts, slots, want, tables)
+        counts = {}
+        for owner in self._list_owners:
+            arrays = {name: host[lay.extra + off: lay.extra + off + max(words, 1)] for o, name, off, words in places if o is owner}
+            for name, got in owner.fill_step_lists(B, nB, lens, starts, arrays).items():
+                counts[f"{owner.__name__}.{name}"] = got
+        self._meta_dev[:lay.total].copy_(self._meta_host[turn][:lay.total], non_blocking=True)
         if self._meta_events[turn] is None:
             self._meta_events[turn] = torch.cuda.Event()
         self._meta_events[turn].record()
+        return lay, places, counts, lens, slots, (n_want if not pad_to else nT), len(want)
 
-    def _upload_decode_replay(self, entries, starts, bucket: int) -> None:
-        """The upload of a captured decode step that is only replayed: the same buffer contents as
-        ``_upload(..., pad_to=bucket)`` gives, without the device views that only a capture needs.
-        What does not change from step to step comes from a template made once per bucket."""
-        B = len(entries)
-        made = self._decode_templates.get(bucket)
-        if made is None:
-            lay = _Layout(bucket, bucket, len(self.cache.groups), self.cache.max_blocks)
-            t = np.zeros(lay.total, dtype=np.int32)
-            t[lay.row_req: lay.row_req + bucket] = np.arange(bucket)
-            t[lay.req_start: lay.req_start + bucket + 1] = np.arange(bucket + 1)
-            t[lay.short_rows: lay.short_rows + bucket] = np.arange(bucket)
-            t[lay.want_rows: lay.want_rows + bucket] = np.arange(bucket)
-            made = self._decode_templates[bucket] = (lay, t)
-        lay, template = made
-        turn = self._meta_turn
-        self._meta_turn = (turn + 1) % len(self._meta_host)
-        if self._meta_events[turn] is not None:
-            self._meta_events[turn].synchronize()
-        host = self._meta_host[turn].numpy()
-        host[:lay.total] = template
-        host[lay.tokens: lay.tokens + B] = [e.tokens[0] for e in entries]
-        host[lay.positions: lay.positions + B] = starts
-        host[lay.req_pos: lay.req_pos + B] = starts
-        reqs = [e.req_id for e in entries]
-        host[lay.slot_ids: lay.slot_ids + B] = self.cache.slot_ids(reqs)
-        mb = self.cache.max_blocks
-        for gi, off in enumerate(lay.tables):
-            self.cache.block_table_rows(gi, reqs, host[off: off + bucket * mb].reshape(bucket, mb))
-        self._copy_meta(turn, lay.total)
+    def _context_of(self, starts, lens) -> int:
+        if not self.context_buckets:
+            return 0
+        longest = max((s + n for s, n in zip(starts, lens)), default=1)
+        return host_rules.context_bucket(longest, self.spec.max_positions)
 
-    def _context(self, lay: _Layout, n_want: int) -> StepContext:
+    def _upload(self, entries, starts, B: int, T: int, pad_to: Optional[int] = None, context: Optional[int] = None) -> StepContext:
+        """Pack and copy the step's metadata; return views of the device copy."""
+        lay, places, counts, lens, slots, n_want, n_rows_wanted = self._pack(entries, starts, B, T, pad_to)
         m, mb = self._meta_dev, self.cache.max_blocks
         sl = lambda off, n: m[off: off + n]
-        return StepContext(
+        ctx = StepContext(
             ntok=lay.T, nreq=lay.B,
             tokens=sl(lay.tokens, lay.T), positions=sl(lay.positions, lay.T),
             row_req=sl(lay.row_req, lay.T), req_start=sl(lay.req_start, lay.B + 1),
             req_pos=sl(lay.req_pos, lay.B), slot_ids=sl(lay.slot_ids, lay.B),
             block_tables=[sl(off, lay.B * mb).view(lay.B, mb) for off in lay.tables],
-            want_rows=sl(lay.want_rows, n_want), n_want=n_want)
+            want_rows=sl(lay.want_rows, n_rows_wanted), n_want=n_want)
+        ctx.context = self._context_of(starts, lens) if context is None else context
+        for owner, name, off, words in places:
+            count, identity = counts[f"{owner.__name__}.{name}"]
+            ctx.lists[f"{owner.__name__}.{name}"] = (None if identity else sl(lay.extra + off, max(count, 1)), count)
+        row, req_start = 0, [0]
+        for n in lens:
+            row += n
+            req_start.append(row)
+        for _ in range(lay.B - B):
+            row += 1
+            req_start.append(row)
+        ctx.host_req_start = req_start
+        ctx.host_req_pos = list(starts) + [0] * (lay.B - B)
+        ctx.host_slot_ids = list(slots) + [0] * (lay.B - B)
+        return ctx
 
     # ---- decode steps as CUDA graphs -----------------------------------------------------------------
     @staticmethod
@@ -330,23 +279,20 @@ class Engine:
         bucket = self._bucket(B)
         if bucket > self.max_requests:
             bucket = B
-        rec = self._graphs.get(bucket)
+        context = self._context_of(starts, [1] * B)
+        key = (bucket, context)
+        rec = self._graphs.get(key)
         if rec is None:
             # Warm up (library handles, lazy module loads) on a batch of padding rows only: they touch
             # the null page and slot 0, so a mixer whose state update is not idempotent sees the real
             # step exactly once, at the replay below.
-            dummy = self._upload([], [], 0, 0, pad_to=bucket)
+            dummy = self._upload([], [], 0, 0, pad_to=bucket, context=context)
             dummy.decode_only = True
             self._forward(dummy)
             torch.cuda.synchronize()
-        if rec is not None:
-            self._upload_decode_replay(entries, starts, bucket)
-        else:
-            ctx = self._upload(entries, starts, B, B, pad_to=bucket)
+            ctx = self._upload(entries, starts, B, B, pad_to=bucket, context=context)
             ctx.decode_only = True
-            from .. import kernels
             graph = torch.cuda.CUDAGraph()
-            before = kernels.launch_count
             # no garbage collection while capturing: an unreachable engine's graphs, destroyed by the collector
             # in the middle of this capture, would invalidate it
             gc_was_on = gc.isenabled()
@@ -357,8 +303,10 @@ class Engine:
             finally:
                 if gc_was_on:
                     gc.enable()
-            rec = (graph, out, kernels.launch_count - before)
-            self._graphs[bucket] = rec
+            rec = (graph, out, self.runner.launches)
+            self._graphs[key] = rec
+        else:
+            self._pack(entries, starts, B, B, pad_to=bucket)      # the same buffer contents; the views are the capture's
         graph, out, launches = rec
         graph.replay()
         self.kernel_launches += launches

@@ -13,6 +13,7 @@ from typing import Optional
 import torch
 
 from . import build as _build
+from . import host as _host
 
 F32, BF16 = 0, 1
 _CODE = {torch.float32: F32, torch.bfloat16: BF16}
@@ -429,40 +430,6 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
     return out
 
 
-def attention_decode_splits(nrows: int, nkvh: int, group: int, max_positions: int, sms: int = 148,
-                            dh: Optional[int] = None) -> int:
-    """How many ways the decode kernels cut each row's key range.  It depends on the batch's size only
-    (not on the lengths), so a captured step keeps its grid; half the longest context stands for the lengths.
-
-    Head sizes 64 and 128 (the tensor-core kernel: a block per row, key/value head and up to 16 query heads,
-    two blocks an SM), from measurements on the 1B, 2B and 8B shapes: as many cuts as make the blocks fill the
-    SMs once (rounded), as long as a block keeps 256 keys; then further, up to two rounds of blocks, as long as a block
-    keeps 1024 keys (a block's fixed part costs about as much as a few hundred keys, and blocks that all
-    start and end together read slower than blocks that overlap).
-
-    Other head sizes (the kernel of the CUDA cores, three blocks an SM): the choice weighs full waves of
-    blocks against a block's fixed cost of about 128 keys' worth of time."""
-    keys = max(1, max_positions // 2)
-    if dh in (64, 128):
-        blocks = max(1, nrows * nkvh * ((group + 15) // 16))
-        slots = 2 * sms
-        s = max(1, min((2 * slots + blocks) // (2 * blocks), keys // 256, 32))     # slots / blocks, rounded
-        while blocks * (s + 1) <= 2 * slots and keys // (s + 1) >= 1024 and s < 32:
-            s += 1
-        return s
-    blocks = max(1, nrows * nkvh * ((group + 3) // 4 if group > 4 else 1))
-    slots = sms * 3
-    best, best_cost = 1, None
-    for s in range(1, 33):
-        if s > 1 and keys / s < 64:
-            break
-        waves = -(-blocks * s // slots)
-        cost = waves * (128 + keys / s)
-        if best_cost is None or cost < best_cost * 0.97:      # prefer fewer splits unless clearly better
-            best, best_cost = s, cost
-    return best
-
-
 def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                      rows: Optional[torch.Tensor], nrows: int, positions: torch.Tensor, row_req: torch.Tensor,
                      block_table: torch.Tensor, nh: int, scale: float, window: int, splits: int,
@@ -500,7 +467,7 @@ def attention_prefill_supports(dh: int) -> bool:
     return bool(_build.load("attention").jk_attention_prefill_supports(_c_int(dh)))
 
 
-TILE_ROWS = 128      # rows of a query tile in the tile lists that the prefill attention kernels take
+TILE_ROWS = _host.attention_tile_rows()      # rows of a query tile in the tile lists that the prefill attention kernels take
 
 
 def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
@@ -524,10 +491,9 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
 
 
 def attention_tcgen05_supports(dh: int, page_size: int) -> bool:
-    """Head sizes 64 and 128 with pages that divide a tile of 128 keys and fill whole groups of 8 rows (the
-    same rule as the library's ``jk_attention_tcgen05_supports``; answered here so that a model the
-    kernel is not built for never compiles its module)."""
-    return dh in (64, 128) and page_size in (8, 16, 32, 64, 128)
+    """Head sizes 64 and 128 with pages that divide a tile of 128 keys and fill whole groups of 8 rows
+    (``jk::attention_tcgen05_takes`` of csrc/host_rules.h; asking does not compile the kernel's module)."""
+    return _host.attention_tcgen05_takes(dh, page_size)
 
 
 def attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,

@@ -1,6 +1,7 @@
 """Compiling the CUDA sources in ``csrc`` for sm_100a into shared objects, in-tree.
 
-Each module is one shared object built with nvcc from its own sources; a module is built
+Each module is one shared object built with nvcc from its own sources (``host``, the rules that run on the host and
+need no CUDA, with the host compiler alone); a module is built
 the first time something asks for it and again when its sources or flags change (a hash of
 both is kept beside the object).  Nothing here needs a GPU: nvcc cross-compiles.  There is
 no fallback: if a module cannot be built or loaded the caller gets an exception.
@@ -29,10 +30,14 @@ MODULES: Dict[str, List[str]] = {
     "gemm_tcgen05": ["gemm_tcgen05.cu", "gemm_skinny.cu"],
     "attention_tcgen05": ["attention_tcgen05.cu"],
     "runner": ["runner.cu", "capi.cu"],
+    "host": ["host.cpp"],
 }
+# modules without device code: built by the host compiler, loadable on a machine without CUDA
+HOST_ONLY = {"host"}
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared"]
 # libraries a module links against (the others need the CUDA runtime only)
 LINK: Dict[str, List[str]] = {"runner": ["-lcublas"]}
-HEADERS = ["common.cuh", "attention_static_scratch.h", "runner.h", "model_api.h", "tcgen05.cuh"]
+HEADERS = ["common.cuh", "attention_static_scratch.h", "runner.h", "model_api.h", "tcgen05.cuh", "host_rules.h"]
 
 # -use_fast_math is deliberately absent: expf, division and sqrt stay accurate.
 NVCC_FLAGS = [
@@ -56,6 +61,14 @@ def find_nvcc() -> str:
                      "the engine has no CPU or library fallback")
 
 
+def find_host_compiler() -> str:
+    for name in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        found = shutil.which(name) if name else None
+        if found:
+            return found
+    raise BuildError("no C++ compiler found ($CXX, g++, c++, clang++) for the host-side rules")
+
+
 def build_dir() -> str:
     """``csrc/_build`` when the tree is writable, else a per-user folder under the temp dir."""
     d = os.path.join(CSRC, "_build")
@@ -74,7 +87,7 @@ def build_dir() -> str:
 
 def _digest(module: str) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS + LINK.get(module, [])).encode())
+    h.update(" ".join((HOST_FLAGS if module in HOST_ONLY else NVCC_FLAGS) + LINK.get(module, [])).encode())
     for name in MODULES[module] + HEADERS:
         with open(os.path.join(CSRC, name), "rb") as f:
             h.update(name.encode())
@@ -108,12 +121,14 @@ def build(module: str, verbose: bool = True) -> str:
         try:
             if is_current(module):        # another process built it while we waited
                 return so
-            nvcc = find_nvcc()
             tmp = f"{so}.tmp{os.getpid()}"
-            cmd = ([nvcc] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp] + [os.path.join(CSRC, s) for s in MODULES[module]]
-                   + LINK.get(module, []))
+            if module in HOST_ONLY:
+                cmd = [find_host_compiler()] + HOST_FLAGS
+            else:
+                cmd = [find_nvcc()] + NVCC_FLAGS
+            cmd = cmd + ["-I", CSRC, "-o", tmp] + [os.path.join(CSRC, s) for s in MODULES[module]] + LINK.get(module, [])
             if verbose:
-                print(f"[infinicore_infer_b200] compiling kernel module '{module}' for sm_100a ...",
+                print(f"[infinicore_infer_b200] compiling module '{module}' " + ("for the host" if module in HOST_ONLY else "for sm_100a") + " ...",
                       file=sys.stderr, flush=True)
             t0 = time.time()
             proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
@@ -128,7 +143,7 @@ def build(module: str, verbose: bool = True) -> str:
             if proc.returncode != 0:
                 if os.path.exists(tmp):
                     os.remove(tmp)
-                raise BuildError(f"nvcc failed for module {module}:\n{' '.join(cmd)}\n{out}")
+                raise BuildError(f"the compiler failed for module {module}:\n{' '.join(cmd)}\n{out}")
             os.replace(tmp, so)
             with open(so + ".sha256", "w") as f:
                 f.write(_digest(module))

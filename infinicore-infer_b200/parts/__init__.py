@@ -1,6 +1,7 @@
 """Parts of a model: norm, position encoding, mixer, feed-forward, block; and the model built of them."""
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, SHORT_ROWS, TILE_ROWS, PendingProduct,
-                   ResidualStream, Runtime, StepContext, part_class, register)
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, ResidualStream, Runtime, StepContext, part_class,
+                   register)
+from .program import HostIO, Program, ProgramRunner
 from .norm import RMSNorm
 from .rope import RotaryTables
 from .attention import Attention
@@ -8,6 +9,6 @@ from .feed_forward import SwiGLU
 from .block import PreNormBlock
 from .model import Model, cache_needs, model_manifest
 
-__all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "ResidualStream", "PendingProduct", "Runtime",
-           "StepContext", "SHORT_ROWS", "TILE_ROWS", "part_class", "register", "RMSNorm", "RotaryTables", "Attention", "SwiGLU",
+__all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "ResidualStream", "Runtime", "StepContext", "Program",
+           "ProgramRunner", "HostIO", "part_class", "register", "RMSNorm", "RotaryTables", "Attention", "SwiGLU",
            "PreNormBlock", "Model", "cache_needs", "model_manifest"]

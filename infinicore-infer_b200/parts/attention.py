@@ -59,60 +59,44 @@ class Attention:
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o))
 
-    def forward(self, h: torch.Tensor, ctx, view, writes_cache: bool = True) -> torch.Tensor:
-        from .. import kernels
-        s, rt = self.spec, self.runtime
-        T = ctx.ntok
-        q = rt.empty(T, s.num_heads * s.head_dim)
-        table = ctx.block_tables[view.group_index]
-        pos = self.position
-        n, k = self.w_qkv.shape
-        # the product's epilogue can rotate and write q and the cache itself: no float32 copy of the
-        # product, no rotary kernel (the tcgen05 kernel for many rows, the small-row kernel for few)
-        fusable = (rt.dtype == torch.bfloat16 and self.b_qkv is None and writes_cache
-                   and not (pos and pos.interleaved) and not rt.library_products_only)
-        if fusable and rt.takes_tcgen05(T, n, k) and kernels.gemm_tcgen05_qkv_supports(s.head_dim):
-            kernels.gemm_tcgen05_qkv(h, self.w_qkv, q, view.k_pages, view.v_pages, pos.cos if pos else None,
-                                     pos.sin if pos else None, ctx.positions, ctx.row_req, table, s.num_heads)
-        elif fusable and T <= 16 and kernels.linear_small_qkv_supports(T, k, s.head_dim):
-            kernels.linear_small_qkv(h, self.w_qkv, q, view.k_pages, view.v_pages, pos.cos if pos else None,
-                                     pos.sin if pos else None, ctx.positions, ctx.row_req, table, s.num_heads)
-        else:
-            qkv = rt.linear(h, self.w_qkv, out_dtype=torch.float32)
-            kernels.rope_kv(qkv, self.b_qkv, ctx.positions, ctx.row_req, table, view.page_size,
-                            pos.cos if pos else None, pos.sin if pos else None,
-                            pos.interleaved if pos else False, q, view.k_pages, view.v_pages,
-                            T, s.num_heads, s.num_kv_heads, s.head_dim, write_cache=writes_cache)
-        o = rt.empty(T, s.num_heads * s.head_dim)
-        self._attend(q, o, view, table, ctx)
-        return rt.product(o, self.w_o)       # the block adds it to the residual stream
+    # ---- work lists: what this mixer asks every step to carry -----------------------------------------------------
+    # Requests that bring few rows to a step go to the split-key decode kernels row by row, the others to the prefill
+    # kernels in tiles of query rows; the rule and the numbers are jk::attention_work_lists of csrc/host_rules.h.
+    LISTS = ("short_rows", "tiles")
 
-    def _attend(self, q, o, view, table, ctx) -> None:
-        """float32: one warp per (row, head), the same arithmetic whatever the batch.  bfloat16: rows of
-        requests with few rows go to the split-key decode kernel, tiles of the others to a tensor-core
-        kernel (tcgen05 where it is built for the head and page size, else mma.sync); head sizes neither
-        is built for take the row kernel."""
-        from .. import kernels
-        s, T = self.spec, ctx.ntok
-        fast = (self.runtime.dtype == torch.bfloat16 and not self.runtime.plain_attention
-                and (ctx.n_short or ctx.n_tiles) and s.head_dim % 8 == 0 and s.head_dim <= 256)
-        if fast and ctx.n_tiles and not (kernels.attention_prefill_supports(s.head_dim)
-                                         or kernels.attention_tcgen05_supports(s.head_dim, view.page_size)):
-            fast = False
-        if not fast:
-            kernels.attention_rows(q, view.k_pages, view.v_pages, o, ctx.positions, ctx.row_req, table, T,
-                                   s.num_heads, s.softmax_scale, s.window or 0)
-            return
-        if ctx.n_tiles:
-            if not self.runtime.legacy_tensor_cores and kernels.attention_tcgen05_supports(s.head_dim, view.page_size):
-                kernels.attention_tcgen05(q, view.k_pages, view.v_pages, o, ctx.tiles, ctx.n_tiles, T, ctx.req_start,
-                                          ctx.req_pos, table, s.num_heads, s.softmax_scale, s.window or 0)
-            else:
-                kernels.attention_prefill(q, view.k_pages, view.v_pages, o, ctx.tiles, ctx.n_tiles, ctx.req_start,
-                                          ctx.req_pos, table, s.num_heads, s.softmax_scale, s.window or 0)
-        if ctx.n_short:
-            splits = kernels.attention_decode_splits(ctx.n_short, s.num_kv_heads, s.num_heads // s.num_kv_heads,
-                                                     s.window or (s.position.max_positions if s.position else 1 << 20),
-                                                     kernels._sm_count(q.device), s.head_dim)
-            kernels.attention_decode(q, view.k_pages, view.v_pages, o, ctx.short_rows, ctx.n_short, ctx.positions,
-                                     ctx.row_req, table, s.num_heads, s.softmax_scale, s.window or 0, splits)
+    @staticmethod
+    def step_list_capacity(T: int, B: int) -> Dict[str, int]:
+        from ..kernels import host
+        short, tiles = host.attention_list_capacity(T, B)
+        return {"short_rows": short, "tiles": tiles}
+
+    @staticmethod
+    def fill_step_lists(B: int, pad_B: int, lens, starts, arrays) -> Dict[str, tuple]:
+        """Fill ``arrays[name]`` (int32 numpy views of the step's metadata buffer); returns name -> (entries, whether
+        the list is simply the rows 0..entries-1, which the kernels take without a list)."""
+        from ..kernels import host
+        n_short, n_tiles = host.attention_work_lists(B, pad_B, lens, starts, arrays["short_rows"], arrays["tiles"])
+        rows = sum(lens) + (pad_B - B)
+        return {"short_rows": (n_short, n_short == rows), "tiles": (n_tiles, False)}
+
+    def plan(self, program, view, writes_cache: bool = True, residual_scale: float = 1.0) -> None:
+        """Three records: the fused q | k | v product with rotation and cache write (h -> q), the attention over the
+        cache (q -> o), the output product added into the stream times ``residual_scale``."""
+        import ctypes
+        s, pos = self.spec, self.position
+        i, f, p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+        short, tiles = program.work_lists(Attention, self.LISTS)
+        ptr = lambda t: p(t.data_ptr() if t is not None else 0)
+        max_positions = getattr(pos, "max_positions", None) or (pos.cos.shape[0] if pos is not None else 1 << 20)
+        program.emit("jk_emit_attention", ptr(self.w_qkv), ptr(self.b_qkv), ptr(self.w_o), i(s.hidden_size), i(s.num_heads),
+                     i(s.num_kv_heads), i(s.head_dim), i(s.window or 0), f(s.softmax_scale), f(residual_scale),
+                     ptr(pos.cos if pos is not None else None), ptr(pos.sin if pos is not None else None),
+                     i(1 if (pos is not None and pos.interleaved) else 0), i(max_positions), ptr(view.k_pages), ptr(view.v_pages),
+                     i(view.k_pages.shape[0]), i(view.group_index), i(1 if writes_cache else 0), i(short), i(tiles),
+                     keep=(self.w_qkv, self.b_qkv, self.w_o, pos, view.k_pages, view.v_pages))
+
+    def forward(self, h: torch.Tensor, ctx, view, writes_cache: bool = True) -> torch.Tensor:
+        """The part alone: its own records over ``h``; float32 ``[T, hidden]`` (the output product, not yet scaled)."""
+        from .program import run_part_alone
+        return run_part_alone(self.runtime, lambda program: self.plan(program, view, writes_cache, 1.0), ctx, h,
+                              self.spec.hidden_size, page_size=view.page_size)

@@ -46,12 +46,47 @@ class PreNormBlock:
         parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
         return sum(p.weight_bytes() for p in parts if hasattr(p, "weight_bytes"))
 
+    def plan(self, program, view, writes_cache: bool = True) -> None:
+        """The block as records, part by part.  A part that has ``plan`` emits its own; one that has not (a part of
+        another kind, defined elsewhere) runs by its ``forward`` as a host step between the records."""
+        s = self.spec.residual_scale
+        hidden = program.hidden_size
+        for norm, part, is_mixer in ((self.mixer_norm, self.mixer, True), (self.ffn_norm, self.feed_forward, False)):
+            if hasattr(norm, "plan"):
+                norm.plan(program)
+            else:
+                program.host(_host_norm(norm, hidden))
+            if hasattr(part, "plan"):
+                part.plan(program, view, writes_cache, s) if is_mixer else part.plan(program, s)
+            else:
+                program.host(_host_branch(part, view, writes_cache, s, hidden, is_mixer))
+
     def forward(self, residual: ResidualStream, ctx, view, writes_cache: bool = True) -> None:
+        """The block by its parts' own ``forward``: what a model that arranges blocks by hand calls."""
         s = self.spec.residual_scale
         h = self.mixer_norm.forward(residual, ctx)
         residual.add(self.mixer.forward(h, ctx, view, writes_cache), s)
         h = self.ffn_norm.forward(residual, ctx)
         residual.add(self.feed_forward.forward(h, ctx), s)
+
+
+def _host_norm(norm, hidden: int):
+    def run_norm(ctx, io):
+        out = norm.forward(ResidualStream(io.view("x", hidden)), ctx)
+        io.view("h", hidden).copy_(out)
+    run_norm.__qualname__ = type(norm).__name__ + ".forward"
+    return run_norm
+
+
+def _host_branch(part, view, writes_cache: bool, scale: float, hidden: int, is_mixer: bool):
+    def run_branch(ctx, io):
+        h = io.view("h", hidden)
+        delta = part.forward(h, ctx, view, writes_cache) if is_mixer else part.forward(h, ctx)
+        stream = ResidualStream(io.view("x", hidden))
+        stream.add(delta, scale)
+        stream.value()
+    run_branch.__qualname__ = type(part).__name__ + ".forward"
+    return run_branch
 
 
 def _children(spec):

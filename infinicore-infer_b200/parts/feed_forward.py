@@ -36,7 +36,15 @@ class SwiGLU:
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
+    def plan(self, program, residual_scale: float = 1.0) -> None:
+        """Two records: gate | up with the activation (h -> act), down added into the stream times ``residual_scale``."""
+        import ctypes
+        s = self.spec
+        program.emit("jk_emit_swiglu", ctypes.c_void_p(self.w_gate_up.data_ptr()), ctypes.c_void_p(self.w_down.data_ptr()),
+                     ctypes.c_int(s.hidden_size), ctypes.c_int(s.intermediate_size), ctypes.c_float(residual_scale),
+                     keep=(self.w_gate_up, self.w_down))
+
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
-        rt = self.runtime
-        act = rt.gate_up_swiglu(h, self.w_gate_up)
-        return rt.product(act, self.w_down)      # the block adds it to the residual stream
+        """The part alone: its own records over ``h``; float32 ``[T, hidden]``."""
+        from .program import run_part_alone
+        return run_part_alone(self.runtime, lambda program: self.plan(program, 1.0), ctx, h, self.spec.hidden_size)

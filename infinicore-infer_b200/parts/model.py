@@ -13,6 +13,7 @@ import torch
 
 from ..weights import MATRIX, TensorDecl
 from .base import ResidualStream, Runtime, StepContext, part_class
+from .program import Program
 
 
 def model_manifest(spec) -> Dict[str, TensorDecl]:
@@ -70,14 +71,43 @@ class Model:
             total += getattr(self.layers[e.layer], "weight_bytes", lambda: 0)()
         return total
 
-    def forward(self, ctx: StepContext, views) -> torch.Tensor:
+    def plan(self, views, page_size: int, max_blocks: int) -> Program:
+        """The whole model as a program: the embedding, the layers in their run order, the final norm over the wanted
+        rows with the logit scale riding on it (as in the reference, scripts/jiuge.py:198-201), the output product."""
+        import ctypes
         from .. import kernels
-        spec, rt = self.spec, self.runtime
-        x = rt.empty(ctx.ntok, spec.hidden_size, dtype=torch.float32)
-        kernels.embed(ctx.tokens, self.embedding, spec.embed_scale, x)
-        residual = ResidualStream(x)
+        spec = self.spec
+        program = Program(self.runtime, spec.hidden_size, page_size, max_blocks, capacity=8 * len(spec.order) + 8)
+        program.emit("jk_emit_embedding", ctypes.c_void_p(self.embedding.data_ptr()), ctypes.c_int(kernels.dtype_code(self.embedding.dtype)),
+                     ctypes.c_int(spec.hidden_size), ctypes.c_float(spec.embed_scale), keep=(self.embedding,))
+        hidden = spec.hidden_size
         for e in spec.order:
-            self.layers[e.layer].forward(residual, ctx, views[e.cache], e.writes_cache)
-        # the logit scale rides on the final norm, as in the reference (scripts/jiuge.py:198-201)
-        h = self.final_norm.forward(residual, ctx, out_scale=spec.logit_scale, rows=ctx.want_rows)
-        return rt.linear(h, self.lm_head, out_dtype=torch.float32)
+            layer, view = self.layers[e.layer], views[e.cache]
+            if hasattr(layer, "plan"):
+                layer.plan(program, view, e.writes_cache)
+            else:
+                program.host(_host_block(layer, view, e.writes_cache, hidden))
+        if hasattr(self.final_norm, "plan"):
+            self.final_norm.plan(program, out_scale=spec.logit_scale, wanted_rows=True)
+        else:
+            program.host(_host_final_norm(self.final_norm, spec.logit_scale, hidden))
+        program.emit("jk_emit_output", ctypes.c_void_p(self.lm_head.data_ptr()), ctypes.c_int(spec.vocab_size),
+                     ctypes.c_int(spec.hidden_size), keep=(self.lm_head,))
+        return program
+
+
+def _host_block(layer, view, writes_cache: bool, hidden: int):
+    def run_block(ctx, io):
+        stream = ResidualStream(io.view("x", hidden))
+        layer.forward(stream, ctx, view, writes_cache)
+        stream.value()
+    run_block.__qualname__ = type(layer).__name__ + ".forward"
+    return run_block
+
+
+def _host_final_norm(norm, logit_scale: float, hidden: int):
+    def run_final_norm(ctx, io):
+        out = norm.forward(ResidualStream(io.view("x", hidden)), ctx, out_scale=logit_scale, rows=ctx.want_rows)
+        io.view("hw", hidden, rows=out.shape[0]).copy_(out)
+    run_final_norm.__qualname__ = type(norm).__name__ + ".forward"
+    return run_final_norm

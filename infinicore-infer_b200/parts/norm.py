@@ -26,6 +26,14 @@ class RMSNorm:
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
+    def plan(self, program, out_scale: float = 1.0, wanted_rows: bool = False) -> None:
+        """One record: add what waits for the stream, normalise every row (or the wanted rows) into the next product's
+        activations."""
+        import ctypes
+        program.emit("jk_emit_rmsnorm", ctypes.c_void_p(self.weight.data_ptr()), ctypes.c_int(self.spec.size),
+                     ctypes.c_float(self.spec.eps), ctypes.c_float(out_scale), ctypes.c_int(1 if wanted_rows else 0),
+                     keep=(self.weight,))
+
     def forward(self, residual: ResidualStream, ctx, out_scale: float = 1.0,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Normalise every row, or only ``rows`` (int32 indices) of the residual stream."""

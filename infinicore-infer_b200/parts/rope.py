@@ -20,12 +20,10 @@ class RotaryTables:
         return {}
 
     def __init__(self, spec, weights, prefix: str, runtime):
+        from ..kernels.host import rotary_tables
         self.spec = spec
-        half = spec.head_dim // 2
-        j = torch.arange(half, dtype=torch.float64)
-        inv_freq = torch.tensor(float(spec.theta), dtype=torch.float64) ** (-(j / half))
-        pos = torch.arange(spec.max_positions, dtype=torch.float64)
-        angle = pos[:, None] * inv_freq[None, :]
-        self.cos = angle.cos().to(torch.float32).to(runtime.device).contiguous()
-        self.sin = angle.sin().to(torch.float32).to(runtime.device).contiguous()
+        cos, sin = rotary_tables(float(spec.theta), spec.head_dim // 2, spec.max_positions)
+        self.cos = torch.from_numpy(cos).to(runtime.device).contiguous()
+        self.sin = torch.from_numpy(sin).to(runtime.device).contiguous()
         self.interleaved = bool(spec.interleaved)
+        self.max_positions = spec.max_positions

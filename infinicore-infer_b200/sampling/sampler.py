@@ -15,18 +15,7 @@ from typing import List, Sequence
 
 import torch
 
-_MASK = (1 << 64) - 1
-
-
-def uniform_for(seed: int, index: int) -> float:
-    """A float in [0, 1) from (seed, index): the splitmix64 finaliser, top 24 bits."""
-    z = (int(seed) * 0x9E3779B97F4A7C15 + (int(index) + 1) * 0xBF58476D1CE4E5B9) & _MASK
-    z ^= z >> 30
-    z = (z * 0xBF58476D1CE4E5B9) & _MASK
-    z ^= z >> 27
-    z = (z * 0x94D049BB133111EB) & _MASK
-    z ^= z >> 31
-    return (z >> 40) / float(1 << 24)
+from ..kernels.host import uniform_for      # noqa: F401  (seed, absolute position) -> [0, 1): one rule, written in csrc/host_rules.h
 
 
 @dataclass

@@ -458,9 +458,7 @@ def test_attention_prefill_kernel_on_tensor_cores(K, nh, nkvh, dh, page, window)
                                                      (6, 2, 64, 32, 100), (2, 1, 128, 64, 33), (4, 2, 64, 128, None),
                                                      (36, 36, 64, 16, None)])
 def test_attention_prefill_kernel_on_tcgen05(K, nh, nkvh, dh, page, window):
-    from infinicore_infer_b200.parts import TILE_ROWS
     assert K.attention_tcgen05_supports(dh, page) and not K.attention_tcgen05_supports(48, 16)
-    assert TILE_ROWS == K.TILE_ROWS
     lens = [150, 460, 128, 40]
     queries = [list(range(0, 150)), list(range(203, 460)), list(range(0, 128)), list(range(31, 40))]
     got, want, _ = _attention_case(K, torch.bfloat16, nh, nkvh, dh, page, window, lens, queries, seed=dh + page, impl="tcgen05")

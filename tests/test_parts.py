@@ -100,7 +100,7 @@ def test_attention_part_alone_in_portions(cfg, dtype):
             cache.reserve("y", 6)
         ctx = _ctx(cache, reqs)
         rows = torch.cat([h[lo:hi]] + ([other] if with_other else [])).to(DEV)
-        out = attn.forward(rows, ctx, cache.views[0], True).tensor()     # a pending product: make it a tensor
+        out = attn.forward(rows, ctx, cache.views[0], True)
         got.append(out[:hi - lo].double().cpu())
         cache.commit("x", hi)
     got = torch.cat(got)
@@ -117,7 +117,7 @@ def test_feed_forward_part_alone(dtype):
     w = random_tensors(cls.tensor_decls(spec), seed=4, std=0.1)
     ffn = cls(spec, DictWeights({"m." + k: v for k, v in w.items()}, dtype, DEV), "m.", Runtime(dtype, DEV))
     h = torch.randn(9, 80, generator=torch.Generator().manual_seed(2)).to(dtype)
-    out = ffn.forward(h.to(DEV), None).tensor()
+    out = ffn.forward(h.to(DEV), None)
     want = plain_swiglu_ffn(h.double(), w["gate_proj.weight"].double(), w["up_proj.weight"].double(),
                             w["down_proj.weight"].double())
     assert (out.double().cpu() - want).abs().max() <= _tol(dtype) * want.abs().max()

@@ -1,5 +1,7 @@
-"""The native runner (csrc/runner.cu) issues the same kernels as the parts do: the two ways of running a
-step must give the same logits, and the runner must leave alone what it is not built for."""
+"""The native step (csrc/runner.cu) replays a model's launch records.  A whole run of records in one call may let
+neighbouring records share work (steps of few rows run without norm kernels); every record as a call of its own is the
+unfused way of running the same program.  The two must give the same logits, and models with parts that emit no
+records must run too, with those parts as host steps."""
 import numpy as np
 import pytest
 import torch
@@ -14,9 +16,9 @@ pytestmark = pytest.mark.gpu
 def test_native_runner_and_parts_give_the_same_logits(tiny_models, name):
     folder = tiny_models[name][0]
     native = make_engine(folder, "bfloat16", 1024)
-    native.runtime.fused_norms = False       # the same kernels as the parts: the runner's own way for few rows is tested below
+    native.runtime.fused_norms = False       # the same kernels both ways: what neighbouring records share is tested below
     parts = make_engine(folder, "bfloat16", 1024, native_runner=False)
-    assert native.runner is not None and parts.runner is None
+    assert not native.runner.one_by_one and parts.runner.one_by_one and native.program.native_only
     toks, want = expected(tiny_models, name, 500, 200)
     toks2, want2 = expected(tiny_models, name, 501, 90)
     reqs = {"a": toks, "b": toks2}
@@ -32,11 +34,12 @@ def test_native_runner_and_parts_give_the_same_logits(tiny_models, name):
             # choice of kernel may differ
             assert np.abs(got_n[key] - got_p[key]).max() <= 2e-3 * scale, (name, what, key)
         check(got_n, "a", want, TOL["bfloat16"], f"{name} native {what}")
-    # decoded tokens only (no library product anywhere): bit for bit
+    # decoded tokens only: the same product kernels; a product that waits for the next norm is added by the norm's
+    # kernel in one way of running and by a kernel of its own in the other, the same float32 sum from two kernels
     steps = tail_decode("a", toks[:40], tail=40)
     got_n, got_p = run(native, steps), run(parts, steps)
     for key in got_n:
-        assert np.array_equal(got_n[key], got_p[key]), (name, "decode", key)
+        assert np.abs(got_n[key] - got_p[key]).max() <= 2e-3 * np.abs(want).max(), (name, "decode", key)
     native.check()
 
 
@@ -50,7 +53,7 @@ def test_steps_of_few_rows_run_without_norm_kernels(tiny_models, name):
     fused = make_engine(folder, "bfloat16", 1024)
     kept = make_engine(folder, "bfloat16", 1024)
     kept.runtime.fused_norms = False         # before its first step: decode steps are captured once
-    assert fused.runtime.fused_norms and fused.runner is not None
+    assert fused.runtime.fused_norms and fused.program.native_only
     toks, want = expected(tiny_models, name, 500, 200)
     toks2, want2 = expected(tiny_models, name, 501, 90)
     plan = [{"a": 150}, {"a": 1, "b": 60}, {"a": 2, "b": 1}, {"a": 1, "b": 1}, {"a": 46, "b": 28}]
@@ -84,7 +87,7 @@ def test_runner_and_parts_route_few_rows_alike(tiny_models, name):
     native = make_engine(folder, "bfloat16", 1024)
     parts = make_engine(folder, "bfloat16", 1024, native_runner=False)
     native.runtime.skinny_min_blocks = parts.runtime.skinny_min_blocks = 1
-    native.runtime.fused_norms = False       # the parts keep their norm kernels; this test is about the products
+    native.runtime.fused_norms = False       # this test is about the products
     toks, want = expected(tiny_models, name, 510, 180)
     for what, steps in (("portions", portions("a", toks, sizes=(100, 17, 30, 5, 28))), ("tail", tail_decode("a", toks))):
         got_n, got_p = run(native, steps), run(parts, steps)
@@ -95,12 +98,15 @@ def test_runner_and_parts_route_few_rows_alike(tiny_models, name):
         check(got_n, "a", want, TOL["bfloat16"], f"{name} few rows {what}")
         check(got_p, "a", want, TOL["bfloat16"], f"{name} few rows {what} (parts)")
     native.check()
-    assert native.runner is not None and native.runner._model.skinny_min_blocks == 1
+    assert native.runner.env.routing.skinny_min_blocks == 1
 
 
-def test_native_runner_leaves_other_models_to_the_parts(tiny_models):
-    from infinicore_infer_b200.engine.runner import NativeRunner
-    eng = make_engine(tiny_models["C"][0], "bfloat16", 256)          # hidden 80: outside the small-row kernels
-    assert eng.runner is None and "small-row" in NativeRunner.why_not
+def test_every_model_has_a_program_of_records(tiny_models):
+    """Sizes outside the fast kernels (hidden 80, heads of 48) and float32 run from records too: the native step picks
+    other kernels for them, it does not hand the model back."""
+    eng = make_engine(tiny_models["C"][0], "bfloat16", 256)
+    assert eng.program.native_only
+    layers = tiny_models["C"][1]["num_hidden_layers"]
+    assert eng.program.launch_list() == ["embed"] + ["norm", "qkv", "attention", "residual", "norm", "gate_up", "residual"] * layers + ["norm", "linear"]
     eng = make_engine(tiny_models["A"][0], "float32", 256)
-    assert eng.runner is None and "bfloat16" in NativeRunner.why_not
+    assert eng.program.native_only and len(eng.program.launch_list()) == 7 * 2 + 3

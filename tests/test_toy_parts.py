@@ -200,6 +200,11 @@ def test_toy_parts_are_registered_built_and_stepped(dtype):
     eng = Engine(spec, DictWeights(w, dtype, DEV), dtype=dtype, device=DEV, cache_tokens=256, page_size=8,
                  max_requests=4, max_step_tokens=256)
     assert eng.cache.views[0].state.shape == (5, 64)
+    # the toy parts run by their own forward between the records; the standard parts around them (the norms, layer 1's
+    # attention with the toy position encoding's tables, its SwiGLU) are launch records of the native step
+    assert eng.program.launch_list() == [
+        "embed", "norm", "host:RunningMean.forward", "norm", "host:Top1Experts.forward",
+        "norm", "qkv", "attention", "residual", "norm", "gate_up", "residual", "norm", "linear"]
     tol = 3e-5 if dtype == torch.float32 else 2.5e-2
     reqs = {r: random_tokens(30 + i, n, cfg["vocab_size"]) for i, (r, n) in enumerate({"a": 40, "b": 23, "c": 31}.items())}
     wants = {r: _plain_toy(cfg, w, t) for r, t in reqs.items()}
