@@ -13,7 +13,13 @@ One JSON line is printed:
               its token ids and block tables from pinned host memory and reads the sampled ids back;
   prefill     one 2,048-token prompt through the step function;
   roofline    bytes a decode step must read (every weight once + the live requests' cache) / time;
-  points      decode tokens per second at batch 1 and 64 (context 4096) and at context 512.
+  points      decode tokens per second at batch 1 and 64 (context 4096) and at context 512;
+  plain       the same engine run one call per operator with library products, the plain attention kernel, separate norm
+              kernels and no CUDA graphs: the shape of the reference's step (src/models/jiuge/jiuge.cpp:195-258), which
+              cannot itself be built here; ``vs_baseline`` is ``value`` over this path's batch-8 decode rate;
+  kernels     device time of each dominant kernel alone at the benchmark's shape (one launch record of the model at a time,
+              walking through the layers so that weights and cache come from memory, not from L2) with its achieved
+              GB/s or TFLOP/s over the measured peak.
 Peaks come from MEASURED_PEAKS.json beside this file if present, else from the fallback values.
 """
 import argparse
@@ -47,7 +53,7 @@ WORKLOADS = {
     "1b-mixed": (SHAPE_1B, 32, (16, 1024), 128, 256, 512),
     "8b-serving": (SHAPE_8B, 64, (512, 2048), 256, 512, 2048),
 }
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
 def load_peaks():
@@ -65,7 +71,8 @@ def load_peaks():
                         flat.setdefault(k, float(v))
             walk(data)
             if "hbm_gbs" in flat and "bf16_tflops" in flat:
-                return {"hbm_gbs": flat["hbm_gbs"], "bf16_tflops": flat["bf16_tflops"]}, "measured"
+                return {"hbm_gbs": flat["hbm_gbs"], "bf16_tflops": flat["bf16_tflops"],
+                        "bf16_tflops_sustained": flat.get("bf16_tflops_sustained", flat["bf16_tflops"])}, "measured"
         except (OSError, ValueError):
             pass
     return dict(FALLBACK_PEAKS), "fallback"
@@ -176,6 +183,51 @@ def run_workload(name, layers=None):
     return 0
 
 
+
+def time_records(engine, ctx, which, repeats=3):
+    """Device time (microseconds per launch) of one kind of launch record, run alone: ``which(l)`` gives the index of
+    layer l's record (or None to skip the layer).  The records of all layers run one after the other, so each launch
+    reads its own layer's weights and cache pages from memory; the best of ``repeats`` walks counts."""
+    import ctypes
+    import torch
+    from infinicore_infer_b200 import kernels
+    from infinicore_infer_b200.parts.program import SLOT, RunnerStep
+    runner, prog = engine.runner, engine.program
+    T = ctx.ntok
+    logits = torch.empty(max(1, ctx.want_rows.numel()), engine.spec.vocab_size, dtype=torch.float32, device=engine.device)
+    runner.buffers.slot[SLOT["logits"]] = logits.data_ptr()
+    runner.buffers.bytes[SLOT["logits"]] = logits.numel() * 4
+    step = RunnerStep(ntok=T, nreq=ctx.nreq, n_want=ctx.want_rows.numel(), context=ctx.context, tokens=ctx.tokens.data_ptr(),
+                      positions=ctx.positions.data_ptr(), row_req=ctx.row_req.data_ptr(), req_start=ctx.req_start.data_ptr(),
+                      req_pos=ctx.req_pos.data_ptr(), want_rows=ctx.want_rows.data_ptr())
+    for g, table in enumerate(ctx.block_tables):
+        step.block_tables[g] = table.data_ptr()
+    for name, index in prog.lists.items():
+        view, n = ctx.lists[name]
+        step.lists[index] = view.data_ptr() if view is not None else None
+        step.list_n[index] = n
+    indices = [i for i in (which(l) for l in range(len(engine.spec.order))) if i is not None]
+    stream = kernels._stream()
+
+    def walk():
+        for i in indices:
+            rc = runner.lib.jk_runner_run(ctypes.byref(runner.env), prog.ops, i, 1, ctypes.byref(step), ctypes.byref(runner.buffers), 1, stream)
+            if rc:
+                raise RuntimeError(runner.lib.jk_runner_last_error().decode())
+    walk()
+    torch.cuda.synchronize()
+    best = None
+    for _ in range(repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        walk()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1000.0 / len(indices)
+        best = us if best is None else min(best, us)
+    return best
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -187,6 +239,9 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the shape has (both numbers are reported)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and context 512 points")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-context-buckets", action="store_true", help="plan every decode step for the model's longest context")
+    ap.add_argument("--no-plain", action="store_true", help="skip the plain (one call per operator) baseline")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel timings")
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
                     help="run a few steps between cudaProfilerStart/Stop (for ncu --profile-from-start off) and exit")
     ap.add_argument("--shape", default="2b", choices=["2b", "1b", "8b"],
@@ -235,7 +290,7 @@ def main():
     weights = DeviceRandomWeights(model_manifest(spec), seed=0, compute_dtype=torch.bfloat16, device=dev, std=0.02,
                                   untied=not shape["tie_word_embeddings"])
     engine = Engine(spec, weights, dtype=torch.bfloat16, device=dev, cache_tokens=cache_tokens, page_size=page,
-                    max_requests=max_b, max_step_tokens=4096)
+                    max_requests=max_b, max_step_tokens=4096, context_buckets=not args.no_context_buckets)
     engine.config = cfg
     for view in engine.cache.views:          # synthetic cache contents
         view.k_pages.normal_(0, 0.5)
@@ -373,6 +428,7 @@ def main():
         flops = T * per_tok + L * 2 * T * T * dh * nh + 2 * d * V
         prefill = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
                    "frac": round(flops / (pms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+                   "frac_of_sustained": round(flops / (pms * 1e-3) / (peaks["bf16_tflops_sustained"] * 1e12), 4),
                    "tflops": round(flops / (pms * 1e-3) / 1e12, 1), "peak_source": peak_source}
 
     if not args.no_points:
@@ -382,17 +438,95 @@ def main():
             pm, _, _ = decode_device(b, c, psteps, pwarm)
             result_points[name] = round(b * 1000.0 / pm, 1)
 
+    # ---- each dominant kernel alone ---------------------------------------------------------------------------
+    kernel_block = None
+    if not args.no_kernels:
+        L, d, nh, nkv, dh, di = (cfg.num_hidden_layers, cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads,
+                                 cfg.head_dim, cfg.intermediate_size)
+        nq = (nh + 2 * nkv) * dh
+        rec = lambda k: (lambda l: 1 + 7 * l + k)             # a layer's records: norm, qkv, attention, o, norm, gate/up, down
+        last = 1 + 7 * L + 1                                   # the output product
+        kernel_block = {"peak_hbm_gbs": peaks["hbm_gbs"], "peak_bf16_tflops": peaks["bf16_tflops"], "peak_source": peak_source}
+
+        def mem(name, us, nbytes):
+            gbs = nbytes / (us * 1e-6) / 1e9
+            kernel_block.update({f"{name}_us": round(us, 2), f"{name}_gbs": round(gbs, 1), f"{name}_frac": round(gbs / peaks["hbm_gbs"], 3)})
+
+        def flop(name, us, flops):
+            tf = flops / (us * 1e-6) / 1e12
+            kernel_block.update({f"{name}_us": round(us, 2), f"{name}_tflops": round(tf, 1), f"{name}_frac": round(tf / peaks["bf16_tflops"], 3)})
+
+        ids = fill(args.batch, args.context - 2, "k")
+        entries = [StepEntry(r, [1], [0]) for r in ids]
+        for r in ids:
+            engine.cache.reserve(r, args.context - 1)
+        dctx = engine._upload(entries, [args.context - 2] * args.batch, args.batch, args.batch)
+        mem("decode_qkv", time_records(engine, dctx, rec(1)), nq * d * 2)
+        mem("decode_attention", time_records(engine, dctx, rec(2)), args.batch * (args.context - 1) * kv_bytes_per_token / L)
+        mem("decode_o", time_records(engine, dctx, rec(3)), d * nh * dh * 2)
+        mem("decode_gate_up", time_records(engine, dctx, rec(5)), 2 * di * d * 2)
+        mem("decode_down", time_records(engine, dctx, rec(6)), d * di * 2)
+        mem("decode_lm_head", time_records(engine, dctx, lambda l: last if l < 3 else None), V * d * 2)
+        layer_bytes = (nq * d + d * nh * dh + 3 * di * d) * 2
+        layer_us = sum(kernel_block[f"decode_{k}_us"] for k in ("qkv", "o", "gate_up", "down"))
+        kernel_block["decode_layer_products_us"] = round(layer_us, 2)
+        kernel_block["decode_layer_products_frac"] = round(layer_bytes / (layer_us * 1e-6) / 1e9 / peaks["hbm_gbs"], 3)
+        drop(ids)
+        T = 2048
+        ptoks = torch.randint(0, V, (T,), generator=gen).tolist()
+        engine.begin("kp")
+        engine.cache.reserve("kp", T)
+        pctx = engine._upload([StepEntry("kp", ptoks, [T - 1])], [0], 1, T)
+        flop("prefill_qkv", time_records(engine, pctx, rec(1)), 2.0 * T * nq * d)
+        flop("prefill_attention", time_records(engine, pctx, rec(2)), 2.0 * T * T * dh * nh)
+        flop("prefill_o", time_records(engine, pctx, rec(3)), 2.0 * T * d * nh * dh)
+        flop("prefill_gate_up", time_records(engine, pctx, rec(5)), 2.0 * T * 2 * di * d)
+        flop("prefill_down", time_records(engine, pctx, rec(6)), 2.0 * T * d * di)
+        engine.end("kp")
+
+    # ---- the plain path: one call per operator, library products, plain attention, norm kernels, no graphs ------
+    plain = None
+    vs_baseline = None
+    if not args.no_plain:
+        rt = engine.runtime
+        saved = (rt.library_products_only, rt.plain_attention, rt.fused_norms, engine.runner.one_by_one, engine.use_graphs)
+        rt.library_products_only, rt.plain_attention, rt.fused_norms = True, True, False
+        engine.runner.one_by_one, engine.use_graphs = True, False
+        plain = {"what": "one call per operator, library products, row attention kernel, norm kernels, no CUDA graphs"}
+        for b in (1, 8, 64) if not args.no_points else (args.batch,):
+            pm, _, _ = decode_device(b, args.context, 6, 3)
+            plain[f"decode_b{b}"] = round(b * 1000.0 / pm, 1)
+        if not args.no_prefill:
+            T = 2048
+            ptoks = torch.randint(0, V, (T,), generator=gen).tolist()
+            times = []
+            for i in range(3):
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                engine.step([StepEntry(f"pp{i}", ptoks, [T - 1])])
+                e1.record()
+                torch.cuda.synchronize()
+                engine.end(f"pp{i}")
+                if i >= 1:
+                    times.append(e0.elapsed_time(e1))
+            plain["prefill_ms"] = round(min(times), 3)
+            plain["prefill_tok_s"] = round(T * 1000.0 / min(times), 1)
+        (rt.library_products_only, rt.plain_attention, rt.fused_norms, engine.runner.one_by_one, engine.use_graphs) = saved
+        base = plain.get(f"decode_b{args.batch}")
+        vs_baseline = round(value / base, 3) if base else None
+
     meta_bytes = 4 * (7 * args.batch + 8 + args.batch * engine.cache.max_blocks * len(engine.cache.groups))
     line = {
         "metric": f"decode tok/s @ batch {args.batch} ({shape_name}, context {args.context})",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": vs_baseline,
         "dtype": "bf16", "data": "synthetic: random-init weights N(0,0.02), uniform random token ids, random cache contents",
         "config": {
             "model": shape_name, "layers": cfg.num_hidden_layers, "layers_of_shape": full_layers,
             "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
             "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-            "tied_embeddings": True, "global_batch": args.batch, "seq_len": args.context,
+            "tied_embeddings": bool(cfg.tie_word_embeddings), "global_batch": args.batch, "seq_len": args.context,
             "context_len": args.context, "page_size": page, "parallelism": "single GPU",
             "l2": "inputs larger than L2: 5.4 GB of weights and the cache are re-read every step",
             "weights_gb": round(weight_bytes / 1e9, 3), "kv_bytes_per_token": kv_bytes_per_token,
@@ -410,6 +544,11 @@ def main():
         line["prefill"] = prefill
     if result_points:
         line["points"] = result_points
+    if plain is not None:
+        line["plain"] = plain
+        line["baseline"] = "the engine's own plain path (the reference cannot be built here and publishes no number)"
+    if kernel_block is not None:
+        line["kernels"] = kernel_block
     print(json.dumps(line))
     return 0
 

@@ -269,7 +269,6 @@ int run_attention(Run &r, const RunnerOp &op) {
         RUN(attention, g_fns.attention_decode(q, op.k_pages, op.v_pages, o, (float *)scratch, short_rows, n_short, r.st.positions,
                                               r.st.row_req, table, r.env.max_blocks, page, nh, nkvh, dh, op.softmax_scale, op.window,
                                               splits, r.stream));
-        if (splits > 1) ++g_launches;        // the merge (a kernel of its own, or the cluster's last phase)
     }
     return JK_OK;
 }

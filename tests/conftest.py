@@ -47,12 +47,18 @@ TINY_D = dict(
     model_type="minicpm", num_hidden_layers=2, hidden_size=128, num_attention_heads=2, num_key_value_heads=1,
     intermediate_size=192, vocab_size=333, max_position_embeddings=448, rms_norm_eps=1e-5,
     rope_theta=20000.0, scale_emb=5.0, scale_depth=1.7, dim_model_base=32, tie_word_embeddings=True)
+# A fifth with biases on the query, key and value projections (the reference's optional ``attn_qkv_b``, scripts/jiuge.py:252-282)
+# and heads of 64 grouped 2:1.
+TINY_E = dict(
+    model_type="fm9g", num_hidden_layers=2, hidden_size=128, num_attention_heads=2, num_key_value_heads=1,
+    intermediate_size=160, vocab_size=270, max_position_embeddings=384, rms_norm_eps=2e-5, rope_theta=30000.0,
+    scale_emb=6.0, scale_depth=1.5, dim_model_base=64, tie_word_embeddings=False, attention_bias=True)
 # Matrices are N(0, std) with std near 1/sqrt(hidden): every product keeps its input's variance, so
 # attention scores spread over several units (a sharp softmax) and a wrong key, page or position
 # moves the logits far beyond any tolerance.  (With N(0, 0.02) scores are all near zero, every
 # softmax is flat, and dropping one key among hundreds would hide inside the rounding.)
 TINY = {"A": (TINY_A, 0, 0.125, 0.01), "B": (TINY_B, 1, 0.1, 0.02), "C": (TINY_C, 2, 0.11, 0.03),
-        "D": (TINY_D, 3, 0.09, 0.02)}
+        "D": (TINY_D, 3, 0.09, 0.02), "E": (TINY_E, 4, 0.09, 0.02)}
 
 
 def make_folder(tmp_path_factory, name):

@@ -21,7 +21,7 @@ DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 # bfloat16: activations are rounded to 8 significant bits about five times a layer; with 2-3 layers
 # the logits carry an error of about sqrt(5 L) * 2^-9 = 0.8 % of their scale; three times that is allowed.
 TOL = {"float32": 3e-5, "bfloat16": 2.5e-2}
-LENGTHS = {"A": [5, 47, 130], "B": [1, 40, 97], "C": [33, 64, 100], "D": [9, 140, 300]}
+LENGTHS = {"A": [5, 47, 130], "B": [1, 40, 97], "C": [33, 64, 100], "D": [9, 140, 300], "E": [3, 70, 200]}
 
 
 def make_engine(folder, dtype, cache_tokens, page_size=16, **kw):
@@ -66,7 +66,7 @@ def engines(tiny_models):
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole_tail_and_portions_agree_with_the_plain_implementation(tiny_models, engines, name, dtype):
     eng = engines(name, dtype)
     for i, n in enumerate(LENGTHS[name]):
@@ -147,7 +147,7 @@ def test_the_tcgen05_kernels_carry_a_whole_model(tiny_models, product_pairs):
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_mixed_requests_in_a_pool_so_small_that_pages_are_used_again(tiny_models, name, dtype):
     lens = {"a": 70, "b": 33, "c": 90, "d": 48, "e": 61, "f": 20}
     reqs, wants = {}, {}
