@@ -186,8 +186,9 @@ def run_workload(name, layers=None):
 
 def time_records(engine, ctx, which, repeats=3):
     """Device time (microseconds per launch) of one kind of launch record, run alone: ``which(l)`` gives the index of
-    layer l's record (or None to skip the layer).  The records of all layers run one after the other, so each launch
-    reads its own layer's weights and cache pages from memory; the best of ``repeats`` walks counts."""
+    layer l's record (or None to skip the layer).  The records of all layers run one after the other as one CUDA graph,
+    so each launch reads its own layer's weights and cache pages from memory and follows its predecessor as closely as
+    in a step; the best of ``repeats`` replays counts."""
     import ctypes
     import torch
     from infinicore_infer_b200 import kernels
@@ -216,11 +217,18 @@ def time_records(engine, ctx, which, repeats=3):
                 raise RuntimeError(runner.lib.jk_runner_last_error().decode())
     walk()
     torch.cuda.synchronize()
+    # the walk as one CUDA graph: launches follow one another as they do in a step (each starts under the tail of the one
+    # before), without the host's time between them
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        walk()
+    graph.replay()
+    torch.cuda.synchronize()
     best = None
     for _ in range(repeats):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        walk()
+        graph.replay()
         e1.record()
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1000.0 / len(indices)

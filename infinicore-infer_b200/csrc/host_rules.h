@@ -263,7 +263,8 @@ inline long long skinny_blocks(int sms, int n, int k, int kind) {
     return (long long)tiles * ((nk + ksteps - 1) / ksteps);
 }
 // Which kernel takes a product of `rows` rows: up to 128 rows the few-rows tcgen05 kernel once it has a block for every
-// SM (it then reads W at 5 to 6 TB/s); up to 16 rows the small-row kernel (if it takes the shape: `small_ok`) where it
+// SM (it then reads W at 5 to 6 TB/s), always once it has four blocks for every SM; up to 16 rows the small-row kernel
+// (if it takes the shape: `small_ok`) where it
 // has a second block on the SM to overlap its load phase with (a slice of 16 rows x K fits twice), or so few tiles that
 // they make one wave, or nothing better; above that the tiled tcgen05 kernel by the rule above; else the library.
 // `tcgen05_ok`: the tcgen05 module is there.
@@ -272,6 +273,10 @@ inline Route product_route(const Routing &r, int rows, int n, int k, int kind, b
     if (rows <= 128) {
         const long long need = r.skinny_min_blocks > 0 ? r.skinny_min_blocks : r.sms;
         const bool skinny = tcgen05_ok && k >= 8 && k % 8 == 0 && skinny_blocks(r.sms, n, k, kind) >= need;
+        // a very wide output (the logits): with four rounds of blocks and more the few-rows tcgen05 kernel reads W at 0.95 of
+        // the copy bandwidth for any row count (2B, 1B and 8B output matrices at 1, 8 and 16 rows: 91, 38 and 92 us against
+        // 132, 50 and 211 us of the small-row kernel at 8 rows)
+        if (skinny && skinny_blocks(r.sms, n, k, kind) >= 4LL * r.sms) return ROUTE_SKINNY;
         if (rows <= 16 && small_ok) {
             const long long out_rows = kind == PRODUCT_SWIGLU ? 2LL * n : n;
             if (!skinny || 2 * (32LL * k + 8192) <= 227 * 1024 || (out_rows + 15) / 16 <= r.sms) return ROUTE_SMALL;
