@@ -29,7 +29,7 @@ MODULES: Dict[str, List[str]] = {
     "linear_small": ["linear_small.cu"],
     "gemm_tcgen05": ["gemm_tcgen05.cu", "gemm_skinny.cu"],
     "attention_tcgen05": ["attention_tcgen05.cu"],
-    "runner": ["runner.cu", "capi.cu"],
+    "runner": ["runner.cu", "capi.cu", "reference_abi.cu"],
     "host": ["host.cpp"],
 }
 # modules without device code: built by the host compiler, loadable on a machine without CUDA
