@@ -8,7 +8,7 @@ request's position is what the cache holds of it, logits come back for the rows 
 and errors are exceptions raised before anything ran.
 
 A step whose entries all carry one token is a decode step: it runs as a CUDA graph captured
-once per batch-size bucket, with the batch padded by rows that read and write the null page.
+once per (batch-size bucket, context bucket), with the batch padded by rows that read and write the null page.
 """
 from __future__ import annotations
 
