@@ -208,9 +208,9 @@ def time_records(engine, ctx, which, repeats=3):
         step.lists[index] = view.data_ptr() if view is not None else None
         step.list_n[index] = n
     indices = [i for i in (which(l) for l in range(len(engine.spec.order))) if i is not None]
-    stream = kernels._stream()
 
     def walk():
+        stream = kernels._stream()          # asked for at each walk: a capture runs on a stream of its own
         for i in indices:
             rc = runner.lib.jk_runner_run(ctypes.byref(runner.env), prog.ops, i, 1, ctypes.byref(step), ctypes.byref(runner.buffers), 1, stream)
             if rc:

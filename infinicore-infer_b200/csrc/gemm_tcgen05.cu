@@ -504,6 +504,10 @@ JK_EXPORT int jk_gemm_tcgen05(const void *act, const void *w, void *out, int M, 
         // as long as a unit keeps 32 steps of K.  Measured at 768 x 4096 x 16384: 164 -> 112 us; at 1536 rows 168 -> 150 us.
         // Four cuts of 128 tiles on 74 pairs of SMs look better on paper (seven waves of quarters against two of whole
         // tiles) and are slower (211 against 190 us): a second wave that is three quarters empty runs faster than a full one.
+        // Shorter units do not help a single wave either.  At 2048 x 2304 x 2304 (144 tiles for 148 SMs, 36 steps each):
+        // whole tiles 20.8 us (the library's product of this shape: 19.5), two cuts of 18 steps 23.0, pairs of blocks 21.7,
+        // tiles of 128 columns 30.2.  Two cuts of 18 steps do help 512 rows of that shape (16.0 -> 11.7 us) and then cost
+        // 512 x 2304 x 5760 as much (20.8 -> 24.0), so the limit of 32 steps stays.
         const int nk = (K + TG_BK - 1) / TG_BK;
         const bool pairs_possible = pair_mode() != 0 && M > TG_BM;
         double best = 1e30;
