@@ -111,6 +111,9 @@ int upload_rotary_tables(JkModel *m) {
 }
 
 // The kernel modules by name from a folder, for a program that has no Python around it.
+// The few-row products' own flag (a bounded wait for a tile of weights that ran out): read and cleared by this function.
+int (*g_small_fault)() = nullptr;
+
 int bind_from_directory(JkModel *m, const char *dir, bool need_gemm_tcgen05, bool need_attention_tcgen05) {
     auto open = [&](const char *module, void **handle) -> int {
         const std::string path = std::string(dir) + "/libjk_" + module + ".so";
@@ -152,6 +155,7 @@ int bind_from_directory(JkModel *m, const char *dir, bool need_gemm_tcgen05, boo
     f.linear_small_norm_supports = (SupportsFn)sym(ls, "jk_linear_small_norm_supports");
     f.linear_small_norm = (LinearSmallNormFn)sym(ls, "jk_linear_small_norm");
     f.linear_small_qkv_norm = (LinearSmallQkvNormFn)sym(ls, "jk_linear_small_qkv_norm");
+    g_small_fault = (int (*)())sym(ls, "jk_linear_small_take_fault");
     f.gemm_tcgen05 = (GemmTcgen05Fn)sym(gt, "jk_gemm_tcgen05");
     f.gemm_tcgen05_qkv = (GemmTcgen05QkvFn)sym(gt, "jk_gemm_tcgen05_qkv");
     f.attention_decode = (AttentionDecodeFn)sym(at, "jk_attention_decode");
@@ -422,6 +426,8 @@ int run_batch(JkModel *m, const uint32_t *tokens, uint32_t ntok, const uint32_t 
 
 // After the stream is idle: did a kernel give up a bounded wait?
 int check_status(JkModel *m) {
+    if (g_small_fault != nullptr && g_small_fault() > 0)
+        JK_FAIL(JK_CUDA_ERROR, "batch: a few-row product gave up the bounded wait for its weights; the results of this batch are invalid");
     int status = 0;
     CUDA_TRY(cudaMemcpy(&status, m->env.status, sizeof(int), cudaMemcpyDeviceToHost), "batch: status word");
     if (status != 0) {

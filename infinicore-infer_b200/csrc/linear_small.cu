@@ -21,6 +21,7 @@
 // The library is asked for the same products when M is larger (the reference sends all of its
 // products to a library: src/models/inference_context.cpp:59-79).
 #include "common.cuh"
+#include "tma.cuh"
 
 JK_DEFINE_ERROR_BUFFER(jk_linear_small)
 
@@ -234,6 +235,8 @@ small_linear_kernel(SmallLinearArgs a) {
 // a few tens of KB that every block reads), a few blocks ahead.  Shared memory holds the tile only
 // (private to each thread: it reads back what it copied, so no barrier stands between copy and use);
 // the K slices' partial sums meet in the same memory once the products are done.
+// The TMA variant (the default where the weights are 16-byte aligned) brings the same tile as boxes of 8 rows x 64 k
+// that one lane of each warp asks for; what a thread reads from shared memory and everything after is the same.
 //   EPI_SWIGLU here pairs 8 gate rows with their 8 up rows in one 16-row tile: a thread's accumulators
 //   c0, c1 are then the gate and c2, c3 the up of the same feature and activation rows.
 //   EPI_QKV (the fused [q | k | v] projection) pairs, in the same way, 8 features of a head's first half
@@ -244,24 +247,37 @@ small_linear_kernel(SmallLinearArgs a) {
 //   src/models/jiuge/jiuge.cpp:200-218).
 // ---------------------------------------------------------------------------------------------------
 constexpr int ST_GROUPS = 4;        // commit groups of a thread's copies
-constexpr int ST_AHEAD = 4;         // blocks of k the activation loads run ahead
+constexpr int ST_AHEAD = 4;         // blocks of k the activation loads run ahead (the TMA variant with 16 rows: 2, see there)
 
 constexpr int ST_MAX_WARPS = 16;
 
-template <int MT, int EPI>
+// TMA = true: the tile comes as boxes of 8 rows x 64 k (1 KB, 128-byte swizzle) that one lane of each warp asks for,
+// the slices of K are whole boxes, and a warp waits on a barrier of its own; a thread then reads from the boxes the same
+// 16 bytes that it would have copied by itself.  Whole 128-byte lines by bulk copies instead of 16-byte copies from every
+// thread: measured on a long stream (the logits' matrix) the per-thread copies reach 4.3 TB/s, TMA boxes 6.2.
+__device__ int sl_fault;        // set when a bounded wait for a tile ran out (the host reads and clears it)
+
+template <int MT, int EPI, bool TMA>
 __global__ void __launch_bounds__(ST_MAX_WARPS * 32)
-small_linear_tile_kernel(SmallLinearArgs a) {
+small_linear_tile_kernel(const __grid_constant__ CUtensorMap map_w, SmallLinearArgs a) {
     pdl_trigger();
-    extern __shared__ __align__(16) unsigned char st_smem[];
-    uint4 *mine = reinterpret_cast<uint4 *>(st_smem) + threadIdx.x;       // [2 * per_slice][threads]
+    extern __shared__ __align__(1024) unsigned char st_smem[];
+    uint4 *mine = reinterpret_cast<uint4 *>(st_smem) + threadIdx.x;       // [2 * per_slice][threads]   (not TMA)
     const int nthreads = blockDim.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;           // warp = K slice
     const int g = lane >> 2, t = lane & 3;
     const int kblocks = a.K / 32;
-    const int per_slice = (kblocks + a.ksplit - 1) / a.ksplit;
+    // TMA: slices of whole boxes (two blocks of 32 k each)
+    const int per_slice = TMA ? 2 * (((kblocks + 1) / 2 + a.ksplit - 1) / a.ksplit) : (kblocks + a.ksplit - 1) / a.ksplit;
     const int kb_begin = min(kblocks, warp * per_slice), kb_end = min(kblocks, kb_begin + per_slice);
     const int nkb = kb_end - kb_begin;
     const int per_group = (per_slice + ST_GROUPS - 1) / ST_GROUPS;
+    unsigned char *boxes = st_smem + (size_t)warp * (per_slice / 2) * 2048;     // TMA: [box of the slice][rows g | rows g + 8][8 x 128 bytes]
+    unsigned long long *tile_full = reinterpret_cast<unsigned long long *>(st_smem + (size_t)a.ksplit * (per_slice / 2) * 2048);   // TMA: [warps]
+    if (TMA && (smem_u32(st_smem) & 1023u)) {                 // swizzled boxes need it; never seen
+        if (threadIdx.x == 0) atomicExch(&sl_fault, 2);
+        return;
+    }
     // weight rows of this thread: EPI_F32: features n0 + g and n0 + g + 8; EPI_SWIGLU: gate and up of n0 + g.
     // Rows are clamped inside the matrix; what a clamped row yields is not stored.
     const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? 8 : 16);
@@ -274,17 +290,39 @@ small_linear_tile_kernel(SmallLinearArgs a) {
         r0 = (size_t)qkv_head * a.qkv.dh + qkv_j0 + g;
         r1 = r0 + a.qkv.dh / 2;
     }
-    const __nv_bfloat16 *p0 = a.w + r0 * a.K + (size_t)kb_begin * 32 + t * 8;
-    const __nv_bfloat16 *p1 = a.w + r1 * a.K + (size_t)kb_begin * 32 + t * 8;
-    for (int d = 0; d < per_slice; ++d) {
-        if (d < nkb) {
-            cp_async16(mine + (size_t)(2 * d) * nthreads, p0 + d * 32);
-            cp_async16(mine + (size_t)(2 * d + 1) * nthreads, p1 + d * 32);
+    if (TMA) {
+        // first rows of the tile's two groups of eight (rows beyond the matrix arrive as zeros)
+        int row_lo = n0, row_hi = EPI == EPI_SWIGLU ? a.N + n0 : n0 + 8;
+        if (EPI == EPI_QKV) {
+            row_lo = qkv_head * a.qkv.dh + qkv_j0;
+            row_hi = row_lo + a.qkv.dh / 2;
         }
-        if ((d + 1) % per_group == 0 || d + 1 == per_slice) cp_async_commit();
+        if (lane == 0) {
+            mbar_init(&tile_full[warp], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+            const int nbox = (nkb + 1) / 2;
+            if (nbox > 0) {
+                mbar_expect_tx(&tile_full[warp], (unsigned)nbox * 2048u);
+                for (int c = 0; c < nbox; ++c) {
+                    tma_load_2d(boxes + (size_t)c * 2048, &map_w, &tile_full[warp], kb_begin * 32 + c * 64, row_lo);
+                    tma_load_2d(boxes + (size_t)c * 2048 + 1024, &map_w, &tile_full[warp], kb_begin * 32 + c * 64, row_hi);
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        const __nv_bfloat16 *p0 = a.w + r0 * a.K + (size_t)kb_begin * 32 + t * 8;
+        const __nv_bfloat16 *p1 = a.w + r1 * a.K + (size_t)kb_begin * 32 + t * 8;
+        for (int d = 0; d < per_slice; ++d) {
+            if (d < nkb) {
+                cp_async16(mine + (size_t)(2 * d) * nthreads, p0 + d * 32);
+                cp_async16(mine + (size_t)(2 * d + 1) * nthreads, p1 + d * 32);
+            }
+            if ((d + 1) % per_group == 0 || d + 1 == per_slice) cp_async_commit();
+        }
+        // every thread commits the same number of groups: pad to ST_GROUPS
+        for (int j = (per_slice + per_group - 1) / per_group; j < ST_GROUPS; ++j) cp_async_commit();
     }
-    // every thread commits the same number of groups: pad to ST_GROUPS
-    for (int j = (per_slice + per_group - 1) / per_group; j < ST_GROUPS; ++j) cp_async_commit();
     pdl_wait();          // the weights do not depend on the kernel before this one; the activations do
 
     // what the epilogue of the first warp needs from memory is asked for now, so that it has arrived by then
@@ -323,32 +361,46 @@ small_linear_tile_kernel(SmallLinearArgs a) {
     float acc[MT][4];
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
-    uint4 bq[ST_AHEAD][MT];
+    constexpr int AHEAD = (TMA && MT == 2) ? 2 : ST_AHEAD;
+    uint4 bq[AHEAD][MT];
 #pragma unroll
-    for (int d = 0; d < ST_AHEAD; ++d)
+    for (int d = 0; d < AHEAD; ++d)
 #pragma unroll
         for (int m = 0; m < MT; ++m)
             bq[d][m] = (arow[m] && d < nkb) ? *reinterpret_cast<const uint4 *>(ap[m] + d * 32) : make_uint4(0, 0, 0, 0);
 
-    for (int q0 = 0; q0 < nkb; q0 += ST_AHEAD) {
+    if (TMA && nkb > 0 && !mbar_wait(&tile_full[warp], 0)) {
+        if (lane == 0) atomicExch(&sl_fault, 1);                // the products below run on what is there: the result is not valid
+        mbar_wait(&tile_full[warp], 0);                          // copies still on their way get a second bounded time to land
+    }
+    for (int q0 = 0; q0 < nkb; q0 += AHEAD) {
 #pragma unroll
-        for (int d = 0; d < ST_AHEAD; ++d) {
+        for (int d = 0; d < AHEAD; ++d) {
             const int q = q0 + d;
             if (q < nkb) {
-                if (q % per_group == 0) {                       // the group of copies this block of k belongs to
-                    const int grp = q / per_group;
-                    if (grp == 0) cp_async_wait<ST_GROUPS - 1>();
-                    else if (grp == 1) cp_async_wait<ST_GROUPS - 2>();
-                    else if (grp == 2) cp_async_wait<ST_GROUPS - 3>();
-                    else cp_async_wait<0>();
+                uint4 w0, w1;
+                if (TMA) {
+                    // 16 bytes t of the block's 64 in row g of both groups; the 16-byte pieces of a row are swizzled by the row
+                    const unsigned char *box = boxes + (size_t)(q >> 1) * 2048 + g * 128 + (((((q & 1) << 2) + t) ^ g) << 4);
+                    w0 = *reinterpret_cast<const uint4 *>(box);
+                    w1 = *reinterpret_cast<const uint4 *>(box + 1024);
+                } else {
+                    if (q % per_group == 0) {                       // the group of copies this block of k belongs to
+                        const int grp = q / per_group;
+                        if (grp == 0) cp_async_wait<ST_GROUPS - 1>();
+                        else if (grp == 1) cp_async_wait<ST_GROUPS - 2>();
+                        else if (grp == 2) cp_async_wait<ST_GROUPS - 3>();
+                        else cp_async_wait<0>();
+                    }
+                    w0 = mine[(size_t)(2 * q) * nthreads];
+                    w1 = mine[(size_t)(2 * q + 1) * nthreads];
                 }
-                const uint4 w0 = mine[(size_t)(2 * q) * nthreads], w1 = mine[(size_t)(2 * q + 1) * nthreads];
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
                     const uint4 b = bq[d][m];
                     mma16816(acc[m], w0.x, w1.x, w0.y, w1.y, b.x, b.y);
                     mma16816(acc[m], w0.z, w1.z, w0.w, w1.w, b.z, b.w);
-                    if (arow[m] && q + ST_AHEAD < nkb) bq[d][m] = *reinterpret_cast<const uint4 *>(ap[m] + (q + ST_AHEAD) * 32);
+                    if (arow[m] && q + AHEAD < nkb) bq[d][m] = *reinterpret_cast<const uint4 *>(ap[m] + (q + AHEAD) * 32);
                 }
             }
         }
@@ -474,14 +526,61 @@ static size_t small_tile_smem(int K, int MT, int ksplit) {
     return tile > red ? tile : red;
 }
 
+// The slices of K of the TMA variant: as many warps (4 to 16) as share the boxes of 64 k out most evenly, more if equal.
+// With 16 activation rows a thread holds 80 registers: ten warps at most, so that three blocks still share an SM.
+// Measured in a 2B decode step (ms, batch 1 / 8 / 16 at 512 keys) for lookahead and warps: 4 and 12: 1.66, 2.02, 2.91;
+// 4 and 9: 1.72, 2.05, 2.75; 2 and 9: 1.75, 2.16, 2.58; 6 and 12: 1.58, 2.04, 3.23; per-thread copies: 1.83, 2.07, 2.62.
+static int tma_ksplit(int K, int MT) {
+    const int boxes = (K + 63) / 64;
+    int best = 1, best_waste = 1 << 30;
+    for (int w = MT == 2 ? 10 : ST_MAX_WARPS; w >= 4; --w) {
+        const int waste = (boxes + w - 1) / w * w - boxes;
+        if (waste < best_waste) { best = w; best_waste = waste; }
+    }
+    return boxes < 4 ? boxes : best;
+}
+static size_t small_tile_smem_tma(int K, int MT, int ksplit) {
+    const int boxes = (K + 63) / 64, per_warp = (boxes + ksplit - 1) / ksplit;
+    const size_t tile = (size_t)ksplit * per_warp * 2048;
+    const size_t red = (size_t)ksplit * MT * 4 * 32 * sizeof(float);
+    return (tile > red ? tile : red) + ST_MAX_WARPS * sizeof(unsigned long long);
+}
+JK_EXPORT int jk_linear_small_take_fault() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, sl_fault, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(sl_fault, &zero, sizeof(int));
+    return v;
+}
+
 template <int MT, int EPI>
-static int launch_tile(const SmallLinearArgs &a, size_t smem, cudaStream_t stream) {
+static int launch_tile(const SmallLinearArgs &a_in, size_t smem, cudaStream_t stream) {
+    SmallLinearArgs a = a_in;
+    const int tiles = EPI == EPI_SWIGLU ? (a.N + 7) / 8 : (a.N + 15) / 16;     // EPI_QKV: 16 features a tile as well
+    static const bool tma_off = [] { const char *v = getenv("JK_SMALL_NO_TMA"); return v && v[0] == '1'; }();
+    const int ks = tma_ksplit(a.K, MT);
+    const size_t smem_tma = small_tile_smem_tma(a.K, MT, ks);
+    CUtensorMap map_w;
+    bool tma = !tma_off && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0 && smem_tma <= 200 * 1024;
+    if (tma) {
+        const int rows = EPI == EPI_SWIGLU ? 2 * a.N : a.N;
+        if (tensor_map_2d(a.w, rows, a.K, a.K, 8, 64, 2, &map_w) != JK_OK) tma = false;      // the other variant needs none
+    }
+    if (tma) {
+        a.ksplit = ks;
+        if (smem_tma > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(small_linear_tile_kernel<MT, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tma);
+            if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "linear_small: %s", cudaGetErrorString(e));
+        }
+        jk_launch(small_linear_tile_kernel<MT, EPI, true>, dim3(tiles), dim3(a.ksplit * 32), smem_tma, stream, map_w, a);
+        JK_CHECK_LAUNCH("linear_small");
+        return JK_OK;
+    }
+    memset(&map_w, 0, sizeof(map_w));
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(small_linear_tile_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(small_linear_tile_kernel<MT, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "linear_small: %s", cudaGetErrorString(e));
     }
-    const int tiles = EPI == EPI_SWIGLU ? (a.N + 7) / 8 : (a.N + 15) / 16;     // EPI_QKV: 16 features a tile as well
-    jk_launch(small_linear_tile_kernel<MT, EPI>, dim3(tiles), dim3(a.ksplit * 32), smem, stream, a);
+    jk_launch(small_linear_tile_kernel<MT, EPI, false>, dim3(tiles), dim3(a.ksplit * 32), smem, stream, map_w, a);
     JK_CHECK_LAUNCH("linear_small");
     return JK_OK;
 }

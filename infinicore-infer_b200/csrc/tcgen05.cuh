@@ -2,43 +2,13 @@
 // tcgen05.mma and its descriptors), the epilogue codes of the entry points, and the cache of tensor maps.
 #pragma once
 
-#include "common.cuh"
-
-#include <cuda.h>
-#include <map>
-#include <mutex>
-#include <tuple>
+#include "tma.cuh"
 
 enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_QKV = 4 };
 
 constexpr int TG_BM = 128, TG_BK = 64, TG_STAGES = 4, TG_THREADS = 192;
-constexpr unsigned TG_SPIN_LIMIT = 1u << 20;      // polls of one wait before it gives up
 
-// ---- PTX wrappers ------------------------------------------------------------------------------
-__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the limit is reached (the caller records where and drains).
-__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity) {
-    for (unsigned i = 0; i < TG_SPIN_LIMIT; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void *smem, const CUtensorMap *map, unsigned long long *bar, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                 ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
+// ---- PTX wrappers (mbarriers and TMA loads: tma.cuh) ------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(unsigned *slot, unsigned columns) {      // one whole warp
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(slot)), "r"(columns) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -141,51 +111,3 @@ __host__ __device__ constexpr unsigned instr_desc_bf16(int bn, int bm = TG_BM) {
 
 // CTAS = 2: a pair of blocks works on a tile of 256 x BN; each holds its 128 rows of A and BN / 2 rows of B,
 // which leaves room for a deeper ring.
-
-// ---- host side ---------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
-// Tensor maps are kept by (pointer, shape, box, type): weights and step buffers come back with the
-// same addresses step after step.  (The reference keeps its operator descriptors in an LRU cache
-// keyed by shapes and strides: src/models/cache_manager.hpp:32-138.)
-static int tensor_map_2d(const void *ptr, int rows, int cols, int ld, int box_rows, int box_cols, int elem_bytes,
-                         CUtensorMap *out) {
-    using Key = std::tuple<const void *, int, int, int, int, int, int>;
-    static std::map<Key, CUtensorMap> cache;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    const Key key(ptr, rows, cols, ld, box_rows, box_cols, elem_bytes);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return JK_OK; }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: the driver has no cuTensorMapEncodeTiled");
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
-    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    CUtensorMap m;
-    const CUresult r = fn(&m, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                          const_cast<void *>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) JK_FAIL(JK_CUDA_ERROR, "gemm_tcgen05: cuTensorMapEncodeTiled failed with %d", (int)r);
-    if (cache.size() > 4096) cache.clear();
-    cache[key] = m;
-    *out = m;
-    return JK_OK;
-}
-

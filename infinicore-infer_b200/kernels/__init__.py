@@ -331,6 +331,12 @@ def gemm_status(device) -> torch.Tensor:
 
 def check_gemm_status(device) -> None:
     """Read the status word (synchronises); raise if a kernel gave up waiting."""
+    small = _build._loaded.get("linear_small")
+    if small is not None:
+        fault = small.jk_linear_small_take_fault()
+        if fault > 0:
+            raise KernelError(f"linear_small: a bounded wait for a tile of weights ran out or shared memory was misaligned "
+                              f"(code {fault}); the step's results are not valid")
     key = str(device)
     if key in _tg_status:
         code = int(_tg_status[key].item())

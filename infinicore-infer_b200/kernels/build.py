@@ -37,7 +37,7 @@ HOST_ONLY = {"host"}
 HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared"]
 # libraries a module links against (the others need the CUDA runtime only)
 LINK: Dict[str, List[str]] = {"runner": ["-lcublas"]}
-HEADERS = ["common.cuh", "attention_static_scratch.h", "runner.h", "model_api.h", "tcgen05.cuh", "host_rules.h"]
+HEADERS = ["common.cuh", "attention_static_scratch.h", "runner.h", "model_api.h", "tcgen05.cuh", "tma.cuh", "host_rules.h"]
 
 # -use_fast_math is deliberately absent: expf, division and sqrt stay accurate.
 NVCC_FLAGS = [
