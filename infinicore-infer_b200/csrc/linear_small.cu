@@ -257,7 +257,7 @@ constexpr int ST_MAX_WARPS = 16;
 // thread: measured on a long stream (the logits' matrix) the per-thread copies reach 4.3 TB/s, TMA boxes 6.2.
 __device__ int sl_fault;        // set when a bounded wait for a tile ran out (the host reads and clears it)
 
-template <int MT, int EPI, bool TMA>
+template <int MT, int EPI, bool TMA, int AHEAD = ST_AHEAD>
 __global__ void __launch_bounds__(ST_MAX_WARPS * 32)
 small_linear_tile_kernel(const __grid_constant__ CUtensorMap map_w, SmallLinearArgs a) {
     pdl_trigger();
@@ -361,7 +361,6 @@ small_linear_tile_kernel(const __grid_constant__ CUtensorMap map_w, SmallLinearA
     float acc[MT][4];
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
-    constexpr int AHEAD = (TMA && MT == 2) ? 2 : ST_AHEAD;
     uint4 bq[AHEAD][MT];
 #pragma unroll
     for (int d = 0; d < AHEAD; ++d)
@@ -567,11 +566,20 @@ static int launch_tile(const SmallLinearArgs &a_in, size_t smem, cudaStream_t st
     }
     if (tma) {
         a.ksplit = ks;
+        // How far the activation loads run ahead of the products: all the way where every block has an SM to itself
+        // (registers are no object there and no load's latency shows: batch 8 at 512 keys 1.99 -> 1.92 ms a step); else 4
+        // blocks of k.  With 16 rows: 4 and 2 (all the way costs 128 registers and spills: batch 16 2.52 -> 2.78 ms).
+        static const int sms = [] {
+            int dev = 0, n = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+            return n;
+        }();
+        auto kernel = tiles <= sms ? small_linear_tile_kernel<MT, EPI, true, MT == 2 ? 4 : 12> : small_linear_tile_kernel<MT, EPI, true, MT == 2 ? 2 : ST_AHEAD>;
         if (smem_tma > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(small_linear_tile_kernel<MT, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tma);
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tma);
             if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "linear_small: %s", cudaGetErrorString(e));
         }
-        jk_launch(small_linear_tile_kernel<MT, EPI, true>, dim3(tiles), dim3(a.ksplit * 32), smem_tma, stream, map_w, a);
+        jk_launch(kernel, dim3(tiles), dim3(a.ksplit * 32), smem_tma, stream, map_w, a);
         JK_CHECK_LAUNCH("linear_small");
         return JK_OK;
     }
