@@ -594,6 +594,29 @@ def test_linear_small_streams_weights_for_few_rows(K, M, N, K_):
     torch.testing.assert_close(out.double().cpu(), want, rtol=1e-4, atol=1e-4)      # float32 accumulation of bf16 products
 
 
+def test_linear_small_with_copies_from_every_thread_instead_of_tma_boxes():
+    """The tile kernel's other way to bring its tile (what runs where the weights are not 16-byte aligned for TMA or
+    a tensor map cannot be had): a process of its own, because the switch is read once."""
+    import os, subprocess, sys
+    code = """
+import math, os, sys, torch
+sys.path.insert(0, os.getcwd())
+from infinicore_infer_b200 import kernels as K
+for M, N, K_ in ((1, 48, 64), (8, 301, 96), (13, 1000, 5760), (16, 2304, 2304)):
+    g = torch.Generator().manual_seed(M * N + K_)
+    act = torch.randn(M, K_, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+    out = torch.full((M, N), 9.0, device="cuda:0")
+    K.linear_small(act.cuda(), w.cuda(), out)
+    torch.testing.assert_close(out.double().cpu(), act.double() @ w.double().T, rtol=1e-4, atol=1e-4)
+print("equal")
+"""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-c", code], cwd=root, env=dict(os.environ, JK_SMALL_NO_TMA="1"),
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0 and "equal" in p.stdout, p.stderr[-2000:]
+
+
 @pytest.mark.parametrize("M", [1, 8, 13])
 @pytest.mark.parametrize("N,K_", [(136, 96), (5760, 2304), (50, 64)])
 def test_linear_small_with_swiglu_epilogue(K, M, N, K_):
