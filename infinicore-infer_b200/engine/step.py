@@ -87,6 +87,9 @@ class Engine:
         self.steps_run = 0
         self.tokens_run = 0
         self.kernel_launches = 0      # this package's kernels launched by steps (replayed graphs included)
+        # A decode step that was asked to may prepare the step after it while the device still runs (see _stage_next).
+        self._staged: Optional[tuple] = None
+        self.staged_steps = 0         # steps that ran from what the step before them had prepared
 
     # ---- construction -------------------------------------------------------------------------
     @classmethod
@@ -116,10 +119,16 @@ class Engine:
         return self.cache.length(req_id) if self.cache.is_live(req_id) else 0
 
     # ---- the step -------------------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], stage_next: bool = False) -> torch.Tensor:
         """Run the entries as one batch; return float32 logits ``[wanted, vocab]`` on the device,
-        in the order of the entries and of their ``want``."""
+        in the order of the entries and of their ``want``.  ``stage_next``: the caller expects to come back with one
+        more token for each of these requests (a decode loop); the step may then prepare that step before it returns."""
         entries = [e for e in entries if len(e.tokens)]
+        staged, self._staged = self._staged, None
+        if staged is not None:
+            if entries and self._staged_fits(staged, entries):
+                return self._run_staged(staged, entries, stage_next)
+            self._drop_staged(staged)
         if not entries:
             return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=self.device)
         self._validate(entries)
@@ -145,6 +154,68 @@ class Engine:
             self.cache.commit(r, n)
         self.steps_run += 1
         self.tokens_run += sum(len(e.tokens) for e in entries)
+        if decode and stage_next:
+            self._stage_next([e.req_id for e in entries], [s + 1 for s in starts])
+        return logits
+
+    # ---- the step after a decode step, prepared while the device runs this one --------------------------------
+    # Between two decode steps of the same requests the device idles while the host validates, takes pages, packs the
+    # metadata and launches.  All of that but the token ids is known one step early: after a decode step's graph is
+    # launched, the next step's pages are taken and its metadata packed into a pinned buffer of its own.  If the next
+    # call brings exactly one token for each of the same requests, only the ids are written, the buffer copied and the
+    # graph replayed; if it brings anything else, the pages taken ahead go back before the step is planned.
+    def _stage_next(self, reqs: List[object], starts: List[int]) -> None:
+        if any(s + 1 > self.spec.max_positions for s in starts):
+            return
+        B = len(reqs)
+        bucket = self._bucket(B)
+        if bucket > self.max_requests:
+            bucket = B
+        key = (bucket, self._context_of(starts, [1] * B))
+        new_len = {r: s + 1 for r, s in zip(reqs, starts)}
+        if key not in self._graphs or not self.cache.can_reserve(new_len):
+            return
+        for r, n in new_len.items():
+            self.cache.reserve(r, n)
+        lay, turn = self._pack([StepEntry(r, [0], [0]) for r in reqs], starts, B, B, pad_to=bucket, copy=False)
+        self._staged = (tuple(reqs), list(starts), new_len, key, lay, turn)
+
+    def _staged_fits(self, staged, entries) -> bool:
+        reqs, starts = staged[0], staged[1]
+        return len(entries) == len(reqs) and all(
+            e.req_id == r and len(e.tokens) == 1 and self.cache.is_live(r) and self.cache.length(r) == s
+            for e, r, s in zip(entries, reqs, starts))
+
+    def _drop_staged(self, staged) -> None:
+        for r in staged[0]:
+            if self.cache.is_live(r):
+                self.cache.truncate(r, self.cache.length(r))
+
+    def _run_staged(self, staged, entries, stage_next: bool) -> torch.Tensor:
+        reqs, starts, new_len, key, lay, turn = staged
+        B = len(entries)
+        tokens = [e.tokens[0] for e in entries]
+        if min(tokens) < 0 or max(tokens) >= self.spec.vocab_size or any(w != 0 for e in entries for w in e.want):
+            self._drop_staged(staged)
+            self._validate(entries)           # says what is wrong with them
+            raise StepError("a wanted place is not among a request's tokens")
+        host = self._meta_host[turn].numpy()
+        host[lay.tokens: lay.tokens + B] = tokens
+        self._meta_dev[:lay.total].copy_(self._meta_host[turn][:lay.total], non_blocking=True)
+        if self._meta_events[turn] is None:
+            self._meta_events[turn] = torch.cuda.Event()
+        self._meta_events[turn].record()
+        graph, out, launches = self._graphs[key]
+        graph.replay()
+        self.kernel_launches += launches
+        for r, n in new_len.items():
+            self.cache.commit(r, n)
+        self.steps_run += 1
+        self.staged_steps += 1
+        self.tokens_run += B
+        logits = self._graph_rows(out, entries)
+        if stage_next:
+            self._stage_next(list(reqs), [s + 1 for s in starts])
         return logits
 
     def _forward(self, ctx: StepContext) -> torch.Tensor:
@@ -191,7 +262,7 @@ class Engine:
             made = self._layouts[key] = (lay, places)
         return made
 
-    def _pack(self, entries, starts, B: int, T: int, pad_to: Optional[int] = None):
+    def _pack(self, entries, starts, B: int, T: int, pad_to: Optional[int] = None, copy: bool = True):
         """Fill a pinned buffer with the step's metadata (``jk::pack_step`` and the mixers' work lists) and copy it in
         one piece.  ``pad_to``: batch size of a captured decode step; missing entries become rows that use slot 0
         and the null page at position 0, and every row is a wanted row."""
@@ -226,6 +297,8 @@ class Engine:
             arrays = {name: host[lay.extra + off: lay.extra + off + max(words, 1)] for o, name, off, words in places if o is owner}
             for name, got in owner.fill_step_lists(B, nB, lens, starts, arrays).items():
                 counts[f"{owner.__name__}.{name}"] = got
+        if not copy:
+            return lay, turn
         self._meta_dev[:lay.total].copy_(self._meta_host[turn][:lay.total], non_blocking=True)
         if self._meta_events[turn] is None:
             self._meta_events[turn] = torch.cuda.Event()
@@ -310,7 +383,11 @@ class Engine:
         graph, out, launches = rec
         graph.replay()
         self.kernel_launches += launches
+        return self._graph_rows(out, entries)
+
+    def _graph_rows(self, out: torch.Tensor, entries) -> torch.Tensor:
         # `out` is the captured graph's own buffer, which the next replay overwrites: the caller gets a copy
+        B = len(entries)
         if all(len(e.want) == 1 for e in entries):
             return out[:B].clone()
         rows = []

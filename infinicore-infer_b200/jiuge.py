@@ -172,7 +172,7 @@ class JiugeForCauslLM:
 
     def batch_infer_one_round(self, tasks: List[InferTask]) -> List[int]:
         """One step over the tasks' pending tokens; one sampled token per task (scripts/jiuge.py:529-537)."""
-        logits = self.engine.step(self._entries(tasks))
+        logits = self.engine.step(self._entries(tasks), stage_next=True)
         params = [SamplingParams(t.temperature, t.topk, t.topp, getattr(t, "seed", self.sample_seed)) for t in tasks]
         return self.sampler.sample(logits, params, [t.pos + len(t.tokens) for t in tasks])
 

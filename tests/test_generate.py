@@ -176,6 +176,49 @@ def test_round_by_round_with_tasks_and_the_cache_pool(tiny_models, models):
     assert not model.engine.cache.lengths
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_rounds_run_from_what_the_round_before_prepared(tiny_models, dtype):
+    """In a loop of ``batch_infer_one_round`` a decode step prepares the next one (pages, metadata) while the device
+    runs; the tokens are the plain implementation's all the same, and when the next call is another step than the
+    one prepared, the pages taken ahead are back before it is planned."""
+    from infinicore_infer_b200.jiuge import JiugeForCauslLM
+    from infinicore_infer_b200.tasks import InferTask, KVCache
+    folder, cfg, w = tiny_models["A"]
+    model = JiugeForCauslLM(folder, dtype=dtype, max_batch=4, page_size=8, num_pages=16)
+    eng = model.engine
+    prompts = [random_tokens(2100 + i, n, cfg["vocab_size"]) for i, n in enumerate((7, 15))]
+    tasks = []
+    for i, p in enumerate(prompts):
+        t = InferTask(i, list(p), model.max_context_len(), 0.0, 1, 1.0, [])
+        t.bind_kvcache(KVCache(model))
+        tasks.append(t)
+    outs = [[], []]
+    for _ in range(12):                                   # 15 + 12 crosses page edges of 8 for both requests
+        for t, o, tok in zip(tasks, outs, model.batch_infer_one_round(tasks)):
+            o.append(tok)
+            t.next(tok)
+    assert eng.staged_steps >= 9                          # all but the prompts' step, the first decode step and its capture
+    margin = 0.0 if dtype == "float32" else 0.05
+    for p, o in zip(prompts, outs):
+        assert_greedy(cfg, w, p, o, margin)
+    eng.cache.check_invariants()
+    # the step that was prepared is not the one that comes: one request alone, then a new prompt beside it
+    in_use = lambda: [g.pool.in_use for g in eng.cache.groups]
+    before = in_use()
+    tok = model.batch_infer_one_round(tasks[:1])[0]
+    assert_greedy(cfg, w, prompts[0] + outs[0], [tok], margin)
+    tasks[0].next(tok)
+    eng.cache.check_invariants()
+    third = InferTask(2, random_tokens(2103, 9, cfg["vocab_size"]), model.max_context_len(), 0.0, 1, 1.0, [])
+    third.bind_kvcache(KVCache(model))
+    toks = model.batch_infer_one_round([tasks[0], third])
+    assert_greedy(cfg, w, list(third.tokens), [toks[1]], margin)
+    for t in tasks + [third]:
+        t.kvcache().drop(model)
+    assert in_use() == [0] * len(eng.cache.groups) and before != in_use()
+    eng.check()
+
+
 def test_perplexity_matches_the_plain_implementation(tiny_models, models):
     _, cfg, w = tiny_models["C"]
     model = models("C", "float32")
