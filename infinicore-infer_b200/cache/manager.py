@@ -53,6 +53,9 @@ class CacheManager:
         self.views: List[object] = [None] * len(needs)
         self.lengths: Dict[object, int] = {}
         self._state_tensors: List[torch.Tensor] = []
+        # request -> positions that every group has pages for already (a step within them asks the groups nothing:
+        # fifteen of sixteen decode steps with pages of 16)
+        self._room: Dict[object, int] = {}
 
         # Needs with equal group keys share a group; a need without a key (per-request state) gets storage of its own.
         # What each kind of need provides is the need's own business (``CacheNeed`` in groups.py).
@@ -89,13 +92,18 @@ class CacheManager:
         return self.lengths[req]
 
     def pages_needed(self, req, new_len: int) -> List[int]:
+        if new_len <= self._room.get(req, 0):
+            return [0] * len(self.groups)
         start = self.lengths.get(req, 0)
         return [g.pages_needed(req, start, new_len) for g in self.groups]
 
     def can_reserve(self, wants: Dict[object, int]) -> bool:
         """Would ``reserve`` succeed for all of ``{request: new_len}`` together?"""
         need = [0] * len(self.groups)
+        room = self._room
         for req, new_len in wants.items():
+            if new_len <= room.get(req, 0):
+                continue
             for gi, n in enumerate(self.pages_needed(req, new_len)):
                 need[gi] += n
         return all(n <= g.pool.available for n, g in zip(need, self.groups))
@@ -106,6 +114,8 @@ class CacheManager:
             raise KeyError(f"request {req!r} was not admitted")
         if new_len > self.max_positions:
             raise ValueError(f"request {req!r}: {new_len} positions exceed the maximum of {self.max_positions}")
+        if new_len <= self._room.get(req, 0):
+            return
         start = self.lengths[req]
         done = []
         try:
@@ -115,6 +125,7 @@ class CacheManager:
             for g, pages in done:
                 g.give_back(req, pages)
             raise
+        self._room[req] = min((len(g.tables[req]) for g in self.groups), default=0) * self.page_size if self.groups else self.max_positions
 
     def commit(self, req, new_len: int) -> None:
         self.lengths[req] = new_len
@@ -128,6 +139,7 @@ class CacheManager:
         for g in self.groups:
             g.truncate(req, new_len)
         self.lengths[req] = new_len
+        self._room[req] = min((len(g.tables.get(req, ())) for g in self.groups), default=0) * self.page_size if self.groups else self.max_positions
 
     def release(self, req) -> None:
         if req not in self.lengths:
@@ -136,6 +148,7 @@ class CacheManager:
             g.release(req)
         self.slots.release(req)
         del self.lengths[req]
+        self._room.pop(req, None)
 
     # ---- what a step uploads ----------------------------------------------------------------
     def block_table_rows(self, group_index: int, reqs: Sequence[object], out: np.ndarray) -> None:
@@ -175,6 +188,12 @@ class CacheManager:
                 raise AssertionError(f"{g.name}: pool says {sorted(held)} are out, tables hold {sorted(seen)}")
             if g.pool.in_use + g.pool.available != g.pool.capacity:
                 raise AssertionError(f"{g.name}: a page is lost")
+            for req, room in self._room.items():
+                table = g.tables.get(req, [])
+                last = (room + self.page_size - 1) // self.page_size
+                first = max(g._first_needed_block(self.lengths.get(req, 0)), g.first_block.get(req, 0))
+                if last > len(table) or any(p == NO_PAGE for p in table[first:last]):
+                    raise AssertionError(f"{g.name}: {req!r} is said to have pages for {room} positions and has not")
             for req, table in g.tables.items():
                 row = g.row(req)
                 mirror = [] if row is None else row.tolist()

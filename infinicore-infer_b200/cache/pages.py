@@ -31,6 +31,9 @@ class PagePool:
         self.reserved = reserved
         self.name = name
         self._pool = NativePagePool(num_pages, reserved)
+        # how many pages are free, counted here as well: every page goes out and comes back through this object, and a
+        # step asks for the count far more often than it takes a page
+        self._free = num_pages - reserved
 
     @property
     def capacity(self) -> int:
@@ -38,11 +41,11 @@ class PagePool:
 
     @property
     def available(self) -> int:
-        return self._pool.available()
+        return self._free
 
     @property
     def in_use(self) -> int:
-        return self.capacity - self._pool.available()
+        return self.capacity - self._free
 
     @property
     def high_water(self) -> int:
@@ -51,13 +54,18 @@ class PagePool:
     def alloc(self, n: int) -> List[int]:
         if n < 0:
             raise ValueError("negative page count")
-        out = self._pool.alloc(n)
+        if n == 0:
+            return []
+        out = self._pool.alloc(n) if n <= self._free else None
         if out is None:
-            raise OutOfPages(n, self._pool.available(), self.name)
+            raise OutOfPages(n, self._free, self.name)
+        self._free -= n
         return out
 
     def free(self, pages: Iterable[int]) -> None:
         pages = list(pages)
+        if not pages:
+            return
         rc = self._pool.free(pages)
         if rc == 1:
             bad = next(p for p in pages if not (self.reserved <= p < self.num_pages))
@@ -67,6 +75,7 @@ class PagePool:
             raise ValueError(f"page {bad} freed twice (or never handed out)")
         if rc == 3:
             raise ValueError("a page appears twice in one free")
+        self._free += len(pages)
 
     def held_pages(self) -> List[int]:
         return [p for p in range(self.reserved, self.num_pages) if self._pool.is_held(p)]

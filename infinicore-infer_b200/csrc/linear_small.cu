@@ -65,6 +65,7 @@ struct SmallLinearArgs {
     int M, N, K, ldo, ksplit, n_units;
     SmallQkvDest qkv;           // EPI_QKV only
     SmallNormFuse norm;         // the tile kernel only
+    int *fault;                 // the TMA tile kernel: receives 1 when its bounded wait runs out, 2 for misaligned shared memory
 };
 
 constexpr int SL_MAX_WARPS = 8;
@@ -255,7 +256,6 @@ constexpr int ST_MAX_WARPS = 16;
 // the slices of K are whole boxes, and a warp waits on a barrier of its own; a thread then reads from the boxes the same
 // 16 bytes that it would have copied by itself.  Whole 128-byte lines by bulk copies instead of 16-byte copies from every
 // thread: measured on a long stream (the logits' matrix) the per-thread copies reach 4.3 TB/s, TMA boxes 6.2.
-__device__ int sl_fault;        // set when a bounded wait for a tile ran out (the host reads and clears it)
 
 template <int MT, int EPI, bool TMA, int AHEAD = ST_AHEAD>
 __global__ void __launch_bounds__(ST_MAX_WARPS * 32)
@@ -275,7 +275,7 @@ small_linear_tile_kernel(const __grid_constant__ CUtensorMap map_w, SmallLinearA
     unsigned char *boxes = st_smem + (size_t)warp * (per_slice / 2) * 2048;     // TMA: [box of the slice][rows g | rows g + 8][8 x 128 bytes]
     unsigned long long *tile_full = reinterpret_cast<unsigned long long *>(st_smem + (size_t)a.ksplit * (per_slice / 2) * 2048);   // TMA: [warps]
     if (TMA && (smem_u32(st_smem) & 1023u)) {                 // swizzled boxes need it; never seen
-        if (threadIdx.x == 0) atomicExch(&sl_fault, 2);
+        if (threadIdx.x == 0 && a.fault != nullptr) *reinterpret_cast<volatile int *>(a.fault) = 2;
         return;
     }
     // weight rows of this thread: EPI_F32: features n0 + g and n0 + g + 8; EPI_SWIGLU: gate and up of n0 + g.
@@ -369,7 +369,7 @@ small_linear_tile_kernel(const __grid_constant__ CUtensorMap map_w, SmallLinearA
             bq[d][m] = (arow[m] && d < nkb) ? *reinterpret_cast<const uint4 *>(ap[m] + d * 32) : make_uint4(0, 0, 0, 0);
 
     if (TMA && nkb > 0 && !mbar_wait(&tile_full[warp], 0)) {
-        if (lane == 0) atomicExch(&sl_fault, 1);                // the products below run on what is there: the result is not valid
+        if (lane == 0 && a.fault != nullptr) *reinterpret_cast<volatile int *>(a.fault) = 1;     // the products below run on what is there
         mbar_wait(&tile_full[warp], 0);                          // copies still on their way get a second bounded time to land
     }
     for (int q0 = 0; q0 < nkb; q0 += AHEAD) {
@@ -544,10 +544,22 @@ static size_t small_tile_smem_tma(int K, int MT, int ksplit) {
     const size_t red = (size_t)ksplit * MT * 4 * 32 * sizeof(float);
     return (tile > red ? tile : red) + ST_MAX_WARPS * sizeof(unsigned long long);
 }
+// The word that a tile kernel writes when its bounded wait runs out lies in pinned host memory that the device
+// reaches too: the host reads it without a copy (after the stream is idle).  One word per process.
+static int *fault_word() {
+    static int *word = [] {
+        int *p = nullptr;
+        if (cudaHostAlloc(reinterpret_cast<void **>(&p), sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) return (int *)nullptr;
+        *p = 0;
+        return p;
+    }();
+    return word;
+}
 JK_EXPORT int jk_linear_small_take_fault() {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, sl_fault, sizeof(int)) != cudaSuccess) return -1;
-    if (v != 0) cudaMemcpyToSymbol(sl_fault, &zero, sizeof(int));
+    int *w = fault_word();
+    if (w == nullptr) return 0;
+    const int v = *reinterpret_cast<volatile int *>(w);
+    if (v != 0) *reinterpret_cast<volatile int *>(w) = 0;
     return v;
 }
 
@@ -566,6 +578,7 @@ static int launch_tile(const SmallLinearArgs &a_in, size_t smem, cudaStream_t st
     }
     if (tma) {
         a.ksplit = ks;
+        a.fault = fault_word();          // (unified addressing: the device uses the host's address)
         // How far the activation loads run ahead of the products: all the way where every block has an SM to itself
         // (registers are no object there and no load's latency shows: batch 8 at 512 keys 1.99 -> 1.92 ms a step); else 4
         // blocks of k.  With 16 rows: 4 and 2 (all the way costs 128 registers and spills: batch 16 2.52 -> 2.78 ms).

@@ -322,15 +322,17 @@ _tg_status = {}
 
 
 def gemm_status(device) -> torch.Tensor:
-    """The device word in which the tcgen05 product kernel records a wait that ran out (0: none)."""
+    """The word in which a kernel records a wait that ran out (0: none).  It lies in pinned host memory, which the
+    device reaches under the same address: a kernel that gives up writes across, and the host reads it without a copy."""
     key = str(device)
     if key not in _tg_status:
-        _tg_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        _tg_status[key] = torch.zeros(1, dtype=torch.int32).pin_memory()
     return _tg_status[key]
 
 
 def check_gemm_status(device) -> None:
-    """Read the status word (synchronises); raise if a kernel gave up waiting."""
+    """Wait for the device's work, read the status words; raise if a kernel gave up waiting."""
+    torch.cuda.synchronize(device)
     small = _build._loaded.get("linear_small")
     if small is not None:
         fault = small.jk_linear_small_take_fault()
