@@ -44,7 +44,10 @@ class Generator:
             return []
         entries = [StepEntry(s.request.id, s.tokens, [len(s.tokens) - 1] if s.samples else [])
                    for s in plan]
-        logits = self.engine.step(entries)
+        # a step of single tokens is most often followed by the same requests' next tokens: the engine may prepare that
+        # step while the device runs this one (what it takes ahead is what these requests, who come first, would take
+        # next anyway, and goes back if another step comes)
+        logits = self.engine.step(entries, stage_next=all(len(s.tokens) == 1 for s in plan))
         samplers = [s for s in plan if s.samples]
         params = [SamplingParams(s.request.temperature, s.request.topk, s.request.topp, s.request.seed)
                   for s in samplers]

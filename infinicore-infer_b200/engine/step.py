@@ -89,6 +89,7 @@ class Engine:
         self.kernel_launches = 0      # this package's kernels launched by steps (replayed graphs included)
         # A decode step that was asked to may prepare the step after it while the device still runs (see _stage_next).
         self._staged: Optional[tuple] = None
+        self._may_stage = os.environ.get("JK_NO_STAGE") != "1"
         self.staged_steps = 0         # steps that ran from what the step before them had prepared
 
     # ---- construction -------------------------------------------------------------------------
@@ -165,7 +166,7 @@ class Engine:
     # call brings exactly one token for each of the same requests, only the ids are written, the buffer copied and the
     # graph replayed; if it brings anything else, the pages taken ahead go back before the step is planned.
     def _stage_next(self, reqs: List[object], starts: List[int]) -> None:
-        if any(s + 1 > self.spec.max_positions for s in starts):
+        if not self._may_stage or any(s + 1 > self.spec.max_positions for s in starts):
             return
         B = len(reqs)
         bucket = self._bucket(B)
