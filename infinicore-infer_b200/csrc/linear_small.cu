@@ -350,6 +350,31 @@ small_linear_tile_kernel(const __grid_constant__ CUtensorMap map_w, SmallLinearA
                 }
         }
     }
+    // EPI_QKV: the row's position, its rotation and (key and value heads) the place of its cache slot hang on two loads
+    // in a row each; asked for now, they are there when the products are done
+    float pre_cs[MT][2], pre_sn[MT][2];
+    size_t pre_slot[MT][2];
+    if (EPI == EPI_QKV && warp == 0) {
+        const SmallQkvDest &d = a.qkv;
+        const int half = d.dh / 2, j = qkv_j0 + g, h = qkv_head;
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int row = m * 8 + 2 * t + c;
+                pre_cs[m][c] = 1.f; pre_sn[m][c] = 0.f; pre_slot[m][c] = 0;
+                if (row >= a.M) continue;
+                const int pos = d.positions[row];
+                if (d.cos_table != nullptr && h < d.nh + d.nkvh) {
+                    pre_cs[m][c] = d.cos_table[(size_t)pos * half + j];
+                    pre_sn[m][c] = d.sin_table[(size_t)pos * half + j];
+                }
+                if (h >= d.nh) {
+                    const int page = d.block_table[(size_t)d.row_req[row] * d.max_blocks + pos / d.page_size];
+                    pre_slot[m][c] = ((size_t)page * d.nkvh * d.page_size + (pos % d.page_size)) * d.dh;
+                }
+            }
+    }
 
     const __nv_bfloat16 *ap[MT];
     bool arow[MT];
@@ -476,10 +501,9 @@ small_linear_tile_kernel(const __grid_constant__ CUtensorMap map_w, SmallLinearA
             for (int c = 0; c < 2; ++c) {
                 const int row = m * 8 + 2 * t + c;
                 if (row >= a.M) continue;
-                const int pos = d.positions[row];
                 float y0 = acc[m][c], y1 = acc[m][c + 2];                 // elements j and j + half of head h
                 if (d.cos_table != nullptr && h < d.nh + d.nkvh) {
-                    const float cs = d.cos_table[(size_t)pos * half + j], sn = d.sin_table[(size_t)pos * half + j];
+                    const float cs = pre_cs[m][c], sn = pre_sn[m][c];
                     const float x0 = y0, x1 = y1;
                     y0 = x0 * cs - x1 * sn;
                     y1 = x0 * sn + x1 * cs;
@@ -488,10 +512,8 @@ small_linear_tile_kernel(const __grid_constant__ CUtensorMap map_w, SmallLinearA
                 if (h < d.nh) {
                     dst = d.q_out + ((size_t)row * d.nh + h) * d.dh;
                 } else {
-                    const int page = d.block_table[(size_t)d.row_req[row] * d.max_blocks + pos / d.page_size];
-                    const size_t slot = ((size_t)page * d.nkvh * d.page_size + (pos % d.page_size)) * d.dh;
                     dst = (h < d.nh + d.nkvh ? d.k_pages + (size_t)(h - d.nh) * d.page_size * d.dh
-                                             : d.v_pages + (size_t)(h - d.nh - d.nkvh) * d.page_size * d.dh) + slot;
+                                             : d.v_pages + (size_t)(h - d.nh - d.nkvh) * d.page_size * d.dh) + pre_slot[m][c];
                 }
                 dst[j] = __float2bfloat16_rn(y0);
                 dst[j + half] = __float2bfloat16_rn(y1);
