@@ -14,6 +14,7 @@
 // (reference: the per-request loop of two batched products and a causal softmax over a
 // materialised [nh, s, t] buffer, src/models/jiuge/jiuge.cpp:206-233.)
 #include "common.cuh"
+#include "host_rules.h"
 
 JK_DEFINE_ERROR_BUFFER(jk_attention)
 
@@ -171,6 +172,10 @@ __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// Rows of one request in one launch of a decode kernel: at most this many (jk::SHORT_ROWS of the work lists), so the
+// kernel before a launch writes keys at most this far back from a row's own position.
+constexpr int DECODE_FRESH_ROWS = jk::SHORT_ROWS;
 
 struct DecodeArgs {
     const __nv_bfloat16 *q;        // [T, nh, dh]
@@ -752,7 +757,10 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     const int g = a.nh / a.nkvh;
     const int h0 = kh * g + ht * GQ_HEADS;         // first query head of this block
     const int heads = min(GQ_HEADS, g - ht * GQ_HEADS);
-    pdl_wait();
+    // Not yet the wait for the kernel before this one: what that kernel writes are the queries and, in the cache, the
+    // keys and values of this step's own rows (at most DECODE_FRESH_ROWS positions back from a row's own: the work
+    // lists send requests with more rows elsewhere).  The step's metadata and all older keys are there already, so the
+    // block finds its pages and asks for its first tiles of old keys while the kernel before still runs.
     const int t = a.rows ? a.rows[ri] : ri;
     const int pos = a.positions[t], req = a.row_req[t];
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0, hi = pos + 1;
@@ -764,6 +772,7 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     const size_t pbase = ((size_t)ri * a.nh + h0) * a.splits + split;      // + head * splits
     if (k0 >= k1 && !a.cluster) {                  // nothing for this split: the merge skips it (in a cluster the block
                                                    // goes on with no tiles: the others wait for it at the barriers)
+        pdl_wait();                                // the scratch may still be read by a merge of the layer before
         if (a.splits > 1 && threadIdx.x < heads) {
             a.part_ml[(pbase + (size_t)threadIdx.x * a.splits) * 2] = -INFINITY;
             a.part_ml[(pbase + (size_t)threadIdx.x * a.splits) * 2 + 1] = 0.f;
@@ -810,20 +819,29 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     locate_tile(0);
     locate_tile(1);
     __syncthreads();
+    // the first tiles, as far as they hold old keys only
+    const int old_hi = pos - (DECODE_FRESH_ROWS - 1);
+    int first = 0;
+    for (; first < GQ_STAGES - 1; ++first) {
+        if (first < ntiles && min(k1, k0 + (first + 1) * GQ_KEYS) > old_hi) break;
+        if (first < ntiles) load_tile(first);
+        cp_async_commit();
+    }
+    pdl_wait();
     {
         // the queries of the group's heads are one contiguous piece of q; heads beyond the group read as zeros
         uint4 *qs = gq_smem + (size_t)GQ_STAGES * 2 * TILE + 2 * GQ_KEYS * sizeof(long long) / sizeof(uint4);
         const uint4 *qg = reinterpret_cast<const uint4 *>(a.q + ((size_t)t * a.nh + h0) * DH);
         for (int idx = threadIdx.x; idx < GQ_HEADS * CH; idx += 128) {
             const int head = idx / CH, ch = idx % CH;
-            cp_async16_or_zero(qs + head * CH + (ch ^ (head & 7)), head < heads ? qg + idx : qg, head < heads);
+            qs[head * CH + (ch ^ (head & 7))] = head < heads ? qg[idx] : make_uint4(0u, 0u, 0u, 0u);
         }
     }
-    for (int i = 0; i < GQ_STAGES - 1; ++i) {
+    for (int i = first; i < GQ_STAGES - 1; ++i) {
         if (i < ntiles) load_tile(i);
         cp_async_commit();
     }
-    __syncthreads();                               // the first tables have been read
+    __syncthreads();                               // the first tables have been read (and the queries are written)
     locate_tile(2);
     // the group's queries as A fragments: rows are heads (zero beyond the group), 16 dims per step; they came
     // with the first tile's group of copies into their own 16 x DH corner of shared memory
