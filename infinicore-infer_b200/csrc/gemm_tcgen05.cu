@@ -131,11 +131,45 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // took tensor memory on an SM and then waited for this grid, while a block of this grid still waited
     // for tensor memory there, would never end.
     pdl_trigger();
-    pdl_wait();       // barriers and tensor memory are set up; now the operands of earlier kernels may be read
+    // barriers and tensor memory are set up.  The weights depend on no kernel before this one: the producer asks for
+    // the first stages' tiles of B at once and waits for the kernel before only then, for the activations (A); the
+    // epilogue warps wait before their first access to what earlier kernels wrote.
 
     if (warp == 0) {
         // ---- TMA producer ----
         if (lane == 0) {
+            // one stage's loads: `which` 1: the tile of B (and the count of the stage's bytes), 2: the tile of A, 3: both
+            auto load_stage = [&](int st, int i, int m0, int n0, int which) {
+                if (CTAS == 2) {
+                    // each block loads its own rows of A and its half of the tile's rows of B (gate rows in the
+                    // first block, up rows in the second for SwiGLU); the first block's barrier counts all bytes
+                    if (rank == 0 && (which & 1)) mbar_expect_tx(&s.full[st], STAGE_BYTES);
+                    const unsigned bar = cluster_addr(&s.full[st], 0);
+                    const int w0 = EPI == EPI_SWIGLU ? (rank ? a.N + n0 : n0) : n0 + rank * (BN / 2);
+                    if (which & 2) tma_load_2d_pair(s.a[st], &map_a, bar, i * TG_BK, m0);
+                    if (which & 1) tma_load_2d_pair(s.b[st], &map_w, bar, i * TG_BK, w0);
+                    return;
+                }
+                if (which & 1) mbar_expect_tx(&s.full[st], STAGE_BYTES);
+                if (which & 2) tma_load_2d(s.a[st], &map_a, &s.full[st], i * TG_BK, m0);
+                if (which & 1) {
+                    tma_load_2d(s.b[st], &map_w, &s.full[st], i * TG_BK, n0);
+                    if (EPI == EPI_SWIGLU)
+                        tma_load_2d(s.b[st] + (BN / 2) * TG_BK, &map_w, &s.full[st], i * TG_BK, a.N + n0);
+                }
+            };
+            // the stages that are free from the start, twice: the weights now, the activations after the wait
+            for (int pass = 1; pass <= 2; ++pass) {
+                int it = 0;
+                for (int tile = worker; tile < num_tiles && it < STAGES; tile += workers) {
+                    int tm, tn;
+                    tile_coords(tile / ksplit, tiles_m, tiles_n, tm, tn);
+                    const int m0 = tm * TILE_M + rank * TG_BM, n0 = tn * OUT_COLS;
+                    const int k_first = (tile % ksplit) * nk_unit, nk = min(nk_unit, nk_all - k_first);
+                    for (int i = k_first; i < k_first + nk && it < STAGES; ++i, ++it) load_stage(it, i, m0, n0, pass);
+                }
+                if (pass == 1) pdl_wait();
+            }
             int it = 0;
             for (int tile = worker; tile < num_tiles && !failed; tile += workers) {
                 int tm, tn;
@@ -143,23 +177,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int m0 = tm * TILE_M + rank * TG_BM, n0 = tn * OUT_COLS;
                 const int k_first = (tile % ksplit) * nk_unit, nk = min(nk_unit, nk_all - k_first);
                 for (int i = k_first; i < k_first + nk; ++i, ++it) {
+                    if (it < STAGES) continue;                       // asked for above
                     const int st = it % STAGES;
-                    if (it >= STAGES && !mbar_wait(&s.empty[st], ((it / STAGES) - 1) & 1)) { failed = 1; break; }
-                    if (CTAS == 2) {
-                        // each block loads its own rows of A and its half of the tile's rows of B (gate rows in the
-                        // first block, up rows in the second for SwiGLU); the first block's barrier counts all bytes
-                        if (rank == 0) mbar_expect_tx(&s.full[st], STAGE_BYTES);
-                        const unsigned bar = cluster_addr(&s.full[st], 0);
-                        const int w0 = EPI == EPI_SWIGLU ? (rank ? a.N + n0 : n0) : n0 + rank * (BN / 2);
-                        tma_load_2d_pair(s.a[st], &map_a, bar, i * TG_BK, m0);
-                        tma_load_2d_pair(s.b[st], &map_w, bar, i * TG_BK, w0);
-                        continue;
-                    }
-                    mbar_expect_tx(&s.full[st], STAGE_BYTES);
-                    tma_load_2d(s.a[st], &map_a, &s.full[st], i * TG_BK, m0);
-                    tma_load_2d(s.b[st], &map_w, &s.full[st], i * TG_BK, n0);
-                    if (EPI == EPI_SWIGLU)
-                        tma_load_2d(s.b[st] + (BN / 2) * TG_BK, &map_w, &s.full[st], i * TG_BK, a.N + n0);
+                    if (!mbar_wait(&s.empty[st], ((it / STAGES) - 1) & 1)) { failed = 1; break; }
+                    load_stage(st, i, m0, n0, 3);
                 }
             }
             if (failed) atomicExch(a.status, 1);
@@ -198,6 +219,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     } else {
         // ---- epilogue: warps 2..5, each owns the 32 lanes (rows) warp % 4 of the accumulator ----
+        pdl_wait();                       // what follows reads and writes what earlier kernels wrote
         const int quarter = warp & 3;
         unsigned char *stage = s.stage_out[quarter];
         int j = 0;
