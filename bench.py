@@ -293,7 +293,7 @@ def main():
     page = 16
     max_b = 1 if args.no_points else 64
     max_b = max(max_b, args.batch)
-    cache_tokens = max_b * (args.context + page)
+    cache_tokens = max(max_b * (args.context + page), 2048 + 4 * page)      # the decode points, or the prompt of 2,048 tokens
     t_load = time.time()
     weights = DeviceRandomWeights(model_manifest(spec), seed=0, compute_dtype=torch.bfloat16, device=dev, std=0.02,
                                   untied=not shape["tie_word_embeddings"])
