@@ -443,7 +443,7 @@ def main():
         psteps, pwarm = min(args.steps, 32), 4
         for name, b, c in (("decode_b1", 1, args.context), ("decode_b64", 64, args.context),
                            ("decode_b1_ctx512", 1, 512), ("decode_b8_ctx512", 8, 512), ("decode_b64_ctx512", 64, 512)):
-            pm, _, _ = decode_device(b, c, psteps, pwarm)
+            pm = sorted(decode_device(b, c, psteps, pwarm)[0] for _ in range(3))[1]       # the median of three runs
             result_points[name] = round(b * 1000.0 / pm, 1)
 
     # ---- each dominant kernel alone ---------------------------------------------------------------------------
