@@ -724,7 +724,7 @@ static int launch_prefill(const PrefillArgs &a, cudaStream_t stream) {
 // sum and accumulator, the four are merged through shared memory at the end.  Output as the kernel
 // above: final rows when there is one split, partial (accumulator, maximum, sum) else.
 // =======================================================================================
-constexpr int GQ_KEYS = 64, GQ_STAGES = 3, GQ_HEADS = 16;
+constexpr int GQ_STAGES = 3, GQ_HEADS = 16;
 
 __device__ __forceinline__ void cp_async16_or_zero(void *smem, const void *gmem, bool valid) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -744,12 +744,16 @@ __device__ __forceinline__ void cluster_sync_all() {      // every thread of eve
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 
-template <int DH>
-__global__ void __launch_bounds__(128)
+// NW warps take 16 keys each of a tile of NW * 16 keys: four as a rule; eight (tiles of 128 keys, one block an SM with
+// heads of 128) for launches of so few blocks that every SM has at most one: a block's pace is set by the chain of a
+// tile's instructions in each warp, and twice the warps pass twice the keys in the same time.
+template <int DH, int NW>
+__global__ void __launch_bounds__(NW * 32)
 attention_decode_gqa_kernel(DecodeArgs a) {
+    constexpr int KEYS = NW * 16, NT = NW * 32;
     static_assert(DH == 64 || DH == 128, "the swizzle chunk ^ (key & 7) needs rows of 8 or 16 chunks");
     constexpr int CH = DH / 8;                     // 16-byte chunks of a key row
-    constexpr int TILE = GQ_KEYS * CH;             // uint4 per tile of keys (or values)
+    constexpr int TILE = KEYS * CH;             // uint4 per tile of keys (or values)
     extern __shared__ uint4 gq_smem[];
     pdl_trigger();
     const int split = blockIdx.x, kh = blockIdx.y % a.nkvh, ht = blockIdx.y / a.nkvh, ri = blockIdx.z;
@@ -764,11 +768,11 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     const int t = a.rows ? a.rows[ri] : ri;
     const int pos = a.positions[t], req = a.row_req[t];
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0, hi = pos + 1;
-    const int tiles_all = (hi - lo + GQ_KEYS - 1) / GQ_KEYS;
+    const int tiles_all = (hi - lo + KEYS - 1) / KEYS;
     // at least two tiles per split (a block's fixed part costs more than a tile): short contexts use fewer of the
     // splits that the grid was sized for, the others report that they saw nothing
     const int per = max(2, (tiles_all + a.splits - 1) / a.splits);
-    const int k0 = lo + split * per * GQ_KEYS, k1 = min(hi, k0 + per * GQ_KEYS);
+    const int k0 = lo + split * per * KEYS, k1 = min(hi, k0 + per * KEYS);
     const size_t pbase = ((size_t)ri * a.nh + h0) * a.splits + split;      // + head * splits
     if (k0 >= k1 && !a.cluster) {                  // nothing for this split: the merge skips it (in a cluster the block
                                                    // goes on with no tiles: the others wait for it at the barriers)
@@ -779,36 +783,36 @@ attention_decode_gqa_kernel(DecodeArgs a) {
         }
         return;
     }
-    const int ntiles = (k1 - k0 + GQ_KEYS - 1) / GQ_KEYS;
+    const int ntiles = (k1 - k0 + KEYS - 1) / KEYS;
     const int *bt = a.block_table + (size_t)req * a.max_blocks;
 
     // Where a tile's 64 keys lie (element offset of the key's row in the pages, -1 beyond the range) is worked out
     // once per tile by 64 threads into a table of two turns; the copies then cost a table read each.
-    long long *tab = reinterpret_cast<long long *>(gq_smem + (size_t)GQ_STAGES * 2 * TILE);       // [2][GQ_KEYS]
+    long long *tab = reinterpret_cast<long long *>(gq_smem + (size_t)GQ_STAGES * 2 * TILE);       // [2][KEYS]
     // in two halves: the read of the block table is issued at the start of an iteration and used at its end, so
     // that the warp does not sit on it
     auto locate_begin = [&](int i) -> int {
-        const int kj = k0 + i * GQ_KEYS + threadIdx.x;
-        return threadIdx.x < GQ_KEYS && kj < k1 ? bt[kj / a.page_size] : -1;
+        const int kj = k0 + i * KEYS + threadIdx.x;
+        return threadIdx.x < KEYS && kj < k1 ? bt[kj / a.page_size] : -1;
     };
     auto locate_end = [&](int i, int page) {
-        if (threadIdx.x < GQ_KEYS) {
-            const int kj = k0 + i * GQ_KEYS + threadIdx.x;
-            tab[(i & 1) * GQ_KEYS + threadIdx.x] =
+        if (threadIdx.x < KEYS) {
+            const int kj = k0 + i * KEYS + threadIdx.x;
+            tab[(i & 1) * KEYS + threadIdx.x] =
                 page < 0 ? -1 : (((long long)page * a.nkvh + kh) * a.page_size + kj % a.page_size) * DH;
         }
     };
     auto locate_tile = [&](int i) { locate_end(i, locate_begin(i)); };
     // 16 bytes of key `key` of a tile lie at chunk ^ (key & 7): ldmatrix reads eight rows without conflicts.  A
     // thread copies the same chunk of every (128 / CH)-th key, so its swizzled chunk never changes.
-    constexpr int KEYS_PER_PASS = 128 / CH;
+    constexpr int KEYS_PER_PASS = NT / CH;
     const int my_key = threadIdx.x / CH, my_ch = threadIdx.x % CH;
     const int my_slot = my_key * CH + (my_ch ^ (my_key & 7));
     auto load_tile = [&](int i) {
         uint4 *kd = gq_smem + (size_t)(i % GQ_STAGES) * 2 * TILE + my_slot, *vd = kd + TILE;
-        const long long *where = tab + (i & 1) * GQ_KEYS + my_key;
+        const long long *where = tab + (i & 1) * KEYS + my_key;
 #pragma unroll
-        for (int c = 0; c < GQ_KEYS / KEYS_PER_PASS; ++c) {
+        for (int c = 0; c < KEYS / KEYS_PER_PASS; ++c) {
             const long long off = where[c * KEYS_PER_PASS];
             const bool valid = off >= 0;
             const size_t src = valid ? (size_t)off + my_ch * 8 : 0;
@@ -823,16 +827,16 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     const int old_hi = pos - (DECODE_FRESH_ROWS - 1);
     int first = 0;
     for (; first < GQ_STAGES - 1; ++first) {
-        if (first < ntiles && min(k1, k0 + (first + 1) * GQ_KEYS) > old_hi) break;
+        if (first < ntiles && min(k1, k0 + (first + 1) * KEYS) > old_hi) break;
         if (first < ntiles) load_tile(first);
         cp_async_commit();
     }
     pdl_wait();
     {
         // the queries of the group's heads are one contiguous piece of q; heads beyond the group read as zeros
-        uint4 *qs = gq_smem + (size_t)GQ_STAGES * 2 * TILE + 2 * GQ_KEYS * sizeof(long long) / sizeof(uint4);
+        uint4 *qs = gq_smem + (size_t)GQ_STAGES * 2 * TILE + 2 * KEYS * sizeof(long long) / sizeof(uint4);
         const uint4 *qg = reinterpret_cast<const uint4 *>(a.q + ((size_t)t * a.nh + h0) * DH);
-        for (int idx = threadIdx.x; idx < GQ_HEADS * CH; idx += 128) {
+        for (int idx = threadIdx.x; idx < GQ_HEADS * CH; idx += NT) {
             const int head = idx / CH, ch = idx % CH;
             qs[head * CH + (ch ^ (head & 7))] = head < heads ? qg[idx] : make_uint4(0u, 0u, 0u, 0u);
         }
@@ -849,7 +853,7 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     {
         cp_async_wait<GQ_STAGES - 2>();
         __syncthreads();
-        const uint4 *qs = gq_smem + (size_t)GQ_STAGES * 2 * TILE + 2 * GQ_KEYS * sizeof(long long) / sizeof(uint4);
+        const uint4 *qs = gq_smem + (size_t)GQ_STAGES * 2 * TILE + 2 * KEYS * sizeof(long long) / sizeof(uint4);
         // matrices: (heads 0-7, dims 0-7), (heads 8-15, dims 0-7), (heads 0-7, dims 8-15), (heads 8-15, dims 8-15)
         const int head = (((lane >> 3) & 1) << 3) + (lane & 7);
 #pragma unroll
@@ -870,7 +874,7 @@ attention_decode_gqa_kernel(DecodeArgs a) {
         if (i + GQ_STAGES - 1 < ntiles) load_tile(i + GQ_STAGES - 1);
         cp_async_commit();
         const uint4 *kt = gq_smem + (size_t)(i % GQ_STAGES) * 2 * TILE, *vt = kt + TILE;
-        const int kw = k0 + i * GQ_KEYS + warp * 16;          // this warp's first key of the tile
+        const int kw = k0 + i * KEYS + warp * 16;          // this warp's first key of the tile
         if (kw >= k1) {                                        // warp-uniform: no key of the tile is this warp's
             locate_end(i + GQ_STAGES, page_ahead);
             continue;
@@ -941,12 +945,12 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     cp_async_wait<0>();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    __syncthreads();                               // the ring is free: it carries the four warps' results
+    __syncthreads();                               // the ring is free: it carries the warps' results
     // [warp][head][DH + 8]: the accumulator, then maximum and sum; with this stride the 8-byte stores of a half warp
     // (four heads, dims 0..7) fall into 32 different banks
     constexpr int RS = DH + 8;
     float *red = reinterpret_cast<float *>(gq_smem);
-    float *fin = red + 4 * GQ_HEADS * RS, *fin_ml = fin + GQ_HEADS * DH;      // this block's result, for its cluster
+    float *fin = red + NW * GQ_HEADS * RS, *fin_ml = fin + GQ_HEADS * DH;      // this block's result, for its cluster
     {
         float *mine = red + (size_t)warp * GQ_HEADS * RS;
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
@@ -961,14 +965,14 @@ attention_decode_gqa_kernel(DecodeArgs a) {
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < heads * DH; idx += 128) {
+    for (int idx = threadIdx.x; idx < heads * DH; idx += NT) {
         const int r = idx / DH, e = idx % DH;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, red[((size_t)w * GQ_HEADS + r) * RS + DH]);
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, red[((size_t)w * GQ_HEADS + r) * RS + DH]);
         float L = 0.f, A = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < NW; ++w) {
             const float *src = red + ((size_t)w * GQ_HEADS + r) * RS;
             const float f = M == -INFINITY ? 0.f : fast_exp2(src[DH] - M);      // a warp without keys: 2^-inf = 0
             L += f * src[DH + 1];
@@ -990,7 +994,7 @@ attention_decode_gqa_kernel(DecodeArgs a) {
         // out of their shared memory and writes the row (the same sums, in the same order, as the merge kernel)
         cluster_sync_all();
         if (split == 0) {
-            for (int idx = threadIdx.x; idx < heads * DH; idx += 128) {
+            for (int idx = threadIdx.x; idx < heads * DH; idx += NT) {
                 const int r = idx / DH;
                 float M = -INFINITY;
                 for (int p = 0; p < a.splits; ++p) M = fmaxf(M, ld_cluster_f32(fin_ml + 2 * r, p));
@@ -1010,42 +1014,51 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     }
 }
 
-template <int DH>
-static int launch_decode_gqa(const DecodeArgs &a, cudaStream_t stream) {
+template <int DH, int NW>
+static int launch_decode_gqa_warps(const DecodeArgs &a, int sms, cudaStream_t stream) {
+    constexpr int KEYS = NW * 16;
     const int g = a.nh / a.nkvh;
-    const size_t ring = (size_t)GQ_STAGES * 2 * GQ_KEYS * DH * sizeof(__nv_bfloat16) + 2 * GQ_KEYS * sizeof(long long)
+    const size_t ring = (size_t)GQ_STAGES * 2 * KEYS * DH * sizeof(__nv_bfloat16) + 2 * KEYS * sizeof(long long)
                         + (size_t)GQ_HEADS * DH * sizeof(__nv_bfloat16);       // tiles, the two tables, the queries
-    const size_t merge = (size_t)4 * GQ_HEADS * (DH + 8) * sizeof(float) + (size_t)GQ_HEADS * (DH + 2) * sizeof(float);
+    const size_t merge = (size_t)NW * GQ_HEADS * (DH + 8) * sizeof(float) + (size_t)GQ_HEADS * (DH + 2) * sizeof(float);
     const size_t smem = ring > merge ? ring : merge;
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_gqa_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_gqa_kernel<DH, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_decode: %s", cudaGetErrorString(e));
     dim3 grid(a.splits, a.nkvh * ((g + GQ_HEADS - 1) / GQ_HEADS), a.nrows);
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
-    }
     // Measured: with heads of 64 (52 KB of shared memory a block) clusters of two are faster than the merge kernel
     // (48.6 against 50.0 us at 8 x 4096 keys, 36 heads), and larger ones as long as all blocks are resident at once (a
     // single row: 14.1 us at eight splits); larger clusters in several waves, and any cluster of the 103 KB blocks of
     // heads of 128, wait for whole groups of free SMs and lose more than the merge kernel costs (37.6 against 30.9 us).
     const long long blocks = (long long)grid.x * grid.y * grid.z;
-    if (DH == 64 && a.splits >= 2 && a.splits <= 8 && (a.splits == 2 || blocks <= 2LL * sms)) {
+    if (DH == 64 && NW == 4 && a.splits >= 2 && a.splits <= 8 && (a.splits == 2 || blocks <= 2LL * sms)) {
         // the splits are one cluster and merge through distributed shared memory: no merge kernel, no scratch
         DecodeArgs c = a;
         c.cluster = 1;
-        const cudaError_t err = jk_launch_clusters(attention_decode_gqa_kernel<DH>, a.splits, grid, dim3(128), smem, stream, c);
+        const cudaError_t err = jk_launch_clusters(attention_decode_gqa_kernel<DH, NW>, a.splits, grid, dim3(NW * 32), smem, stream, c);
         if (err != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "attention_decode_gqa (clusters of %d): %s", a.splits, cudaGetErrorString(err));
         return JK_OK;
     }
-    jk_launch(attention_decode_gqa_kernel<DH>, grid, dim3(128), smem, stream, a);
+    jk_launch(attention_decode_gqa_kernel<DH, NW>, grid, dim3(NW * 32), smem, stream, a);
     JK_CHECK_LAUNCH("attention_decode_gqa");
     if (a.splits > 1) {
         jk_launch(attention_combine_kernel, dim3(a.nh, a.nrows), dim3(64), 0, stream, a);
         JK_CHECK_LAUNCH("attention_combine");
     }
     return JK_OK;
+}
+
+template <int DH>
+static int launch_decode_gqa(const DecodeArgs &a, cudaStream_t stream) {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    static const bool wide_off = [] { const char *v = getenv("JK_GQA_NO_WIDE"); return v && v[0] == '1'; }();
+    const long long blocks = (long long)a.splits * a.nkvh * ((a.nh / a.nkvh + GQ_HEADS - 1) / GQ_HEADS) * a.nrows;
+    if (DH == 128 && blocks <= sms && !wide_off) return launch_decode_gqa_warps<DH, 8>(a, sms, stream);
+    return launch_decode_gqa_warps<DH, 4>(a, sms, stream);
 }
 
 // Head sizes 64 and 128 go to the tensor-core decode kernel, which reads keys and values once per group of query

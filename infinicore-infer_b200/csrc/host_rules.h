@@ -187,6 +187,10 @@ inline int decode_splits(int nrows, int nkvh, int group, int keys, int sms, int 
         const long long slots = 2LL * sms;
         long long s = std::max(1LL, std::min({(2 * slots + blocks) / (2 * blocks), (long long)keys / 256, 32LL}));
         while (blocks * (s + 1) <= 2 * slots && keys / (s + 1) >= 1024 && s < 32) ++s;
+        // heads of 128: a launch of at most one block an SM runs blocks of eight warps, which pass keys twice as fast;
+        // half the cuts is then better than two rounds of the narrow blocks (16 rows x 4,096 keys, 2 key/value heads:
+        // 18.3 against 21.5 us)
+        if (dh == 128 && blocks * s > sms && blocks * (s / 2) <= sms && s >= 2) s /= 2;
         return (int)s;
     }
     const long long blocks = std::max(1, nrows * nkvh * (group > 4 ? (group + 3) / 4 : 1));

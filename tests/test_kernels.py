@@ -454,6 +454,23 @@ def test_attention_prefill_kernel_on_tensor_cores(K, nh, nkvh, dh, page, window)
     _close(got, want, torch.bfloat16, scale=2.0)
 
 
+@pytest.mark.parametrize("requests,splits", [(3, 4), (40, 2), (20, 8)])
+def test_grouped_decode_attention_with_heads_of_128_in_blocks_of_four_and_of_eight_warps(K, requests, splits):
+    """Heads of 128: a launch of at most one block an SM (3 requests x 2 key/value heads x 4 cuts) runs blocks of eight
+    warps on tiles of 128 keys, a larger one (40 x 2 x 2, 20 x 2 x 8) blocks of four on tiles of 64; both against the
+    plain attention, with a key far back that one row must find."""
+    nh, nkvh, dh, page = 32, 2, 128, 16
+    g = torch.Generator().manual_seed(requests)
+    lens = [int(x) for x in torch.randint(130, 700, (requests,), generator=g)]
+    queries = [[n - 1] for n in lens]
+    plant = [(0, lens[0] - 1, 3, 17), (requests - 1, lens[-1] - 1, lens[-1] // 2, 5)]
+    got, want, v = _attention_case(K, torch.bfloat16, nh, nkvh, dh, page, None, lens, queries, plant=plant, seed=7,
+                                   impl="decode", splits=splits)
+    _close(got, want, torch.bfloat16, scale=2.0)
+    assert torch.allclose(got[0, 17].float().cpu(), v[0][3, 17 // 16], atol=2e-2)        # the row found the far key
+    assert torch.allclose(got[requests - 1, 5].float().cpu(), v[-1][lens[-1] // 2, 0], atol=2e-2)
+
+
 @pytest.mark.parametrize("nh,nkvh,dh,page,window", [(4, 4, 64, 16, None), (3, 1, 64, 8, None), (8, 2, 128, 16, None),
                                                      (6, 2, 64, 32, 100), (2, 1, 128, 64, 33), (4, 2, 64, 128, None),
                                                      (36, 36, 64, 16, None)])
