@@ -454,12 +454,14 @@ def test_attention_prefill_kernel_on_tensor_cores(K, nh, nkvh, dh, page, window)
     _close(got, want, torch.bfloat16, scale=2.0)
 
 
-@pytest.mark.parametrize("requests,splits", [(3, 4), (40, 2), (20, 8)])
-def test_grouped_decode_attention_with_heads_of_128_in_blocks_of_four_and_of_eight_warps(K, requests, splits):
-    """Heads of 128: a launch of at most one block an SM (3 requests x 2 key/value heads x 4 cuts) runs blocks of eight
-    warps on tiles of 128 keys, a larger one (40 x 2 x 2, 20 x 2 x 8) blocks of four on tiles of 64; both against the
-    plain attention, with a key far back that one row must find."""
-    nh, nkvh, dh, page = 32, 2, 128, 16
+@pytest.mark.parametrize("dh", [64, 128])
+@pytest.mark.parametrize("requests,splits", [(3, 4), (40, 2), (18, 8), (20, 8)])
+def test_grouped_decode_attention_in_blocks_of_four_and_of_eight_warps(K, dh, requests, splits):
+    """A launch of at most one block an SM (3 requests x 2 key/value heads x 4 cuts) runs blocks of eight warps on tiles
+    of 128 keys, a larger one blocks of four on tiles of 64, whose cuts merge inside clusters (heads of 64: 40 x 2 x 2 and
+    18 x 2 x 8) or through the merge kernel (20 x 2 x 8, and heads of 128); all against the plain attention, with a key
+    far back that a row must find."""
+    nh, nkvh, page = 32, 2, 16
     g = torch.Generator().manual_seed(requests)
     lens = [int(x) for x in torch.randint(130, 700, (requests,), generator=g)]
     queries = [[n - 1] for n in lens]
