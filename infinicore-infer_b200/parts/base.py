@@ -78,7 +78,8 @@ class Runtime:
         self.tcgen05_min_rows = 129
         self.tcgen05_min_tiles = 200
         self.tcgen05_min_fill_pct = 80
-        self.skinny_min_blocks: Optional[int] = None   # fewest blocks for the few-rows tcgen05 kernel (None: one per SM)
+        # fewest blocks for the few-rows tcgen05 kernel (None: one per SM); JK_SKINNY_MIN_BLOCKS=n sets it for a comparison
+        self.skinny_min_blocks: Optional[int] = int(os.environ["JK_SKINNY_MIN_BLOCKS"]) if os.environ.get("JK_SKINNY_MIN_BLOCKS") else None
         # steps of at most 16 rows run without norm kernels (the products around a norm share its work:
         # csrc/linear_small.cu, SmallNormFuse); JK_NO_FUSED_NORM=1 keeps the norm kernels
         self.fused_norms = os.environ.get("JK_NO_FUSED_NORM") != "1"
