@@ -1028,7 +1028,8 @@ static int launch_decode_gqa_warps(const DecodeArgs &a, int sms, cudaStream_t st
     // Measured: with heads of 64 (52 KB of shared memory a block) clusters of two are faster than the merge kernel
     // (48.6 against 50.0 us at 8 x 4096 keys, 36 heads), and larger ones as long as all blocks are resident at once (a
     // single row: 14.1 us at eight splits); larger clusters in several waves, and any cluster of the 103 KB blocks of
-    // heads of 128, wait for whole groups of free SMs and lose more than the merge kernel costs (37.6 against 30.9 us).
+    // heads of 128, wait for whole groups of free SMs and lose more than the merge kernel costs (37.6 against 30.9 us;
+    // the blocks of eight warps, 203 KB each, in clusters of eight: 36.1 against 15.0 us at 8 rows x 4,096 keys).
     const long long blocks = (long long)grid.x * grid.y * grid.z;
     if (DH == 64 && NW == 4 && a.splits >= 2 && a.splits <= 8 && (a.splits == 2 || blocks <= 2LL * sms)) {
         // the splits are one cluster and merge through distributed shared memory: no merge kernel, no scratch
