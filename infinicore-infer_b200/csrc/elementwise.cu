@@ -110,6 +110,54 @@ __global__ void add_rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__
     }
 }
 
+// The same for steps of many rows: a warp per row, the row in registers (NV groups of four floats a lane), every load
+// of a row on its way before the first is used, no shared memory and no barrier (a prefill of 2,048 tokens of the 2B
+// shape: 9.94 -> 9.90 ms).
+template <typename TD, typename TO, int NV>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_kernel(float *__restrict__ x, const TD *__restrict__ delta, float delta_scale, const float *__restrict__ w, float eps,
+                        float out_scale, TO *__restrict__ out, const int *__restrict__ rows, int nout, int d) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (i >= nout) return;
+    const int r = rows ? rows[i] : i;
+    float *xr = x + (size_t)r * d;
+    const TD *dr = delta ? delta + (size_t)r * d : nullptr;
+    float4 v[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int c = (j * 32 + lane) * 4;
+        v[j] = c < d ? load4(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (dr) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int c = (j * 32 + lane) * 4;
+            if (c < d) {
+                const float4 dv = load4(dr + c);
+                v[j] = make_float4(v[j].x + delta_scale * dv.x, v[j].y + delta_scale * dv.y, v[j].z + delta_scale * dv.z, v[j].w + delta_scale * dv.w);
+                if (!rows) store4(xr + c, v[j]);
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)d + eps) * out_scale;
+    TO *o = out + (size_t)i * d;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int c = (j * 32 + lane) * 4;
+        if (c < d) {
+            const float4 g = load4(w + c);
+            store4(o + c, make_float4(v[j].x * inv * g.x, v[j].y * inv * g.y, v[j].z * inv * g.z, v[j].w * inv * g.w));
+        }
+    }
+}
+
 template <typename TD, typename TO>
 static int launch_add_rmsnorm(float *x, const void *delta, float delta_scale, const float *w,
                               float eps, float out_scale, void *out, const int *rows, int nout,
@@ -122,6 +170,19 @@ static int launch_add_rmsnorm(float *x, const void *delta, float delta_scale, co
         cudaError_t e = vec ? cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
                             : cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "add_rmsnorm: %s", cudaGetErrorString(e));
+    }
+    if (vec && nout >= 256 && d <= 24 * 128) {
+        // many rows: a warp per row
+        const int blocks = (nout + 7) / 8;
+#define JK_ROWS_LAUNCH(NV_)                                                                                              \
+        jk_launch(add_rmsnorm_rows_kernel<TD, TO, NV_>, dim3(blocks), dim3(256), 0, stream, x, (const TD *)delta, delta_scale, w, eps, \
+                  out_scale, (TO *)out, rows, nout, d)
+        if (d <= 8 * 128) JK_ROWS_LAUNCH(8);
+        else if (d <= 16 * 128) JK_ROWS_LAUNCH(16);
+        else JK_ROWS_LAUNCH(24);
+#undef JK_ROWS_LAUNCH
+        JK_CHECK_LAUNCH("add_rmsnorm");
+        return JK_OK;
     }
     if (vec) {
         const int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);

@@ -42,7 +42,8 @@ def test_embed(K, dtype, V, d, T):
 
 @pytest.mark.parametrize("out_dtype", DTYPES)
 @pytest.mark.parametrize("delta_dtype", [None, torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,d,eps", [(5, 80, 1e-5), (3, 2304, 1e-6), (2, 5000, 3e-6), (1, 14336, 1e-5)])
+@pytest.mark.parametrize("T,d,eps", [(5, 80, 1e-5), (3, 2304, 1e-6), (2, 5000, 3e-6), (1, 14336, 1e-5),
+                                     (300, 2304, 1e-6), (261, 1000, 1e-5), (257, 3072, 1e-5), (256, 132, 1e-5), (400, 3076, 1e-5)])
 def test_add_rmsnorm(K, out_dtype, delta_dtype, T, d, eps):
     g = torch.Generator().manual_seed(d)
     x = torch.randn(T, d, generator=g) * 3
@@ -64,6 +65,16 @@ def test_add_rmsnorm_gathers_rows_without_touching_the_stream(K):
     rows = torch.tensor([8, 0, 3, 3], dtype=torch.int32)
     xd = x.to(DEV).clone()
     out = torch.empty(4, 96, device=DEV)
+    K.add_rmsnorm(xd, delta.to(DEV), 2.0, w.to(DEV), 1e-6, out, rows=rows.to(DEV))
+    assert torch.equal(xd.cpu(), x)
+    _close(out, plain_rmsnorm((x + 2 * delta).double()[rows.long()], w.double(), 1e-6), torch.float32)
+    # many gathered rows (a warp a row)
+    x = torch.randn(400, 264, generator=g)
+    delta = torch.randn(400, 264, generator=g)
+    w = 1 + 0.1 * torch.randn(264, generator=g)
+    rows = torch.randint(0, 400, (300,), generator=g).to(torch.int32)
+    xd = x.to(DEV).clone()
+    out = torch.empty(300, 264, device=DEV)
     K.add_rmsnorm(xd, delta.to(DEV), 2.0, w.to(DEV), 1e-6, out, rows=rows.to(DEV))
     assert torch.equal(xd.cpu(), x)
     _close(out, plain_rmsnorm((x + 2 * delta).double()[rows.long()], w.double(), 1e-6), torch.float32)
